@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-KV decode-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg0|cfg3] [--impl reference]
+
+One *step* is one decode step's worth of attention: every layer of the workload attends once
+over its packed cache (one `mixed_attn_decode` call per layer).  The default workload is the
+Qwen3-8B-shaped configuration: 36 layers, 32 query / 8 KV heads, head_dim 128, 32 sequences of
+16384 tokens per GPU, per-block rungs drawn 10/20/40/20/10 % over 16/8/4/2-bit/centroid with the
+first and last block of each row at 16-bit.  All inputs are synthetic and seeded; nothing is read
+from disk.  Sequences are independent, so N GPUs run N disjoint batches with no collective on
+the data path (weak scaling).
+
+Prints ONE JSON line on rank 0.  `value` is whole-job context-tokens/s with every input resident
+in HBM; `e2e` is the same metric through the Python entry point with the step's queries coming
+from pinned host memory and the outputs read back; `roofline` compares the decode kernel's
+algorithmic bytes per launch with the measured HBM copy bandwidth; `cpu_baseline` times the CPU
+oracle on a bounded sample (rank 0, N=1 only).
+
+`--impl reference` times the CPU restatement of the reference's path on the host cores instead
+(the reference ships no CPU kernel and its Python cannot travel to the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: layers, Hq, Hkv, D, seqs per GPU, tokens, rung probabilities (16, 8, 4, 2, centroid)
+    "cfg1": dict(layers=36, Hq=32, Hkv=8, D=128, B=32, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
+                 name="qwen3-8b-shape decode attention, 36 layers, 32 seq x 16384 tok per GPU"),
+    "cfg0": dict(layers=64, Hq=16, Hkv=2, D=128, B=1, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
+                 name="qwen2.5-3b-shape single-sequence layer, 64 distinct layer buffers of 16384 tok"),
+    "cfg3": dict(layers=28, Hq=28, Hkv=4, D=128, B=1, T=1048576, probs=(0.02, 0.08, 0.30, 0.40, 0.20),
+                 name="qwen2.5-7b-1m-shape decode attention, 28 layers, 1 seq x 1048576 tok"),
+}
+GROUP = 32
+LADDER = (16, 8, 4, 2, 1)
+METRIC = "packed_kv_decode_attn_context_tokens_per_s"
+UNIT = "context-tokens/s"
+
+
+def measured_peak_gbs():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def draw_levels(seed, B, Hkv, nb, probs):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    pick = torch.multinomial(torch.tensor(probs), B * Hkv * nb, replacement=True, generator=g)
+    lv = torch.tensor(LADDER, dtype=torch.int32)[pick].view(B, Hkv, nb)
+    lv[..., 0] = 16
+    lv[..., -1] = 16
+    return lv
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                smax = float(r[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_layers(w, rank, device):
+    """Seeded packed caches, one per layer, built by the GPU pack kernel."""
+    import torch
+    from geodesia_kv_b200.pack_layout import pack_cache
+    caches = []
+    nb = w["T"] // 64
+    for layer in range(w["layers"]):
+        gen = torch.Generator(device=device).manual_seed(1000 + layer + 100003 * rank)
+        # K ~ N(0,1) with 4 outlier channels per head scaled x8, V ~ N(0,1); one (B, Hkv) slab at a time
+        k = torch.randn(w["B"], w["Hkv"], w["T"], w["D"], device=device, dtype=torch.bfloat16, generator=gen)
+        v = torch.randn(w["B"], w["Hkv"], w["T"], w["D"], device=device, dtype=torch.bfloat16, generator=gen)
+        ch = torch.rand(w["Hkv"], w["D"], device=device, generator=gen).argsort(-1)[:, :4]
+        scale = torch.ones(w["Hkv"], w["D"], device=device, dtype=torch.bfloat16)
+        scale.scatter_(1, ch, 8.0)
+        k *= scale[None, :, None, :]
+        level = draw_levels(1000 + layer + 100003 * rank, w["B"], w["Hkv"], nb, w["probs"]).to(device)
+        caches.append(pack_cache(k, v, level, GROUP))
+        del k, v
+    return caches
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from geodesia_kv_b200 import cuda_ext
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ext = cuda_ext.get_ext()
+    if ext is None:
+        raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
+
+    w = WORKLOADS[args.workload]
+    caches = build_layers(w, rank, device)
+    L, B, Hq, D = w["layers"], w["B"], w["Hq"], w["D"]
+    gen = torch.Generator(device=device).manual_seed(5 + rank)
+    qs = [torch.randn(B, Hq, D, device=device, generator=gen) * D ** -0.5 for _ in range(L)]
+    alg_bytes = [c.algorithmic_bytes() + 2 * 4 * B * Hq * D for c in caches]
+    cache_bytes = sum(c.data.numel() for c in caches)
+
+    def step_resident():
+        for c, q in zip(caches, qs):
+            ext.mixed_attn_decode(q, *c.kernel_args())
+
+    q_host = [q.cpu().pin_memory() for q in qs]
+    o_host = [torch.empty(B, Hq, D).pin_memory() for _ in range(L)]
+    q_dev = [torch.empty_like(q) for q in qs]
+
+    def step_e2e():
+        for i, c in enumerate(caches):
+            q_dev[i].copy_(q_host[i], non_blocking=True)
+            out = ext.mixed_attn_decode(q_dev[i], *c.kernel_args())
+            o_host[i].copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+
+    ms_step = ms_total / args.steps
+    tokens_per_step = world * B * w["T"]
+    value = tokens_per_step / (ms_step / 1e3)
+    peak, peak_kind = measured_peak_gbs()
+    launches = args.steps * L
+    avg_launch_s = (ms_total / 1e3) / launches
+    bytes_per_launch = sum(alg_bytes) / L
+    achieved = bytes_per_launch / avg_launch_s / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
+        "config": {"workload": w["name"], "layers": L, "q_heads": Hq, "kv_heads": w["Hkv"], "head_dim": D,
+                   "sequences_per_gpu": B, "context_tokens": w["T"], "group": GROUP,
+                   "rung_mix_16_8_4_2_c": list(w["probs"]), "sharding": f"dp{world}: independent sequences, no collective",
+                   "l2": f"inputs larger than L2: {cache_bytes / 1e9:.1f} GB of packed cache per GPU, each layer read once per step"},
+        "per_gpu": value / world,
+        "hbm_gbs_per_gpu": achieved,
+        "e2e": {"value": tokens_per_step / (ms_e2e / args.steps / 1e3), "unit": UNIT,
+                "h2d_bytes_per_step": L * B * Hq * D * 4, "d2h_bytes_per_step": L * B * Hq * D * 4,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": 2 * launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "kernel": "decode split kernel (+ its LSE combine, timed together)",
+                     "algorithmic_bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_launch_s * 1e6},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_from_cache(caches[0], qs[0], w)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_from_cache(cache, q, w, max_seconds=25.0):
+    """The CPU oracle on one layer of the workload (all host threads), bounded in time."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import gkv_oracle
+    gkv_oracle.build()
+    u16 = lambda t: t.cpu().view(__import__("torch").int16).numpy().view(np.uint16)
+    B = cache.data.shape[0]
+    # size the sample from a one-sequence probe so the whole leg stays within max_seconds
+    def run(nseq):
+        args = (q[:nseq].cpu().numpy(), cache.data[:nseq].cpu().numpy(), cache.offs[:nseq].cpu().numpy(),
+                u16(cache.klo[:nseq]), u16(cache.kstep[:nseq]), u16(cache.vlo[:nseq]), u16(cache.vstep[:nseq]),
+                cache.level[:nseq].cpu().numpy(), cache.valid[:nseq].cpu().numpy(), 64, cache.group)
+        t0 = time.perf_counter()
+        gkv_oracle.mixed_attn_decode(*args)
+        return time.perf_counter() - t0
+    probe = run(1)
+    nseq = max(1, min(B, int(max_seconds * 0.6 / max(probe, 1e-6))))
+    dt = min(run(nseq) for _ in range(1)) if nseq > 1 else probe
+    tokens = nseq * w["T"] / w["layers"]          # one layer is 1/layers of a step over nseq sequences
+    return {"value": tokens / dt, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
+            "sample": f"layer 0 of the workload, {nseq} of {B} sequences, all KV heads; one pass of the C oracle "
+                      f"({dt:.2f} s), scaled to a {w['layers']}-layer step"}
+
+
+def run_reference(args):
+    """Reference arm: the CPU restatement of the reference's path on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "oracle"))
+    sys.path.insert(0, str(ROOT / "tests"))
+    import gkv_oracle
+    gkv_oracle.build()
+    w = WORKLOADS[args.workload]
+    nb_full = w["T"] // 64
+    # bounded sample: ONE sequence, ONE layer, at most 256 blocks per head (the per-sequence
+    # block count of the 16k configs); packed on the CPU by the oracle itself.
+    nb = min(nb_full, 256)
+    rng = np.random.default_rng(1000)
+    rows = []
+    for h in range(w["Hkv"]):
+        k = rng.standard_normal((nb, 64, w["D"]), dtype=np.float32)
+        v = rng.standard_normal((nb, 64, w["D"]), dtype=np.float32)
+        k[:, :, rng.permutation(w["D"])[:4]] *= 8.0
+        lv = rng.choice(np.array(LADDER), size=nb, p=np.asarray(w["probs"]))
+        lv[0] = lv[-1] = 16
+        rows.append(gkv_oracle.pack_row(k, v, lv, GROUP))
+    stride = max(r["data"].size for r in rows)
+    data = np.zeros((1, w["Hkv"], stride), np.uint8)
+    for h, r in enumerate(rows):
+        data[0, h, :r["data"].size] = r["data"]
+    st = lambda key: np.stack([r[key] for r in rows])[None]
+    q = rng.standard_normal((1, w["Hq"], w["D"]), dtype=np.float32) * np.float32(w["D"] ** -0.5)
+    call = lambda: gkv_oracle.mixed_attn_decode(q, data, st("offs"), st("klo"), st("kstep"), st("vlo"), st("vstep"),
+                                                st("level"), st("valid"), 64, GROUP)
+    for _ in range(max(args.warmup, 1)):
+        call()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        call()
+    dt = (time.perf_counter() - t0) / args.steps
+    # one sample = nb*64 tokens of one layer; a step attends over `layers` layers
+    value = (nb * 64) / (dt * w["layers"])
+    sample = (f"1 sequence x 1 layer x {nb} blocks ({nb * 64} tokens) per step, all {w['Hkv']} KV heads, "
+              f"scaled to a {w['layers']}-layer step")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * w["layers"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp64 accumulate (C oracle)",
+            "data": "synthetic",
+            "config": {"workload": w["name"], "layers": w["layers"], "q_heads": w["Hq"], "kv_heads": w["Hkv"],
+                       "head_dim": w["D"], "context_tokens": w["T"], "group": GROUP},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU kernel for this path and its Python cannot travel; this is the C "
+                    "restatement of its algorithm (oracle/gkv_oracle.c) on all host threads"}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,61 @@
+"""ctypes binding of ``libgeodesia_kv_b200.so`` (the C ABI in ``include/geodesia_kv_b200.h``).
+
+There is no CPU fallback anywhere in this package: if the library cannot be
+loaded the import of the first kernel entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libgeodesia_kv_b200.so"
+
+_lib = None
+
+_vp, _i, _i64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes); mirrors include/geodesia_kv_b200.h one to one
+SIGNATURES = {
+    "gkv_abi_version": (_i, []),
+    "gkv_error_string": (C.c_char_p, [_i]),
+    "gkv_last_cuda_error": (_i, []),
+    "gkv_decode_workspace_bytes": (_sz, [_i] * 5),
+    "gkv_mixed_attn_decode": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
+    "gkv_mixed_attn_decode_partial": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
+    "gkv_combine_partials": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "gkv_pack_blocks": (_i, [_vp, _vp, _i, _vp, _vp] + [_vp] * 4 + [_vp, _vp] + [_i] * 7 + [_i64, _i, _vp]),
+    "gkv_demote_blocks": (_i, [_vp] * 6 + [_vp] * 4 + [_i] * 5 + [_i64, _i64, _i, _vp]),
+    "gkv_unpack_blocks": (_i, [_vp] * 7 + [_vp, _vp] + [_i] * 5 + [_i64, _i, _vp]),
+    "gkv_allocate": (_i, [_vp] * 4 + [C.POINTER(_f), _vp, _f, _vp, _vp, _i, _i, _vp]),
+    "gkv_block_distortion": (_i, [_vp] * 4 + [_i] * 5 + [_f, _i64, _i, _vp]),
+}
+
+
+class GkvError(RuntimeError):
+    pass
+
+
+def load():
+    """Load (building first if the sources are newer) and return the ctypes library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        from . import build as _build
+        _build.build()
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError here = header and library disagree
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        lib = load()
+        msg = lib.gkv_error_string(rc).decode()
+        if rc == -5:
+            msg += f" [cudaError {lib.gkv_last_cuda_error()}]"
+        raise GkvError(f"{what}: {msg}")

@@ -1,0 +1,179 @@
+// Decode attention over the packed cache: planning, the LSE combine and the C ABI.
+#include "decode_generic.cuh"
+
+namespace gkv {
+
+int g_last_cuda_error = 0;
+
+// ---- LSE merge of split records -----------------------------------------------------------
+// Records are D+2 floats [m, l, o[D]].  Record s of output row r lives at
+//   rec + r_base(r) + s * stride_s.
+// Follows geodesia_kv_cuda/mixed_attn.cu:171-200 (splits with m = -inf are skipped, the
+// denominator clamps at 1e-20); `normalise == 0` writes the merged record instead of o/l.
+struct CombineParams {
+    const float* rec;
+    float* out;
+    int parts, D;
+    int rep, nsplit;     // internal layout (rows, nsplit, rep, D+2) when rep > 0
+    int64_t stride_s;    // external layout (parts, rows, D+2) when rep == 0
+    int normalise;
+};
+
+__global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
+    const int orow = blockIdx.x, D = p.D;
+    const float* base;
+    int64_t stride;
+    if (p.rep > 0) {
+        const int row = orow / p.rep, r = orow % p.rep;
+        base = p.rec + ((size_t)row * p.nsplit * p.rep + r) * (D + 2);
+        stride = (int64_t)p.rep * (D + 2);
+    } else {
+        base = p.rec + (size_t)orow * (D + 2);
+        stride = p.stride_s;
+    }
+    float m = -INFINITY;
+    for (int s = 0; s < p.parts; ++s) m = fmaxf(m, base[s * stride]);
+    float l = 0.f;
+    for (int s = 0; s < p.parts; ++s) {
+        const float ms = base[s * stride];
+        if (ms > -INFINITY) l += base[s * stride + 1] * expf(ms - m);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < p.parts; ++s) {
+            const float ms = base[s * stride];
+            if (ms > -INFINITY) a += base[s * stride + 2 + d] * expf(ms - m);
+        }
+        if (p.normalise) p.out[(size_t)orow * D + d] = a / fmaxf(l, 1e-20f);
+        else p.out[(size_t)orow * (D + 2) + 2 + d] = a;
+    }
+    if (!p.normalise && threadIdx.x == 0) {
+        p.out[(size_t)orow * (D + 2) + 0] = m;
+        p.out[(size_t)orow * (D + 2) + 1] = l;
+    }
+}
+
+// ---- split plan -------------------------------------------------------------------------------
+struct Plan {
+    int nsplit, bps;
+};
+
+static Plan make_plan(int rows, int nb) {
+    // Enough slices for ~4 CTAs per SM (the generic kernel runs 2-3 CTAs per SM).
+    int nsplit = (kNumSM * 4 + rows - 1) / rows;
+    if (nsplit > nb) nsplit = nb;
+    if (nsplit < 1) nsplit = 1;
+    const int bps = nb > 0 ? (nb + nsplit - 1) / nsplit : 1;
+    nsplit = nb > 0 ? (nb + bps - 1) / bps : 1;
+    return {nsplit, bps};
+}
+
+static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
+    const int rows = B * Hkv;
+    const Plan pl = make_plan(rows, nb);
+    return ((size_t)B * Hq * pl.nsplit * (D + 2) * sizeof(float) + 255) & ~(size_t)255;
+}
+
+static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
+                       const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
+                       const int32_t* valid, float* out, int normalise, void* workspace,
+                       size_t ws_bytes, int B, int Hq, int Hkv, int D, int nb, int block, int group,
+                       int64_t stride_bh, int meta_rows, void* stream_) {
+    if (block != kP) return GKV_E_BLOCK;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || nb < 0 || group <= 0) return GKV_E_SHAPE;
+    if (D <= 0 || D > kMaxD || D % 8 != 0) return GKV_E_SHAPE;
+    const int rep = Hq / Hkv, rows = B * Hkv;
+    if (rep > 16) return GKV_E_SHAPE;
+    if (meta_rows != 1 && meta_rows != rows) return GKV_E_SHAPE;
+    if (!q || !out) return GKV_E_NULL;
+    if (nb > 0 && (!data || !offs || !klo || !kstep || !vlo || !vstep || !level || !valid)) return GKV_E_NULL;
+    const size_t need = workspace_bytes(B, Hq, Hkv, D, nb);
+    if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return GKV_E_WORKSPACE;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    const Plan pl = make_plan(rows, nb);
+    DecodeParams p;
+    p.q = q; p.data = data; p.offs = offs;
+    p.klo = static_cast<const __half*>(klo); p.kstep = static_cast<const __half*>(kstep);
+    p.vlo = static_cast<const __half*>(vlo); p.vstep = static_cast<const __half*>(vstep);
+    p.level = level; p.valid = valid;
+    p.part = static_cast<float*>(workspace);
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.nb = nb; p.group = group;
+    p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.rep = rep;
+    p.nsplit = pl.nsplit; p.bps = pl.bps; p.per_row_meta = meta_rows != 1; p.stride_bh = stride_bh;
+
+    const size_t smem = decode_generic_smem(rep, D);
+    static bool attr_set = false;
+    if (!attr_set) {
+        GKV_CUDA_TRY(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)decode_generic_smem(16, kMaxD)));
+        attr_set = true;
+    }
+    decode_generic_kernel<<<dim3(pl.nsplit, rows), kGenThreads, smem, stream>>>(p);
+    GKV_LAUNCH_CHECK();
+
+    CombineParams c;
+    c.rec = p.part; c.out = out; c.parts = pl.nsplit; c.D = D; c.rep = rep; c.nsplit = pl.nsplit;
+    c.stride_s = 0; c.normalise = normalise;
+    combine_kernel<<<B * Hq, 128, 0, stream>>>(c);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+}  // namespace gkv
+
+extern "C" {
+
+int gkv_abi_version(void) { return 1; }
+
+int gkv_last_cuda_error(void) { return gkv::g_last_cuda_error; }
+
+const char* gkv_error_string(int code) {
+    switch (code) {
+        case GKV_OK: return "ok";
+        case GKV_E_BLOCK: return "only 64-token blocks are supported";
+        case GKV_E_SHAPE: return "unsupported or inconsistent shape";
+        case GKV_E_NULL: return "a required pointer is null";
+        case GKV_E_WORKSPACE: return "workspace missing, misaligned or too small";
+        case GKV_E_CUDA: return "a CUDA call failed (see gkv_last_cuda_error)";
+        case GKV_E_ARG: return "an argument is out of range";
+        default: return "unknown error code";
+    }
+}
+
+size_t gkv_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || nb < 0) return 0;
+    return gkv::workspace_bytes(B, Hq, Hkv, D, nb);
+}
+
+int gkv_mixed_attn_decode(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
+                          const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
+                          const int32_t* valid, float* out, void* workspace, size_t workspace_bytes,
+                          int B, int Hq, int Hkv, int D, int nb, int block, int group,
+                          int64_t stride_bh, int meta_rows, void* stream) {
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, workspace,
+                            workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream);
+}
+
+int gkv_mixed_attn_decode_partial(const float* q, const uint8_t* data, const int64_t* offs,
+                                  const void* klo, const void* kstep, const void* vlo, const void* vstep,
+                                  const int32_t* level, const int32_t* valid, float* partial,
+                                  void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D,
+                                  int nb, int block, int group, int64_t stride_bh, int meta_rows,
+                                  void* stream) {
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, partial, 0, workspace,
+                            workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream);
+}
+
+int gkv_combine_partials(const float* partials, float* out, int parts, int rows, int D, void* stream) {
+    if (!partials || !out) return GKV_E_NULL;
+    if (parts <= 0 || rows <= 0 || D <= 0) return GKV_E_SHAPE;
+    gkv::CombineParams c;
+    c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
+    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1;
+    gkv::combine_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,314 @@
+// Pack, demote and unpack kernels for the bit-ladder block format.
+//
+// One CTA owns one block of one cache row.  The block's K and V are first brought into
+// shared memory as fp32 tiles (from dense inputs when packing, from the packed bytes at the
+// current rung when demoting — so no dense copy of the cache ever exists in global memory),
+// then re-expressed at the target rung with exactly the arithmetic of the reference's
+// quantize_codes (tests/test_cuda_kernel.py:18-33): fp32 min/max per group, step =
+// max(hi-lo, 1e-8)/(2^b-1) with IEEE division, lo and step rounded to fp16 BEFORE the codes
+// are taken, code = clamp(rint((x-lo16)/step16), 0, 2^b-1), codes packed little-endian in the
+// byte (geodesia_kv/packed.py:23-40).  This file is compiled without fast-math.
+#include "gkv_common.cuh"
+
+namespace gkv {
+
+constexpr int kPackThreads = 256;
+
+struct TileJob {
+    uint8_t* dst;          // block start in the destination row
+    __half* klo; __half* kstep; __half* vlo; __half* vstep;   // this block's scale planes
+    int level, D, group, G, gv;
+};
+
+// Tiles: sk, sv hold [64][D] fp32.  scode is a [64][D] byte scratch.
+__device__ void quantize_tile_and_store(const TileJob& j, const float* __restrict__ sk,
+                                        const float* __restrict__ sv, uint8_t* __restrict__ scode) {
+    const int tid = threadIdx.x, D = j.D, lv = j.level;
+    const int hb = half_bytes(lv, D);
+    const bool scales_needed = (lv == 8 || lv == 4 || lv == 2);
+    if (!scales_needed) {
+        // the reference keeps zero scale planes for rungs 16 and 1 (pack_layout.py:25-28)
+        for (int i = tid; i < j.G * D; i += kPackThreads) { j.klo[i] = __ushort_as_half(0); j.kstep[i] = __ushort_as_half(0); }
+        for (int i = tid; i < kP * j.gv; i += kPackThreads) { j.vlo[i] = __ushort_as_half(0); j.vstep[i] = __ushort_as_half(0); }
+    }
+    if (lv == 16) {
+        __nv_bfloat16* ko = reinterpret_cast<__nv_bfloat16*>(j.dst);
+        __nv_bfloat16* vo = reinterpret_cast<__nv_bfloat16*>(j.dst + hb);
+        for (int i = tid; i < kP * D; i += kPackThreads) {
+            ko[i] = __float2bfloat16_rn(sk[i]);
+            vo[i] = __float2bfloat16_rn(sv[i]);
+        }
+        return;
+    }
+    if (lv == 1) {
+        // mean over the 64 tokens: fp32, tokens added in order, one division
+        __half* ko = reinterpret_cast<__half*>(j.dst);
+        __half* vo = reinterpret_cast<__half*>(j.dst + hb);
+        for (int d = tid; d < 2 * D; d += kPackThreads) {
+            const float* src = d < D ? sk + d : sv + (d - D);
+            float s = 0.f;
+            for (int t = 0; t < kP; ++t) s = __fadd_rn(s, src[t * D]);
+            const __half h = __float2half_rn(__fdiv_rn(s, (float)kP));
+            if (d < D) ko[d] = h; else vo[d - D] = h;
+        }
+        return;
+    }
+    const float qmax = (float)((1 << lv) - 1);
+    const int per = 8 / lv;
+    for (int which = 0; which < 2; ++which) {
+        const float* src = which ? sv : sk;
+        if (which == 0) {
+            // K: per channel over groups of g consecutive tokens; scales (G, D)
+            const int g = min(j.group, kP);
+            for (int u = tid; u < j.G * D; u += kPackThreads) {
+                const int tg = u / D, d = u - tg * D;
+                float lo = INFINITY, hi = -INFINITY;
+                for (int i = 0; i < g; ++i) {
+                    const float x = src[(tg * g + i) * D + d];
+                    lo = fminf(lo, x); hi = fmaxf(hi, x);
+                }
+                const float step = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), qmax);
+                const __half l16 = __float2half_rn(lo), s16 = __float2half_rn(step);
+                j.klo[u] = l16; j.kstep[u] = s16;
+                const float lf = __half2float(l16), sf = __half2float(s16);
+                for (int i = 0; i < g; ++i) {
+                    const int e = (tg * g + i) * D + d;
+                    float c = rintf(__fdiv_rn(__fsub_rn(src[e], lf), sf));
+                    c = (c != c) ? 0.f : fminf(fmaxf(c, 0.f), qmax);
+                    scode[e] = (uint8_t)c;
+                }
+            }
+        } else {
+            // V: per token over groups of g consecutive channels; scales (P, gv)
+            const int g = min(j.group, D);
+            for (int u = tid; u < kP * j.gv; u += kPackThreads) {
+                const int t = u / j.gv, cg = u - t * j.gv;
+                float lo = INFINITY, hi = -INFINITY;
+                for (int i = 0; i < g; ++i) {
+                    const float x = src[t * D + cg * g + i];
+                    lo = fminf(lo, x); hi = fmaxf(hi, x);
+                }
+                const float step = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), qmax);
+                const __half l16 = __float2half_rn(lo), s16 = __float2half_rn(step);
+                j.vlo[u] = l16; j.vstep[u] = s16;
+                const float lf = __half2float(l16), sf = __half2float(s16);
+                for (int i = 0; i < g; ++i) {
+                    const int e = t * D + cg * g + i;
+                    float c = rintf(__fdiv_rn(__fsub_rn(src[e], lf), sf));
+                    c = (c != c) ? 0.f : fminf(fmaxf(c, 0.f), qmax);
+                    scode[e] = (uint8_t)c;
+                }
+            }
+        }
+        __syncthreads();
+        uint8_t* out = j.dst + which * hb;
+        for (int o = tid; o < hb; o += kPackThreads) {
+            uint32_t byte = 0;
+            for (int i = 0; i < per; ++i) byte |= (uint32_t)scode[o * per + i] << (i * lv);
+            out[o] = (uint8_t)byte;
+        }
+        __syncthreads();
+    }
+}
+
+// Exact dequantisation of one block into the fp32 tiles (mixed_attn.cu:93-159).
+__device__ void dequant_block_to_tiles(const uint8_t* __restrict__ blk, int lv, int D, int group, int gv,
+                                       const __half* klo, const __half* kstep, const __half* vlo,
+                                       const __half* vstep, float* sk, float* sv) {
+    const uint8_t* vb = blk + half_bytes(lv, D);
+    for (int e = threadIdx.x; e < kP * D; e += blockDim.x) {
+        const int t = e / D, d = e - t * D;
+        float kx, vx;
+        if (lv == 1) {
+            kx = half_bits_to_float(reinterpret_cast<const uint16_t*>(blk)[d]);
+            vx = half_bits_to_float(reinterpret_cast<const uint16_t*>(vb)[d]);
+        } else if (lv == 16) {
+            kx = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(blk)[e]);
+            vx = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(vb)[e]);
+        } else {
+            const int ks = (t / group) * D + d, vs = t * gv + d / group;
+            kx = __fmaf_rn((float)unpack_code(blk, e, lv), __half2float(kstep[ks]), __half2float(klo[ks]));
+            vx = __fmaf_rn((float)unpack_code(vb, e, lv), __half2float(vstep[vs]), __half2float(vlo[vs]));
+        }
+        sk[e] = kx;
+        sv[e] = vx;
+    }
+}
+
+struct PackParams {
+    const void* k; const void* v; int src_dtype;
+    uint8_t* data; const int64_t* offs;
+    __half* klo; __half* kstep; __half* vlo; __half* vstep;
+    const int32_t* level; const int32_t* valid;
+    int nb, b_lo, D, group, G, gv, per_row_meta;
+    int64_t stride_bh;
+};
+
+__device__ __forceinline__ float load_src(const void* p, int dtype, size_t i) {
+    if (dtype == 0) return static_cast<const float*>(p)[i];
+    if (dtype == 1) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+__global__ void __launch_bounds__(kPackThreads) pack_blocks_kernel(PackParams p) {
+    extern __shared__ float smem[];
+    const int D = p.D;
+    float* sk = smem;
+    float* sv = sk + kP * D;
+    uint8_t* scode = reinterpret_cast<uint8_t*>(sv + kP * D);
+    const int blk = p.b_lo + blockIdx.x, row = blockIdx.y;
+    const int mrow = p.per_row_meta ? row : 0;
+    const int lv = p.level[(size_t)mrow * p.nb + blk];
+    if (!level_ok(lv)) return;
+    int nvalid = p.valid ? p.valid[(size_t)mrow * p.nb + blk] : kP;
+    nvalid = max(1, min(nvalid, kP));
+    const size_t src0 = ((size_t)row * p.nb + blk) * kP * D;
+    for (int e = threadIdx.x; e < kP * D; e += kPackThreads) {
+        const int t = e / D, d = e - t * D;
+        const int ts = min(t, nvalid - 1);               // pad by repeating the last real row
+        sk[e] = load_src(p.k, p.src_dtype, src0 + (size_t)ts * D + d);
+        sv[e] = load_src(p.v, p.src_dtype, src0 + (size_t)ts * D + d);
+    }
+    __syncthreads();
+    TileJob j;
+    j.dst = p.data + (size_t)row * p.stride_bh + p.offs[(size_t)mrow * p.nb + blk];
+    const size_t sb = (size_t)row * p.nb + blk;
+    j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
+    j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
+    j.level = lv; j.D = D; j.group = p.group; j.G = p.G; j.gv = p.gv;
+    quantize_tile_and_store(j, sk, sv, scode);
+}
+
+struct DemoteParams {
+    const uint8_t* data_old; const int64_t* offs_old; const int32_t* level_old;
+    uint8_t* data_new; const int64_t* offs_new; const int32_t* level_new;
+    __half* klo; __half* kstep; __half* vlo; __half* vstep;
+    int nb, D, group, G, gv, per_row_meta;
+    int64_t stride_old, stride_new;
+};
+
+__global__ void __launch_bounds__(kPackThreads) demote_blocks_kernel(DemoteParams p) {
+    extern __shared__ float smem[];
+    const int D = p.D;
+    float* sk = smem;
+    float* sv = sk + kP * D;
+    uint8_t* scode = reinterpret_cast<uint8_t*>(sv + kP * D);
+    const int blk = blockIdx.x, row = blockIdx.y;
+    const int mrow = p.per_row_meta ? row : 0;
+    const size_t mi = (size_t)mrow * p.nb + blk;
+    const int lo = p.level_old[mi], ln = p.level_new[mi];
+    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo) return;   // never promote
+    const size_t sb = (size_t)row * p.nb + blk;
+    TileJob j;
+    j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
+    j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
+    dequant_block_to_tiles(p.data_old + (size_t)row * p.stride_old + p.offs_old[mi], lo, D, p.group, p.gv,
+                           j.klo, j.kstep, j.vlo, j.vstep, sk, sv);
+    __syncthreads();
+    j.dst = p.data_new + (size_t)row * p.stride_new + p.offs_new[mi];
+    j.level = ln; j.D = D; j.group = p.group; j.G = p.G; j.gv = p.gv;
+    quantize_tile_and_store(j, sk, sv, scode);
+}
+
+struct UnpackParams {
+    const uint8_t* data; const int64_t* offs;
+    const __half* klo; const __half* kstep; const __half* vlo; const __half* vstep;
+    const int32_t* level; float* k_out; float* v_out;
+    int nb, D, group, G, gv, per_row_meta;
+    int64_t stride_bh;
+};
+
+__global__ void __launch_bounds__(kPackThreads) unpack_blocks_kernel(UnpackParams p) {
+    const int blk = blockIdx.x, row = blockIdx.y, D = p.D;
+    const int mrow = p.per_row_meta ? row : 0;
+    const size_t mi = (size_t)mrow * p.nb + blk;
+    const int lv = p.level[mi];
+    if (!level_ok(lv)) return;
+    const size_t sb = (size_t)row * p.nb + blk;
+    dequant_block_to_tiles(p.data + (size_t)row * p.stride_bh + p.offs[mi], lv, D, p.group, p.gv,
+                           p.klo + sb * p.G * D, p.kstep + sb * p.G * D, p.vlo + sb * kP * p.gv,
+                           p.vstep + sb * kP * p.gv, p.k_out + sb * kP * D, p.v_out + sb * kP * D);
+}
+
+static size_t tile_smem(int D) { return (size_t)kP * D * (2 * sizeof(float) + 1); }
+
+static int set_smem(const void* fn, size_t bytes) {
+    GKV_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return GKV_OK;
+}
+
+}  // namespace gkv
+
+extern "C" {
+
+int gkv_pack_blocks(const void* k, const void* v, int src_dtype, uint8_t* data, const int64_t* offs,
+                    void* klo, void* kstep, void* vlo, void* vstep, const int32_t* level,
+                    const int32_t* valid, int rows, int nb, int b_lo, int b_hi, int D, int block,
+                    int group, int64_t stride_bh, int meta_rows, void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (rows <= 0 || nb <= 0 || D <= 0 || D > kMaxD || D % 8 || group <= 0) return GKV_E_SHAPE;
+    if (kP % min(group, kP) || D % min(group, D)) return GKV_E_SHAPE;
+    if (meta_rows != 1 && meta_rows != rows) return GKV_E_SHAPE;
+    if (b_lo < 0 || b_hi > nb || b_lo > b_hi || src_dtype < 0 || src_dtype > 2) return GKV_E_ARG;
+    if (!k || !v || !data || !offs || !klo || !kstep || !vlo || !vstep || !level) return GKV_E_NULL;
+    if (b_lo == b_hi) return GKV_OK;
+    PackParams p;
+    p.k = k; p.v = v; p.src_dtype = src_dtype; p.data = data; p.offs = offs;
+    p.klo = (__half*)klo; p.kstep = (__half*)kstep; p.vlo = (__half*)vlo; p.vstep = (__half*)vstep;
+    p.level = level; p.valid = valid; p.nb = nb; p.b_lo = b_lo; p.D = D; p.group = group;
+    p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.per_row_meta = meta_rows != 1;
+    p.stride_bh = stride_bh;
+    int rc = set_smem((const void*)pack_blocks_kernel, tile_smem(kMaxD));
+    if (rc) return rc;
+    pack_blocks_kernel<<<dim3(b_hi - b_lo, rows), kPackThreads, tile_smem(D), (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+int gkv_demote_blocks(const uint8_t* data_old, const int64_t* offs_old, const int32_t* level_old,
+                      uint8_t* data_new, const int64_t* offs_new, const int32_t* level_new, void* klo,
+                      void* kstep, void* vlo, void* vstep, int rows, int nb, int D, int block, int group,
+                      int64_t stride_old, int64_t stride_new, int meta_rows, void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (rows <= 0 || nb <= 0 || D <= 0 || D > kMaxD || D % 8 || group <= 0) return GKV_E_SHAPE;
+    if (kP % min(group, kP) || D % min(group, D)) return GKV_E_SHAPE;
+    if (meta_rows != 1 && meta_rows != rows) return GKV_E_SHAPE;
+    if (!data_old || !offs_old || !level_old || !data_new || !offs_new || !level_new || !klo || !kstep ||
+        !vlo || !vstep)
+        return GKV_E_NULL;
+    DemoteParams p;
+    p.data_old = data_old; p.offs_old = offs_old; p.level_old = level_old;
+    p.data_new = data_new; p.offs_new = offs_new; p.level_new = level_new;
+    p.klo = (__half*)klo; p.kstep = (__half*)kstep; p.vlo = (__half*)vlo; p.vstep = (__half*)vstep;
+    p.nb = nb; p.D = D; p.group = group; p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group;
+    p.per_row_meta = meta_rows != 1; p.stride_old = stride_old; p.stride_new = stride_new;
+    int rc = set_smem((const void*)demote_blocks_kernel, tile_smem(kMaxD));
+    if (rc) return rc;
+    demote_blocks_kernel<<<dim3(nb, rows), kPackThreads, tile_smem(D), (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+int gkv_unpack_blocks(const uint8_t* data, const int64_t* offs, const void* klo, const void* kstep,
+                      const void* vlo, const void* vstep, const int32_t* level, float* k_out, float* v_out,
+                      int rows, int nb, int D, int block, int group, int64_t stride_bh, int meta_rows,
+                      void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (rows <= 0 || nb <= 0 || D <= 0 || D > kMaxD || group <= 0) return GKV_E_SHAPE;
+    if (meta_rows != 1 && meta_rows != rows) return GKV_E_SHAPE;
+    if (!data || !offs || !klo || !kstep || !vlo || !vstep || !level || !k_out || !v_out) return GKV_E_NULL;
+    UnpackParams p;
+    p.data = data; p.offs = offs;
+    p.klo = (const __half*)klo; p.kstep = (const __half*)kstep; p.vlo = (const __half*)vlo; p.vstep = (const __half*)vstep;
+    p.level = level; p.k_out = k_out; p.v_out = v_out; p.nb = nb; p.D = D; p.group = group;
+    p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.per_row_meta = meta_rows != 1;
+    p.stride_bh = stride_bh;
+    unpack_blocks_kernel<<<dim3(nb, rows), kPackThreads, 0, (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+}  // extern "C"
