@@ -1,5 +1,9 @@
 // Decode attention over the packed cache: planning, the LSE combine and the C ABI.
+#include <stdlib.h>
+#include <string.h>
+
 #include "decode_generic.cuh"
+#include "decode_mma.cuh"
 
 namespace gkv {
 
@@ -17,6 +21,7 @@ struct CombineParams {
     int rep, nsplit;     // internal layout (rows, nsplit, rep, D+2) when rep > 0
     int64_t stride_s;    // external layout (parts, rows, D+2) when rep == 0
     int normalise;
+    const int* status;   // when non-null and non-zero the producing kernel gave up: poison the output
 };
 
 __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
@@ -31,6 +36,7 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
         base = p.rec + (size_t)orow * (D + 2);
         stride = p.stride_s;
     }
+    const float poison = (p.status && *p.status) ? __int_as_float(0x7fc00000) : 0.f;
     float m = -INFINITY;
     for (int s = 0; s < p.parts; ++s) m = fmaxf(m, base[s * stride]);
     float l = 0.f;
@@ -44,6 +50,7 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
             const float ms = base[s * stride];
             if (ms > -INFINITY) a += base[s * stride + 2 + d] * expf(ms - m);
         }
+        a += poison;
         if (p.normalise) p.out[(size_t)orow * D + d] = a / fmaxf(l, 1e-20f);
         else p.out[(size_t)orow * (D + 2) + 2 + d] = a;
     }
@@ -55,23 +62,72 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
 
 // ---- split plan -------------------------------------------------------------------------------
 struct Plan {
-    int nsplit, bps;
+    int nsplit, bps;      // records per cache row, blocks per record
+    bool mma;             // tensor-core kernel (persistent, work items of `bps` blocks)
+    int grid;
 };
 
-static Plan make_plan(int rows, int nb) {
-    // Enough slices for ~4 CTAs per SM (the generic kernel runs 2-3 CTAs per SM).
+constexpr size_t kHeaderBytes = 256;   // work counter + status word in front of the records
+
+static bool mma_shape_ok(int D, int group, int rep) {
+    return (D == 64 || D == 128) && (group == 16 || group == 32 || group == 64) && D % group == 0 && rep <= 8;
+}
+
+static bool force_generic() {
+    const char* e = getenv("GKV_DECODE_KERNEL");
+    return e && strcmp(e, "generic") == 0;
+}
+
+static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mma) {
+    Plan pl;
+    pl.mma = allow_mma && mma_shape_ok(D, group, rep) && !force_generic();
+    if (pl.mma) {
+        pl.grid = 2 * kNumSM;
+        const long total = (long)rows * nb;
+        int chunk = (int)(total / ((long)pl.grid * 8));
+        chunk = (chunk / 4) * 4;
+        if (chunk < 4) chunk = 4;
+        if (chunk > 32) chunk = 32;
+        pl.bps = chunk;
+        pl.nsplit = nb > 0 ? (nb + chunk - 1) / chunk : 1;
+        const long items = (long)rows * pl.nsplit;
+        if (items < pl.grid) pl.grid = (int)(items > 0 ? items : 1);
+        return pl;
+    }
+    // generic kernel: enough slices for ~4 CTAs per SM
     int nsplit = (kNumSM * 4 + rows - 1) / rows;
     if (nsplit > nb) nsplit = nb;
     if (nsplit < 1) nsplit = 1;
-    const int bps = nb > 0 ? (nb + nsplit - 1) / nsplit : 1;
-    nsplit = nb > 0 ? (nb + bps - 1) / bps : 1;
-    return {nsplit, bps};
+    pl.bps = nb > 0 ? (nb + nsplit - 1) / nsplit : 1;
+    pl.nsplit = nb > 0 ? (nb + pl.bps - 1) / pl.bps : 1;
+    pl.grid = 0;
+    return pl;
 }
 
+static size_t records_bytes(int B, int Hq, const Plan& pl, int D) {
+    return (size_t)B * Hq * pl.nsplit * (D + 2) * sizeof(float);
+}
+
+// Upper bound over both kernels, so the caller's buffer fits whichever is dispatched.
 static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
-    const int rows = B * Hkv;
-    const Plan pl = make_plan(rows, nb);
-    return ((size_t)B * Hq * pl.nsplit * (D + 2) * sizeof(float) + 255) & ~(size_t)255;
+    const int rows = B * Hkv, rep = Hq / (Hkv > 0 ? Hkv : 1);
+    size_t need = records_bytes(B, Hq, make_plan(rows, nb, D, 32, rep, false), D);
+    const size_t alt = records_bytes(B, Hq, make_plan(rows, nb, 128, 32, 1, true), D);
+    if (alt > need) need = alt;
+    return (kHeaderBytes + need + 255) & ~(size_t)255;
+}
+
+template <int D, int G>
+static int launch_mma(const mma::Params& p, int grid, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        GKV_CUDA_TRY(cudaFuncSetAttribute(mma::decode_mma_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)mma::Cfg<D, G>::SMEM));
+        attr_set = true;
+    }
+    mma::decode_mma_kernel<D, G><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
 }
 
 static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
@@ -91,30 +147,54 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return GKV_E_WORKSPACE;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
-    const Plan pl = make_plan(rows, nb);
-    DecodeParams p;
-    p.q = q; p.data = data; p.offs = offs;
-    p.klo = static_cast<const __half*>(klo); p.kstep = static_cast<const __half*>(kstep);
-    p.vlo = static_cast<const __half*>(vlo); p.vstep = static_cast<const __half*>(vstep);
-    p.level = level; p.valid = valid;
-    p.part = static_cast<float*>(workspace);
-    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.nb = nb; p.group = group;
-    p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.rep = rep;
-    p.nsplit = pl.nsplit; p.bps = pl.bps; p.per_row_meta = meta_rows != 1; p.stride_bh = stride_bh;
+    const bool scales_aligned = ((reinterpret_cast<uintptr_t>(klo) | reinterpret_cast<uintptr_t>(kstep) |
+                                  reinterpret_cast<uintptr_t>(vlo) | reinterpret_cast<uintptr_t>(vstep)) & 15) == 0;
+    const Plan pl = make_plan(rows, nb, D, group, rep, scales_aligned && nb > 0);
+    int* header = static_cast<int*>(workspace);
+    float* records = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kHeaderBytes);
 
-    const size_t smem = decode_generic_smem(rep, D);
-    static bool attr_set = false;
-    if (!attr_set) {
-        GKV_CUDA_TRY(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)decode_generic_smem(16, kMaxD)));
-        attr_set = true;
+    if (pl.mma) {
+        GKV_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, stream));
+        mma::Params mp;
+        mp.q = q; mp.data = data; mp.offs = offs;
+        mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
+        mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);
+        mp.level = level; mp.valid = valid; mp.part = records; mp.counter = header; mp.status = header + 1;
+        mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps;
+        mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
+        mp.stride_bh = stride_bh;
+        int rc;
+        if (D == 128 && group == 32) rc = launch_mma<128, 32>(mp, pl.grid, stream);
+        else if (D == 128 && group == 16) rc = launch_mma<128, 16>(mp, pl.grid, stream);
+        else if (D == 128 && group == 64) rc = launch_mma<128, 64>(mp, pl.grid, stream);
+        else if (D == 64 && group == 32) rc = launch_mma<64, 32>(mp, pl.grid, stream);
+        else if (D == 64 && group == 16) rc = launch_mma<64, 16>(mp, pl.grid, stream);
+        else rc = launch_mma<64, 64>(mp, pl.grid, stream);
+        if (rc) return rc;
+    } else {
+        DecodeParams p;
+        p.q = q; p.data = data; p.offs = offs;
+        p.klo = static_cast<const __half*>(klo); p.kstep = static_cast<const __half*>(kstep);
+        p.vlo = static_cast<const __half*>(vlo); p.vstep = static_cast<const __half*>(vstep);
+        p.level = level; p.valid = valid;
+        p.part = records;
+        p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.nb = nb; p.group = group;
+        p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.rep = rep;
+        p.nsplit = pl.nsplit; p.bps = pl.bps; p.per_row_meta = meta_rows != 1; p.stride_bh = stride_bh;
+        const size_t smem = decode_generic_smem(rep, D);
+        static bool attr_set = false;
+        if (!attr_set) {
+            GKV_CUDA_TRY(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)decode_generic_smem(16, kMaxD)));
+            attr_set = true;
+        }
+        decode_generic_kernel<<<dim3(pl.nsplit, rows), kGenThreads, smem, stream>>>(p);
+        GKV_LAUNCH_CHECK();
     }
-    decode_generic_kernel<<<dim3(pl.nsplit, rows), kGenThreads, smem, stream>>>(p);
-    GKV_LAUNCH_CHECK();
 
     CombineParams c;
-    c.rec = p.part; c.out = out; c.parts = pl.nsplit; c.D = D; c.rep = rep; c.nsplit = pl.nsplit;
-    c.stride_s = 0; c.normalise = normalise;
+    c.rec = records; c.out = out; c.parts = pl.nsplit; c.D = D; c.rep = rep; c.nsplit = pl.nsplit;
+    c.stride_s = 0; c.normalise = normalise; c.status = pl.mma ? header + 1 : nullptr;
     combine_kernel<<<B * Hq, 128, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
@@ -170,7 +250,7 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     if (parts <= 0 || rows <= 0 || D <= 0) return GKV_E_SHAPE;
     gkv::CombineParams c;
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
-    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1;
+    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr;
     gkv::combine_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;

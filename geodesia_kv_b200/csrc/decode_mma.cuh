@@ -1,0 +1,899 @@
+// Tensor-core split decode kernel for the packed bit-ladder cache (sm_100a).
+//
+// Why tensor cores at all: at HBM speed the 16k-token mix delivers ~7.8e12 codes/s per GPU.
+// With a GQA group of 4-8 query heads every code needs 4-8 FMAs plus its unpack, which is
+// above the FP32 issue rate of the chip (the CUDA-core kernel in decode_generic.cuh measures
+// ~3 % of HBM bandwidth).  The group's QK^T and PV products are therefore issued as
+// m16n8k16 MMAs straight from registers; the bytes never make a second trip through shared
+// memory, which is why this is mma.sync and not tcgen05 (whose operands must be staged in
+// shared memory in canonical layout at 2 B per code).
+//
+// Structure (one CTA = 4 consumer warps + 1 producer warp, two CTAs per SM, persistent):
+//   * work items are (cache row, chunk of consecutive blocks), handed out by an atomic
+//     counter; every item ends in one (m, l, o) record per query head of the row;
+//   * the producer warp streams each block's bytes and its four scale planes into a byte
+//     ring in shared memory with cp.async.bulk + mbarrier (non-multicast), several blocks
+//     ahead of the consumers;
+//   * consumer warp w takes the blocks whose position in the stream is w mod 4 and runs a
+//     private online softmax over them; the four states are merged at the end of the item.
+//
+// Arithmetic.  Integer codes are fed to the MMA as fp16 values from the LINEAR range of the
+// format: bit patterns 0..2047 (subnormals and the first binade) are worth pattern * 2^-24, so a
+// code masked out of the packed word already is the number "code * 2^k * 2^-24" and unpacking
+// needs no int->float conversion.  The tensor core aligns the products of a dot product by their
+// nominal exponents, so a code sitting in the low mantissa bits wastes that many bits of the
+// accumulation window (measured: 2-bit codes at bit 0 lose ~10 bits); codes are therefore
+// placed as high in the linear range as a single shift allows (bits 8-9 / 6-7 for 2-bit,
+// 7-10 / 3-6 for 4-bit, 0-7 for 8-bit) and the power of two is folded into the query planes.
+// De-quantisation is hoisted out of the contraction:
+//   q . (c*step + lo) = (q*step) . c + q . lo        (per token group, per channel)
+//   p . (c*step + lo) = (p*step) . c + p . lo        (per token, per channel group)
+// The small operands q*step and p*step are split into fp16 hi + lo halves that ride in the
+// otherwise unused MMA rows 8..15 (the GQA group is at most 8 heads), giving ~22 significant
+// bits; the lo terms are two tiny extra MMAs.  Accumulation is fp32 throughout.
+#pragma once
+
+#include "gkv_common.cuh"
+
+namespace gkv {
+namespace mma {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;
+constexpr int kNSlot = 16;                 // descriptor slots (blocks in flight per CTA)
+constexpr uint32_t kRingBytes = 72 * 1024; // byte ring per CTA
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // every wait gives up after ~1 s, flags the error, returns
+
+struct Desc {           // one block in the ring
+    uint32_t off;       // byte offset of the block in the ring
+    int32_t level;      // 0 = nothing to do (padding slot)
+    int32_t nvalid;
+    int32_t pad;
+};
+
+struct ItemDesc {       // one work item; published before any of its blocks so that the four
+    int32_t item;       // consumer warps can meet at the item start without waiting for data
+    int32_t row;
+    int32_t rounds;     // every warp consumes exactly one slot per round
+    int32_t exit;
+};
+
+struct Params {
+    const float* q;
+    const uint8_t* data;
+    const int64_t* offs;
+    const __half* klo;
+    const __half* kstep;
+    const __half* vlo;
+    const __half* vstep;
+    const int32_t* level;
+    const int32_t* valid;
+    float* part;        // (items, rep, D+2)
+    int* counter;       // work-item counter (zeroed before launch)
+    int* status;        // error word (zeroed before launch)
+    int B, Hq, Hkv, nb, rep;
+    int chunk;          // blocks per item
+    int items_per_row, items;
+    int per_row_meta;
+    int64_t stride_bh;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false if the phase did not complete within kWaitLimitNs of wall time.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t a = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 63u) == 63u) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// (x*y) as fp16 hi + lo, x given as fp16 hi/lo halves, y exact fp16: hi = rn(xh*y),
+// lo = rn(xl*y + (xh*y - hi)); the inner difference is exact in an fp16 FMA.
+__device__ __forceinline__ void mul_split(uint32_t xh, uint32_t xl, uint32_t y, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __hmul2(u32_as_h2(xh), u32_as_h2(y));
+    const __half2 e = __hfma2(u32_as_h2(xh), u32_as_h2(y), __hneg2(h));
+    hi = h2_as_u32(h);
+    lo = h2_as_u32(__hfma2(u32_as_h2(xl), u32_as_h2(y), e));
+}
+
+// Two fp32 values -> packed fp16 hi pair and residual lo pair (element 0 in the low half).
+__device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    const float2 hf = __half22float2(h);
+    hi = h2_as_u32(h);
+    lo = h2_as_u32(__floats2half2_rn(x0 - hf.x, x1 - hf.y));
+}
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// ---- channel arrangement of the QK contraction -----------------------------------------------
+// Thread t of a quad owns DT = D/4 consecutive channels of a token row.  MMA k-step s, slot e
+// (e = 0,1 -> first B register, e = 2,3 -> second) maps to channel DT*t + arr_chan(bits, s, e);
+// the maps follow the cheapest shift-and-mask unpack of each code width (one 32-bit AND yields
+// the two codes that sit 16 bits apart).  arr_scale is the exact power of two folded into the
+// prepared query so that every slot of a rung carries the same weight:
+//   4-bit: even nibbles land on bits 3-6 (8c), odd nibbles on bits 7-10 (128c)  -> x16 / x1
+//   2-bit: even fields land on bits 8-9 (256c), odd fields on bits 6-7 (64c)    -> x1 / x4
+__host__ __device__ constexpr int arr_chan(int bits, int s, int e) {
+    return bits == 4   ? 8 * (s >> 1) + 2 * (s & 1) + (e >> 1) + 4 * (e & 1)
+           : bits == 2 ? 16 * (s >> 2) + 2 * (s & 3) + (e >> 1) + 8 * (e & 1)
+                       : 4 * s + e;   // 8-bit codes and raw bf16
+}
+__host__ __device__ constexpr float arr_scale(int bits, int e) {
+    return bits == 4 ? ((e >> 1) ? 1.f : 16.f) : bits == 2 ? ((e >> 1) ? 4.f : 1.f) : 1.f;
+}
+// 2^24 / (weight of one code in the linear range) for the K contraction of each rung
+__host__ __device__ constexpr float k_unscale(int bits) { return bits == 4 ? 131072.f : bits == 2 ? 65536.f : 16777216.f; }
+// V contraction: bit position the codes are brought to, and the weight scale that goes with it
+__host__ __device__ constexpr int v_pos(int bits) { return bits == 4 ? 4 : bits == 2 ? 8 : 0; }
+
+template <int D, int G>
+struct Cfg {
+    static constexpr int DT = D / 4;          // channels per thread in QK
+    static constexpr int KS = D / 16;         // QK k-steps
+    static constexpr int CH = KS / 2;         // 16-byte chunks of prepared q per thread (2 k-steps each)
+    static constexpr int TG = kP / G;         // token groups (K scales)
+    static constexpr int NTG = G / 8;         // token n-tiles per token group
+    static constexpr int GV = D / G;          // channel groups (V scales)
+    static constexpr int NT = G / 8;          // channel n-tiles per channel group
+    static constexpr int NTILE = D / 8;       // output n-tiles
+    static constexpr int KSCALE = TG * D * 2; // bytes of klo (or kstep) of one block
+    static constexpr int VSCALE = kP * GV * 2;
+    // prepared-q planes, in halves: [plane][chunk][lane][8]
+    static constexpr int QPLANE = CH * 32 * 8;
+    // planes: 0/1 arr8 hi/lo, 2/3 arr4 hi/lo, 4/5 arr2 hi/lo, 6/7 bf16 hi/lo
+    static constexpr int QPREP_BYTES = 8 * QPLANE * 2;
+    static constexpr int STAGE_FLOATS = kConsumerWarps * 8 * (D + 2);
+    static constexpr size_t SMEM = kRingBytes + QPREP_BYTES + 8 * D * 4 + 64 + STAGE_FLOATS * 4 +
+                                   kNSlot * sizeof(Desc) + 2 * kNSlot * 8 + 2 * sizeof(ItemDesc) + 5 * 8 + 64;
+    static_assert(D % 32 == 0 && (G == 16 || G == 32 || G == 64) && D % G == 0, "unsupported shape");
+};
+
+template <int D, int G>
+struct Smem {
+    using C = Cfg<D, G>;
+    uint8_t* ring;
+    __half* qprep;
+    float* sq;        // [8][D] raw query (fp32, softmax scale included)
+    float* sf;        // [8] per-head factor 2^-eq * log2(e); [8..16) unused
+    float* stage;
+    Desc* desc;
+    uint64_t* full;
+    uint64_t* empty;
+    ItemDesc* item;        // [2]
+    uint64_t* item_full;   // [2]
+    uint64_t* item_empty;  // [2]
+    uint64_t* sync_bar;    // consumer rendezvous (4 arrivals: one per warp)
+    __device__ explicit Smem(uint8_t* base) {
+        ring = base;
+        qprep = reinterpret_cast<__half*>(base + kRingBytes);
+        sq = reinterpret_cast<float*>(base + kRingBytes + C::QPREP_BYTES);
+        sf = sq + 8 * D;
+        stage = sf + 16;
+        desc = reinterpret_cast<Desc*>(stage + C::STAGE_FLOATS);
+        full = reinterpret_cast<uint64_t*>(desc + kNSlot);
+        empty = full + kNSlot;
+        item_full = empty + kNSlot;
+        item_empty = item_full + 2;
+        sync_bar = item_empty + 2;
+        item = reinterpret_cast<ItemDesc*>(sync_bar + 1);
+    }
+};
+
+// ================================ producer ====================================================
+template <int D, int G>
+__device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
+    using C = Cfg<D, G>;
+    const int lane = threadIdx.x & 31;
+    uint32_t head = 0, used = 0;
+    int seq_alloc = 0, seq_free = 0;
+    __shared__ uint32_t slot_bytes[kNSlot];
+
+    auto release_oldest = [&]() -> bool {
+        const int s = seq_free % kNSlot;
+        if (!mbar_wait(&sm.empty[s], (uint32_t)(seq_free / kNSlot) & 1u)) return false;
+        used -= slot_bytes[s];
+        ++seq_free;
+        return true;
+    };
+
+    int item = 0;
+    if (lane == 0) item = atomicAdd(p.counter, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    bool ok = true;
+    for (int iseq = 0; ok; ++iseq) {
+        const bool done = item >= p.items;
+        int next_item = 0;
+        if (!done && lane == 0) next_item = atomicAdd(p.counter, 1);   // prefetch the next item id
+        const int row = done ? 0 : item / p.items_per_row;
+        const int b_lo = done ? 0 : (item % p.items_per_row) * p.chunk;
+        const int nblk = done ? 0 : min(p.chunk, p.nb - b_lo);
+        const int mrow = p.per_row_meta ? row : 0;
+        const int rounds = (nblk + kConsumerWarps - 1) / kConsumerWarps;
+        // the item descriptor goes out first, through its own double buffer
+        if (lane == 0) {
+            const int ib = iseq & 1;
+            if (iseq >= 2) ok = mbar_wait(&sm.item_empty[ib], (uint32_t)((iseq >> 1) - 1) & 1u);
+            if (ok) {
+                ItemDesc it;
+                it.item = item; it.row = row; it.rounds = rounds; it.exit = done ? 1 : 0;
+                sm.item[ib] = it;
+                mbar_arrive(&sm.item_full[ib]);
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok || done) break;
+        // metadata of up to 32 blocks at a time, one per lane
+        for (int base = 0; base < rounds * kConsumerWarps && ok; base += 32) {
+            int lv = 0, nv = 0;
+            int64_t off = 0;
+            const int k = base + lane;
+            if (k < nblk) {
+                const size_t mi = (size_t)mrow * p.nb + b_lo + k;
+                lv = p.level[mi];
+                nv = min(p.valid[mi], kP);
+                off = p.offs[mi];
+                if (!level_ok(lv) || nv <= 0) lv = 0;
+            }
+            const int cnt = min(32, rounds * kConsumerWarps - base);
+            for (int j = 0; j < cnt && ok; ++j) {
+                const int lvj = __shfl_sync(0xffffffffu, lv, j);
+                const int nvj = __shfl_sync(0xffffffffu, nv, j);
+                const int64_t offj = __shfl_sync(0xffffffffu, off, j);
+                const int kk = base + j;
+                const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
+                const uint32_t dbytes = lvj ? 2u * (uint32_t)half_bytes(lvj, D) : 0u;
+                const uint32_t sbytes = quant ? 2u * (C::KSCALE + C::VSCALE) : 0u;
+                const uint32_t need = (dbytes + sbytes + 127u) & ~127u;
+                const int slot = seq_alloc % kNSlot;
+                uint32_t dst = 0;
+                if (lane == 0) {
+                    while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
+                    const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
+                    while (ok && used + waste + need > kRingBytes) ok = release_oldest();
+                    dst = waste ? 0u : head;
+                    used += waste + need;
+                    head = dst + need;
+                    if (head >= kRingBytes) head = 0;
+                    slot_bytes[slot] = waste + need;
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (!ok) break;
+                dst = __shfl_sync(0xffffffffu, dst, 0);
+                if (lane == 0) {
+                    Desc d;
+                    d.off = dst; d.level = lvj; d.nvalid = nvj; d.pad = 0;
+                    sm.desc[slot] = d;
+                }
+                if (lvj) {
+                    const size_t sb = (size_t)row * p.nb + b_lo + kk;
+                    const uint8_t* src = p.data + (size_t)row * p.stride_bh + offj;
+                    uint8_t* d0 = sm.ring + dst;
+                    const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+                    if (aligned) {
+                        if (lane == 0) {
+                            mbar_arrive_tx(&sm.full[slot], dbytes + sbytes);
+                            bulk_g2s(d0, src, dbytes, &sm.full[slot]);
+                            if (quant) {
+                                bulk_g2s(d0 + dbytes, p.klo + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
+                                bulk_g2s(d0 + dbytes + C::KSCALE, p.kstep + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
+                                bulk_g2s(d0 + dbytes + 2 * C::KSCALE, p.vlo + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
+                                bulk_g2s(d0 + dbytes + 2 * C::KSCALE + C::VSCALE, p.vstep + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
+                            }
+                        }
+                    } else {
+                        // block start not 16-byte aligned: the whole warp copies it by hand
+                        for (uint32_t i = lane; i < dbytes; i += 32) d0[i] = src[i];
+                        if (quant) {
+                            const uint16_t* s0 = reinterpret_cast<const uint16_t*>(p.klo + sb * (C::KSCALE / 2));
+                            const uint16_t* s1 = reinterpret_cast<const uint16_t*>(p.kstep + sb * (C::KSCALE / 2));
+                            const uint16_t* s2 = reinterpret_cast<const uint16_t*>(p.vlo + sb * (C::VSCALE / 2));
+                            const uint16_t* s3 = reinterpret_cast<const uint16_t*>(p.vstep + sb * (C::VSCALE / 2));
+                            uint16_t* o = reinterpret_cast<uint16_t*>(d0 + dbytes);
+                            for (int i = lane; i < C::KSCALE / 2; i += 32) { o[i] = s0[i]; o[C::KSCALE / 2 + i] = s1[i]; }
+                            o += C::KSCALE;
+                            for (int i = lane; i < C::VSCALE / 2; i += 32) { o[i] = s2[i]; o[C::VSCALE / 2 + i] = s3[i]; }
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm.full[slot]);
+                    }
+                } else if (lane == 0) {
+                    mbar_arrive(&sm.full[slot]);
+                }
+                ++seq_alloc;
+            }
+        }
+        item = __shfl_sync(0xffffffffu, next_item, 0);
+    }
+    if (!ok && lane == 0) {
+        atomicExch(p.status, 1);
+        atomicExch(abort_flag, 1);
+    }
+}
+
+// ================================ consumers ===================================================
+template <int D, int G>
+struct WarpState {
+    using C = Cfg<D, G>;
+    float o[C::NTILE][4];   // rows r (c0,c1) and r+8 (c2,c3) of every output n-tile, scaled 2^-16
+    float ob[4];            // sum_j p_j * vlo[j][cg], scaled 2^8
+    float m;                // running max of head r (log2 domain), replicated over the quad
+    float l;              // this thread's share of the running sum
+};
+
+// Prepared-query fragment loader: plane pl, returns the 4 registers of chunk i (k-steps 2i, 2i+1).
+template <int D, int G>
+__device__ __forceinline__ uint4 load_qchunk(const Smem<D, G>& sm, int plane, int i, int lane) {
+    using C = Cfg<D, G>;
+    return *reinterpret_cast<const uint4*>(sm.qprep + (size_t)plane * C::QPLANE + ((size_t)i * 32 + lane) * 8);
+}
+
+// Rendezvous of the four consumer warps on an mbarrier (bounded, unlike bar.sync).
+__device__ __forceinline__ bool consumer_sync(uint64_t* bar, uint32_t& phase) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+    const bool ok = mbar_wait(bar, phase);
+    phase ^= 1u;
+    return ok;
+}
+
+// Build the prepared query planes for the current row (all 128 consumer threads).
+template <int D, int G>
+__device__ bool prepare_query(const Params& p, Smem<D, G>& sm, int row, uint32_t& phase) {
+    using C = Cfg<D, G>;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = row / p.Hkv, hk = row % p.Hkv;
+    const float* q = p.q + ((size_t)b * p.Hq + (size_t)hk * p.rep) * D;
+    for (int i = tid; i < 8 * D; i += kConsumers) {
+        const int h = i / D;
+        sm.sq[i] = h < p.rep ? q[i] : 0.f;
+    }
+    if (!consumer_sync(sm.sync_bar, phase)) return false;
+    // per-head power-of-two scale bringing max|q| into [8, 16): two heads per warp
+    for (int h = warp * 2; h < warp * 2 + 2; ++h) {
+        float mx = 0.f;
+        for (int d = lane; d < D; d += 32) mx = fmaxf(mx, fabsf(sm.sq[h * D + d]));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        int eq = 0;
+        if (mx > 0.f && mx < INFINITY) eq = 3 - ilogbf(mx);
+        eq = max(-100, min(100, eq));
+        if (lane == 0) {
+            sm.sf[h] = ldexpf(1.4426950408889634f, -eq);
+            sm.sf[8 + h] = ldexpf(1.0f, eq);
+        }
+    }
+    if (!consumer_sync(sm.sync_bar, phase)) return false;
+    // every thread fills entries (chunk i, lane l, half j) of each plane
+    for (int idx = tid; idx < C::CH * 32 * 8; idx += kConsumers) {
+        const int j = idx & 7, l = (idx >> 3) & 31, i = idx >> 8;
+        const int r = l >> 2, t = l & 3;
+        const int s = 2 * i + (j >> 2), e = j & 3;
+        const float sc = sm.sf[8 + r];
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const int bits = a == 0 ? 8 : a == 1 ? 4 : 2;
+            const float x = sm.sq[r * D + C::DT * t + arr_chan(bits, s, e)] * sc * arr_scale(bits, e);
+            const __half h = __float2half_rn(x);
+            sm.qprep[(2 * a) * C::QPLANE + idx] = h;
+            sm.qprep[(2 * a + 1) * C::QPLANE + idx] = __float2half_rn(x - __half2float(h));
+        }
+        const float x = sm.sq[r * D + C::DT * t + arr_chan(16, s, e)] * sc;
+        const __nv_bfloat16 hb = __float2bfloat16_rn(x);
+        reinterpret_cast<__nv_bfloat16*>(sm.qprep)[6 * C::QPLANE + idx] = hb;
+        reinterpret_cast<__nv_bfloat16*>(sm.qprep)[7 * C::QPLANE + idx] = __float2bfloat16_rn(x - __bfloat162float(hb));
+    }
+    return consumer_sync(sm.sync_bar, phase);
+}
+
+// ---- K side of a quantised block: scores in the log2 domain ---------------------------------
+template <int D, int G, int BITS>
+__device__ __forceinline__ void scores_quant(const Smem<D, G>& sm, const uint8_t* blk, float (&z)[16], int lane) {
+    using C = Cfg<D, G>;
+    const int r = lane >> 2, t = lane & 3;
+    constexpr int RB = D * BITS / 8;                     // bytes per token row
+    constexpr int TB = RB / 4;                           // bytes per thread per row
+    const uint8_t* klo = blk + 2 * (kP * RB);
+    const uint8_t* kst = klo + C::KSCALE;
+    constexpr int plane = BITS == 8 ? 0 : BITS == 4 ? 2 : 4;
+    const float f = sm.sf[r];
+
+    // q . klo for every token group: one n-tile whose column n is token group n
+    float bias[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+        const bool live = r < C::TG;
+        const uint4* lo4 = reinterpret_cast<const uint4*>(klo + ((live ? r : 0) * D + C::DT * t) * 2);
+#pragma unroll
+        for (int i = 0; i < C::CH; ++i) {
+            const uint4 qh = load_qchunk(sm, 0, i, lane), ql = load_qchunk(sm, 1, i, lane);
+            uint4 b = lo4[i];
+            if (!live) b = make_uint4(0, 0, 0, 0);
+            mma_f16(bias, qh.x, ql.x, qh.y, ql.y, b.x, b.y);
+            mma_f16(bias, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
+        }
+    }
+#pragma unroll
+    for (int tg = 0; tg < C::TG; ++tg) {
+        float acc[C::NTG][4];
+#pragma unroll
+        for (int n = 0; n < C::NTG; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < C::CH; ++i) {               // two k-steps at a time
+            const uint4 qh = load_qchunk(sm, plane, i, lane), ql = load_qchunk(sm, plane + 1, i, lane);
+            // step pairs of k-steps 2i and 2i+1 in this arrangement
+            uint32_t sp[4];
+            const uint32_t* nat = reinterpret_cast<const uint32_t*>(kst + (tg * D + C::DT * t) * 2);
+            if (BITS == 8) {
+                const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
+                sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
+            } else if (BITS == 4) {                       // s = 2x+y with x = i: words 4i+y, 4i+y+2
+                const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
+                sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
+                sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
+            } else {                                      // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
+                const int x = i >> 1, y0 = 2 * (i & 1);
+                const uint2 va = *reinterpret_cast<const uint2*>(nat + 8 * x + y0);
+                const uint2 vb = *reinterpret_cast<const uint2*>(nat + 8 * x + y0 + 4);
+                sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
+                sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
+            }
+            uint32_t a[8];
+            mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
+            mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
+            mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
+            mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
+#pragma unroll
+            for (int n = 0; n < C::NTG; ++n) {
+                const int tok = (tg * C::NTG + n) * 8 + r;
+                const uint8_t* row = blk + tok * RB + t * TB;
+                uint32_t b0, b1, b2, b3;                  // B registers of k-steps 2i (b0,b1) and 2i+1 (b2,b3)
+                if (BITS == 8) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(row + 8 * i);
+                    b0 = prmt(w.x, 0u, 0x4140); b1 = prmt(w.x, 0u, 0x4342);
+                    b2 = prmt(w.y, 0u, 0x4140); b3 = prmt(w.y, 0u, 0x4342);
+                } else if (BITS == 4) {
+                    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * i);
+                    const uint32_t u = w << 3, v = w >> 5;
+                    b0 = u & 0x00780078u; b1 = u & 0x07800780u;
+                    b2 = v & 0x00780078u; b3 = v & 0x07800780u;
+                } else {
+                    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * (i >> 1));
+                    if ((i & 1) == 0) {        // fields 0..3 (and 8..11) of the word
+                        const uint32_t u = w << 4;
+                        b0 = (w << 8) & 0x03000300u; b1 = u & 0x00C000C0u;
+                        b2 = u & 0x03000300u;        b3 = w & 0x00C000C0u;
+                    } else {                   // fields 4..7 (and 12..15)
+                        const uint32_t u = w >> 4;
+                        b0 = w & 0x03000300u; b1 = u & 0x00C000C0u;
+                        b2 = u & 0x03000300u; b3 = (w >> 8) & 0x00C000C0u;
+                    }
+                }
+                mma_f16(acc[n], a[0], a[1], a[2], a[3], b0, b1);
+                mma_f16(acc[n], a[4], a[5], a[6], a[7], b2, b3);
+            }
+        }
+        // bias of this token group for head r lives in lane 4r + tg/2, column tg & 1
+        const float bsel = (tg & 1) ? bias[1] + bias[3] : bias[0] + bias[2];
+        const float bg = __shfl_sync(0xffffffffu, bsel, (lane & ~3) | (tg >> 1));
+#pragma unroll
+        for (int n = 0; n < C::NTG; ++n) {
+            const int nt = tg * C::NTG + n;
+            z[2 * nt + 0] = fmaf(acc[n][0] + acc[n][2], k_unscale(BITS), bg) * f;
+            z[2 * nt + 1] = fmaf(acc[n][1] + acc[n][3], k_unscale(BITS), bg) * f;
+        }
+    }
+}
+
+template <int D, int G>
+__device__ __forceinline__ void scores_bf16(const Smem<D, G>& sm, const uint8_t* blk, float (&z)[16], int lane) {
+    using C = Cfg<D, G>;
+    const int r = lane >> 2, t = lane & 3;
+    const float f = sm.sf[r];
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < C::CH; ++i) {
+        const uint4 qh = load_qchunk(sm, 6, i, lane), ql = load_qchunk(sm, 7, i, lane);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const uint4 w = *reinterpret_cast<const uint4*>(blk + ((n * 8 + r) * D + C::DT * t) * 2 + 16 * i);
+            mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w.x, w.y);
+            mma_bf16(acc[n], qh.z, ql.z, qh.w, ql.w, w.z, w.w);
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        z[2 * n + 0] = (acc[n][0] + acc[n][2]) * f;
+        z[2 * n + 1] = (acc[n][1] + acc[n][3]) * f;
+    }
+}
+
+// ---- online-softmax update shared by all rungs --------------------------------------------------
+// z: scores of head r for tokens 8*nt + 2t + {0,1} (log2 domain).  Returns p in z.
+template <int D, int G>
+__device__ __forceinline__ void softmax_update(WarpState<D, G>& st, float (&z)[16], int nvalid, int lane) {
+    using C = Cfg<D, G>;
+    const int t = lane & 3;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
+        if (tok >= nvalid) z[i] = -INFINITY;
+        mx = fmaxf(mx, z[i]);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mnew = fmaxf(st.m, mx);            // finite: the caller guarantees nvalid >= 1
+    const float corr = ex2(st.m - mnew);           // 0 when st.m = -inf
+    st.m = mnew;
+    float ls = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        z[i] = ex2(z[i] - mnew);
+        ls += z[i];
+    }
+    st.l = st.l * corr + ls;
+    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+        for (int n = 0; n < C::NTILE; ++n) {
+            st.o[n][0] *= corr; st.o[n][1] *= corr; st.o[n][2] *= corr; st.o[n][3] *= corr;
+        }
+        st.ob[0] *= corr; st.ob[1] *= corr; st.ob[2] *= corr; st.ob[3] *= corr;
+    }
+}
+
+// ---- V side of a quantised block ------------------------------------------------------------------
+template <int D, int G, int BITS>
+__device__ __forceinline__ void values_quant(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk,
+                                             const float (&pz)[16], int nvalid, int lane) {
+    using C = Cfg<D, G>;
+    const int r = lane >> 2, t = lane & 3;
+    constexpr int RB = D * BITS / 8;
+    const uint8_t* vb = blk + kP * RB;
+    const uint8_t* vlo = blk + 2 * (kP * RB) + 2 * C::KSCALE;
+    const uint8_t* vst = vlo + C::VSCALE;
+    constexpr int NB = C::NT * BITS;                 // bits one thread reads per token per channel group
+    constexpr int POS = v_pos(BITS);                 // codes are brought to bits [POS, POS+BITS) of each half
+    constexpr uint32_t MASK = (((1u << BITS) - 1u) << POS) * 0x00010001u;
+    constexpr float PSCALE = (float)(256 >> POS);    // weights carry 2^(8-POS) so that every rung adds p*v*2^-16
+    const __half2 lo_scale = __float2half2_rn((float)(1 << POS));
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const int ta = 16 * ks + 2 * t, tb = ta + 8;  // token pairs (ta, ta+1) and (tb, tb+1)
+        uint32_t ph[2], pl[2];
+        split_f16x2(pz[4 * ks + 0] * PSCALE, pz[4 * ks + 1] * PSCALE, ph[0], pl[0]);
+        split_f16x2(pz[4 * ks + 2] * PSCALE, pz[4 * ks + 3] * PSCALE, ph[1], pl[1]);
+        const bool ragged = nvalid < 16 * ks + 16;   // warp-uniform: some token of this k-step is masked
+        // V scale rows of the four tokens: [token][GV] halves
+        const uint16_t* st_a = reinterpret_cast<const uint16_t*>(vst) + ta * C::GV;
+        const uint16_t* st_b = reinterpret_cast<const uint16_t*>(vst) + tb * C::GV;
+        const uint16_t* lo_a = reinterpret_cast<const uint16_t*>(vlo) + ta * C::GV;
+        const uint16_t* lo_b = reinterpret_cast<const uint16_t*>(vlo) + tb * C::GV;
+        // p . vlo: column n of this n-tile is channel group n
+        {
+            uint32_t b0 = 0, b1 = 0;
+            if (r < C::GV) {
+                b0 = (uint32_t)lo_a[r] | ((uint32_t)lo_a[C::GV + r] << 16);
+                b1 = (uint32_t)lo_b[r] | ((uint32_t)lo_b[C::GV + r] << 16);
+                if (ragged) {
+                    if (ta >= nvalid) b0 = 0; else if (ta + 1 >= nvalid) b0 &= 0xffffu;
+                    if (tb >= nvalid) b1 = 0; else if (tb + 1 >= nvalid) b1 &= 0xffffu;
+                }
+            }
+            if (POS) {                                 // keep the 2^8 scale of the p . vlo accumulator
+                b0 = h2_as_u32(__hmul2(u32_as_h2(b0), lo_scale));
+                b1 = h2_as_u32(__hmul2(u32_as_h2(b1), lo_scale));
+            }
+            mma_f16(st.ob, ph[0], pl[0], ph[1], pl[1], b0, b1);
+        }
+#pragma unroll
+        for (int cg = 0; cg < C::GV; ++cg) {
+            uint32_t sa = (uint32_t)st_a[cg] | ((uint32_t)st_a[C::GV + cg] << 16);
+            uint32_t sb = (uint32_t)st_b[cg] | ((uint32_t)st_b[C::GV + cg] << 16);
+            if (ragged) {
+                if (ta >= nvalid) sa = 0; else if (ta + 1 >= nvalid) sa &= 0xffffu;
+                if (tb >= nvalid) sb = 0; else if (tb + 1 >= nvalid) sb &= 0xffffu;
+            }
+            uint32_t a0, a1, a2, a3;
+            mul_split(ph[0], pl[0], sa, a0, a1);
+            mul_split(ph[1], pl[1], sb, a2, a3);
+            // codes of this thread's NT channels for the four tokens
+            const int bitoff = (G * cg + C::NT * r) * BITS;
+            uint32_t x[4][(NB + 31) / 32];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int tok = (k & 2 ? tb : ta) + (k & 1);
+                const uint8_t* src = vb + tok * RB + bitoff / 8;
+                if (NB >= 32) {
+#pragma unroll
+                    for (int w = 0; w < (NB + 31) / 32; ++w) x[k][w] = reinterpret_cast<const uint32_t*>(src)[w];
+                } else if (NB == 16) {
+                    x[k][0] = *reinterpret_cast<const uint16_t*>(src);
+                } else {
+                    x[k][0] = (uint32_t)(*src) >> (bitoff % 8);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < C::NT; ++i) {
+                const int bp = i * BITS;              // bit position of channel i inside x
+                const int w = bp / 32, wb = bp % 32;
+                // pack the two tokens' 16-bit halves that contain the field, then shift/mask
+                const uint32_t selA = (wb < 16) ? 0x5410u : 0x7632u;
+                const uint32_t pa = prmt(x[0][w], x[1][w], selA), pb = prmt(x[2][w], x[3][w], selA);
+                const int sh = wb % 16;
+                const uint32_t b0 = (sh >= POS ? pa >> (sh - POS) : pa << (POS - sh)) & MASK;
+                const uint32_t b1 = (sh >= POS ? pb >> (sh - POS) : pb << (POS - sh)) & MASK;
+                mma_f16(st.o[cg * C::NT + i], a0, a1, a2, a3, b0, b1);
+            }
+        }
+    }
+}
+
+template <int D, int G>
+__device__ __forceinline__ void values_bf16(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk,
+                                            const float (&pz)[16], int nvalid, int lane) {
+    using C = Cfg<D, G>;
+    const int r = lane >> 2, t = lane & 3;
+    const uint8_t* vb = blk + kP * D * 2;
+    constexpr float kScale = 1.52587890625e-05f;      // 2^-16: same accumulator scale as the code path
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const int ta = 16 * ks + 2 * t, tb = ta + 8;
+        uint32_t a0, a1, a2, a3;
+        split_bf16x2(pz[4 * ks + 0] * kScale, pz[4 * ks + 1] * kScale, a0, a1);
+        split_bf16x2(pz[4 * ks + 2] * kScale, pz[4 * ks + 3] * kScale, a2, a3);
+        const bool ragged = nvalid < 16 * ks + 16;
+        uint32_t ma = 0xffffffffu, mb = 0xffffffffu;   // masks zeroing rows beyond nvalid (they may hold anything)
+        if (ragged) {
+            ma = ta >= nvalid ? 0u : ta + 1 >= nvalid ? 0xffffu : 0xffffffffu;
+            mb = tb >= nvalid ? 0u : tb + 1 >= nvalid ? 0xffffu : 0xffffffffu;
+        }
+#pragma unroll
+        for (int cg = 0; cg < C::GV; ++cg) {
+            const int ch = G * cg + C::NT * r;
+            uint32_t x[4][C::NT / 2];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int tok = (k & 2 ? tb : ta) + (k & 1);
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(vb + (tok * D + ch) * 2);
+#pragma unroll
+                for (int w = 0; w < C::NT / 2; ++w) x[k][w] = src[w];
+            }
+#pragma unroll
+            for (int i = 0; i < C::NT; ++i) {
+                const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = prmt(x[0][i / 2], x[1][i / 2], sel) & ma;
+                const uint32_t b1 = prmt(x[2][i / 2], x[3][i / 2], sel) & mb;
+                mma_bf16(st.o[cg * C::NT + i], a0, a1, a2, a3, b0, b1);
+            }
+        }
+    }
+}
+
+// ---- a centroid block: one key and one value stand for nvalid tokens ------------------------------
+template <int D, int G>
+__device__ __forceinline__ void centroid_block(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk,
+                                               int nvalid, int lane) {
+    using C = Cfg<D, G>;
+    const int r = lane >> 2, t = lane & 3;
+    const __half2* ck = reinterpret_cast<const __half2*>(blk) + (C::DT * t) / 2;
+    const float* q = sm.sq + r * D + C::DT * t;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < C::DT / 2; ++i) {
+        const float2 k2 = __half22float2(ck[i]);
+        s = fmaf(q[2 * i], k2.x, s);
+        s = fmaf(q[2 * i + 1], k2.y, s);
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    const float z = s * 1.4426950408889634f;
+    const float mnew = fmaxf(st.m, z);
+    const float corr = ex2(st.m - mnew);
+    st.m = mnew;
+    const float w = ex2(z - mnew) * (float)nvalid;
+    st.l = st.l * corr + (t == 0 ? w : 0.f);
+    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+        for (int n = 0; n < C::NTILE; ++n) {
+            st.o[n][0] *= corr; st.o[n][1] *= corr; st.o[n][2] *= corr; st.o[n][3] *= corr;
+        }
+        st.ob[0] *= corr; st.ob[1] *= corr; st.ob[2] *= corr; st.ob[3] *= corr;
+    }
+    const __half* cv = reinterpret_cast<const __half*>(blk + D * 2);
+    const float ws = w * 1.52587890625e-05f;
+#pragma unroll
+    for (int cg = 0; cg < C::GV; ++cg)
+#pragma unroll
+        for (int i = 0; i < C::NT; ++i) {
+            st.o[cg * C::NT + i][0] = fmaf(ws, __half2float(cv[G * cg + C::NT * (2 * t) + i]), st.o[cg * C::NT + i][0]);
+            st.o[cg * C::NT + i][1] = fmaf(ws, __half2float(cv[G * cg + C::NT * (2 * t + 1) + i]), st.o[cg * C::NT + i][1]);
+        }
+}
+
+template <int D, int G>
+__device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
+    using C = Cfg<D, G>;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = lane >> 2, t = lane & 3;
+    WarpState<D, G> st;
+    uint32_t sync_phase = 0;
+    int seq = warp;
+    int code = 0;                                   // non-zero: a wait gave up
+    for (int iseq = 0; code == 0; ++iseq) {
+        const int ib = iseq & 1;
+        if (!mbar_wait(&sm.item_full[ib], (uint32_t)(iseq >> 1) & 1u)) { code = 2; break; }
+        const ItemDesc it = sm.item[ib];
+        if (it.exit) return;
+        if (!prepare_query(p, sm, it.row, sync_phase)) { code = 3; break; }
+#pragma unroll
+        for (int n = 0; n < C::NTILE; ++n) st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.f;
+        st.ob[0] = st.ob[1] = st.ob[2] = st.ob[3] = 0.f;
+        st.m = -INFINITY;
+        st.l = 0.f;
+
+        for (int round = 0; round < it.rounds; ++round, seq += kConsumerWarps) {
+            const int slot = seq % kNSlot;
+            if (!mbar_wait(&sm.full[slot], (uint32_t)(seq / kNSlot) & 1u)) { code = 4; break; }
+            const Desc d = sm.desc[slot];
+            if (d.level) {
+                const uint8_t* blk = sm.ring + d.off;
+                float z[16];
+                if (d.level == 1) {
+                    centroid_block(sm, st, blk, d.nvalid, lane);
+                } else {
+                    if (d.level == 16) scores_bf16(sm, blk, z, lane);
+                    else if (d.level == 8) scores_quant<D, G, 8>(sm, blk, z, lane);
+                    else if (d.level == 4) scores_quant<D, G, 4>(sm, blk, z, lane);
+                    else scores_quant<D, G, 2>(sm, blk, z, lane);
+                    softmax_update(st, z, d.nvalid, lane);
+                    if (d.level == 16) values_bf16(sm, st, blk, z, d.nvalid, lane);
+                    else if (d.level == 8) values_quant<D, G, 8>(sm, st, blk, z, d.nvalid, lane);
+                    else if (d.level == 4) values_quant<D, G, 4>(sm, st, blk, z, d.nvalid, lane);
+                    else values_quant<D, G, 2>(sm, st, blk, z, d.nvalid, lane);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.empty[slot]);
+        }
+        if (code) break;
+
+        // ---- merge the four warp states of this item and write its record ----------------------
+        float l = st.l;
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        float* mine = sm.stage + (size_t)warp * 8 * (D + 2) + (size_t)r * (D + 2);
+        if (t == 0) { mine[0] = st.m; mine[1] = l; }
+        // p . vlo of channel group cg sits in lane 4r + cg/2, column cg & 1, scaled 2^8
+        const float ob_even = st.ob[0] + st.ob[2], ob_odd = st.ob[1] + st.ob[3];
+#pragma unroll
+        for (int cg = 0; cg < C::GV; ++cg) {
+            const float src = (cg & 1) ? ob_odd : ob_even;
+            const float bias = __shfl_sync(0xffffffffu, src, (lane & ~3) | (cg >> 1)) * 0.00390625f;
+#pragma unroll
+            for (int i = 0; i < C::NT; ++i) {
+                const int n = cg * C::NT + i;
+                mine[2 + G * cg + C::NT * (2 * t) + i] = fmaf(st.o[n][0] + st.o[n][2], 65536.f, bias);
+                mine[2 + G * cg + C::NT * (2 * t + 1) + i] = fmaf(st.o[n][1] + st.o[n][3], 65536.f, bias);
+            }
+        }
+        if (!consumer_sync(sm.sync_bar, sync_phase)) { code = 5; break; }
+        float* rec = p.part + (size_t)it.item * p.rep * (D + 2);
+        for (int h = warp; h < p.rep; h += kConsumerWarps) {
+            float mw[kConsumerWarps], mmax = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                mw[w] = sm.stage[(size_t)w * 8 * (D + 2) + (size_t)h * (D + 2)];
+                mmax = fmaxf(mmax, mw[w]);
+            }
+            float lsum = 0.f, wgt[kConsumerWarps];
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                wgt[w] = (mw[w] == -INFINITY) ? 0.f : ex2(mw[w] - mmax);
+                lsum += wgt[w] * sm.stage[(size_t)w * 8 * (D + 2) + (size_t)h * (D + 2) + 1];
+            }
+            for (int dd = lane; dd < D; dd += 32) {
+                float a = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w)
+                    a = fmaf(wgt[w], sm.stage[(size_t)w * 8 * (D + 2) + (size_t)h * (D + 2) + 2 + dd], a);
+                rec[(size_t)h * (D + 2) + 2 + dd] = a;
+            }
+            if (lane == 0) {
+                // records are kept in the natural-log domain like the generic kernel's
+                rec[(size_t)h * (D + 2) + 0] = mmax * 0.6931471805599453f;
+                rec[(size_t)h * (D + 2) + 1] = lsum;
+            }
+        }
+        if (!consumer_sync(sm.sync_bar, sync_phase)) { code = 6; break; }
+        if (tid == 0) mbar_arrive(&sm.item_empty[ib]);
+        if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+    }
+    if (code && lane == 0) {
+        atomicExch(p.status, code);
+        atomicExch(abort_flag, 1);
+    }
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(Params p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ int abort_flag;
+    Smem<D, G> sm(smem_raw);
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kNSlot; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.item_full[s], 1);
+            mbar_init(&sm.item_empty[s], 1);
+        }
+        mbar_init(sm.sync_bar, kConsumerWarps);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x >= kConsumers) producer_loop<D, G>(p, sm, &abort_flag);
+    else consumer_loop<D, G>(p, sm, &abort_flag);
+}
+
+}  // namespace mma
+}  // namespace gkv

@@ -11,6 +11,17 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-3          # max-abs bound on attention outputs stated for this path
 
 
+@pytest.fixture(params=["mma", "generic"], autouse=True)
+def kernel_choice(request, monkeypatch):
+    """Every test runs once per decode kernel: the tensor-core kernel (default dispatch) and the
+    exact-fp32 CUDA-core kernel that covers the shapes the former does not."""
+    if request.param == "generic":
+        monkeypatch.setenv("GKV_DECODE_KERNEL", "generic")
+    else:
+        monkeypatch.delenv("GKV_DECODE_KERNEL", raising=False)
+    return request.param
+
+
 @pytest.fixture(scope="module")
 def ext():
     from geodesia_kv_b200.cuda_ext import get_ext
@@ -126,6 +137,21 @@ def test_peaked_softmax_and_large_scores(ext, oracle):
     want = oracle.mixed_attn_decode(q, *oracle_args(c))
     got = run(ext, q, to_torch(c, "cuda"), c)
     assert np.isfinite(got).all() and np.abs(got - want).max() < TOL
+
+
+def test_block_starts_that_are_not_16_byte_aligned(ext, oracle):
+    """A cache row living at an odd address cannot be bulk-copied; the kernel must still read it."""
+    c = oracle_cache(oracle, 31, 1, 1, 9, 128, 32)
+    t = to_torch(c, "cuda")
+    n = t["data"].numel()
+    buf = torch.zeros(n + 64, dtype=torch.uint8, device="cuda")
+    buf[4:4 + n] = t["data"].view(-1)
+    t["data"] = buf[4:4 + n].view(1, 1, n)
+    assert t["data"].is_contiguous() and t["data"].data_ptr() % 16 == 4
+    q = np.random.default_rng(2).standard_normal((1, 4, 128), dtype=np.float32) * np.float32(128 ** -0.5)
+    want = oracle.mixed_attn_decode(q, *oracle_args(c))
+    got = ext.mixed_attn_decode(torch.from_numpy(q).cuda(), *kernel_args(t, c)).cpu().numpy()
+    assert np.abs(got - want).max() < 5e-5
 
 
 def test_empty_cache_gives_zeros(ext):
