@@ -39,6 +39,8 @@ WORKLOADS = {
     # name: layers, Hq, Hkv, D, seqs per GPU, tokens, rung probabilities (16, 8, 4, 2, centroid)
     "cfg1": dict(layers=36, Hq=32, Hkv=8, D=128, B=32, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
                  name="qwen3-8b-shape decode attention, 36 layers, 32 seq x 16384 tok per GPU"),
+    "cfg1-small": dict(layers=2, Hq=32, Hkv=8, D=128, B=8, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
+                       name="profiling-sized slice of the qwen3-8b-shape workload: 2 layers, 8 seq x 16384 tok"),
     "cfg0": dict(layers=64, Hq=16, Hkv=2, D=128, B=1, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
                  name="qwen2.5-3b-shape single-sequence layer, 64 distinct layer buffers of 16384 tok"),
     "cfg3": dict(layers=28, Hq=28, Hkv=4, D=128, B=1, T=1048576, probs=(0.02, 0.08, 0.30, 0.40, 0.20),

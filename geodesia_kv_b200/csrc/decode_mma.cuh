@@ -442,150 +442,163 @@ __device__ bool prepare_query(const Params& p, Smem<D, G>& sm, int row, uint32_t
     return consumer_sync(sm.sync_bar, phase);
 }
 
-// ---- K side of a quantised block: scores in the log2 domain ---------------------------------
-template <int D, int G, int BITS>
-__device__ __forceinline__ void scores_quant(const Smem<D, G>& sm, const uint8_t* blk, float (&z)[16], int lane) {
+// The blocks are processed in UNITS of G tokens (one token group of the K scales): scores of
+// the unit, online-softmax update, value product of the unit.  Loops over the contraction
+// (chunks of two k-steps on the K side, 16-token k-steps on the V side) are real loops, not
+// unrolled: the fully unrolled kernel was 130 KB of code and spent most of its time waiting
+// for instruction fetches.
+template <int D, int G>
+struct Unit {
+    static constexpr int U = G;          // tokens
+    static constexpr int NU = G / 8;     // token n-tiles
+    static constexpr int KU = G / 16;    // PV k-steps
+    static constexpr int ZN = G / 4;     // scores held per thread
+};
+
+// ---- q . klo for every token group of a quantised block: one n-tile whose column n is group n ----
+template <int D, int G>
+__device__ __forceinline__ void key_bias(const Smem<D, G>& sm, const uint8_t* klo, float (&bias)[4], int lane) {
     using C = Cfg<D, G>;
+    const int r = lane >> 2, t = lane & 3;
+    const bool live = r < C::TG;
+    const uint4* lo4 = reinterpret_cast<const uint4*>(klo + ((live ? r : 0) * D + C::DT * t) * 2);
+    bias[0] = bias[1] = bias[2] = bias[3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < C::CH; ++i) {
+        const uint4 qh = load_qchunk(sm, 0, i, lane), ql = load_qchunk(sm, 1, i, lane);
+        uint4 b = lo4[i];
+        if (!live) b = make_uint4(0, 0, 0, 0);
+        mma_f16(bias, qh.x, ql.x, qh.y, ql.y, b.x, b.y);
+        mma_f16(bias, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
+    }
+}
+
+// ---- K side of one unit of a quantised block: scores in the log2 domain ---------------------------
+template <int D, int G, int BITS>
+__device__ __forceinline__ void scores_unit(const Smem<D, G>& sm, const uint8_t* blk, int tg, const float (&bias)[4],
+                                            float (&z)[Unit<D, G>::ZN], int lane) {
+    using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
     const int r = lane >> 2, t = lane & 3;
     constexpr int RB = D * BITS / 8;                     // bytes per token row
     constexpr int TB = RB / 4;                           // bytes per thread per row
-    const uint8_t* klo = blk + 2 * (kP * RB);
-    const uint8_t* kst = klo + C::KSCALE;
+    const uint8_t* kst = blk + 2 * (kP * RB) + C::KSCALE;
     constexpr int plane = BITS == 8 ? 0 : BITS == 4 ? 2 : 4;
     const float f = sm.sf[r];
+    const uint32_t* nat = reinterpret_cast<const uint32_t*>(kst + (tg * D + C::DT * t) * 2);
+    const uint8_t* row0 = blk + (tg * UU::U + r) * RB + t * TB;
 
-    // q . klo for every token group: one n-tile whose column n is token group n
-    float bias[4] = {0.f, 0.f, 0.f, 0.f};
-    {
-        const bool live = r < C::TG;
-        const uint4* lo4 = reinterpret_cast<const uint4*>(klo + ((live ? r : 0) * D + C::DT * t) * 2);
+    float acc[UU::NU][4];
 #pragma unroll
-        for (int i = 0; i < C::CH; ++i) {
-            const uint4 qh = load_qchunk(sm, 0, i, lane), ql = load_qchunk(sm, 1, i, lane);
-            uint4 b = lo4[i];
-            if (!live) b = make_uint4(0, 0, 0, 0);
-            mma_f16(bias, qh.x, ql.x, qh.y, ql.y, b.x, b.y);
-            mma_f16(bias, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
+    for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll 1
+    for (int i = 0; i < C::CH; ++i) {                   // two k-steps at a time
+        const uint4 qh = load_qchunk(sm, plane, i, lane), ql = load_qchunk(sm, plane + 1, i, lane);
+        uint32_t sp[4];                                  // step pairs of k-steps 2i and 2i+1 in this arrangement
+        if (BITS == 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
+            sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
+        } else if (BITS == 4) {                          // s = 2x+y with x = i: words 4i+y, 4i+y+2
+            const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
+            sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
+            sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
+        } else {                                         // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
+            const int w0 = 8 * (i >> 1) + 2 * (i & 1);
+            const uint2 va = *reinterpret_cast<const uint2*>(nat + w0);
+            const uint2 vb = *reinterpret_cast<const uint2*>(nat + w0 + 4);
+            sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
+            sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
+        }
+        uint32_t a[8];
+        mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
+        mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
+        mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
+        mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
+#pragma unroll
+        for (int n = 0; n < UU::NU; ++n) {
+            const uint8_t* row = row0 + n * 8 * RB;
+            uint32_t b0, b1, b2, b3;                     // B registers of k-steps 2i (b0,b1) and 2i+1 (b2,b3)
+            if (BITS == 8) {
+                const uint2 w = *reinterpret_cast<const uint2*>(row + 8 * i);
+                b0 = prmt(w.x, 0u, 0x4140); b1 = prmt(w.x, 0u, 0x4342);
+                b2 = prmt(w.y, 0u, 0x4140); b3 = prmt(w.y, 0u, 0x4342);
+            } else if (BITS == 4) {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * i);
+                const uint32_t u = w << 3, v = w >> 5;
+                b0 = u & 0x00780078u; b1 = u & 0x07800780u;
+                b2 = v & 0x00780078u; b3 = v & 0x07800780u;
+            } else {
+                // fields 4h..4h+3 (and +8) of the word, h = i & 1, brought to bits 8-9 / 6-7
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * (i >> 1)) >> (8 * (i & 1));
+                const uint32_t u = w << 4;
+                b0 = (w << 8) & 0x03000300u; b1 = u & 0x00C000C0u;
+                b2 = u & 0x03000300u;        b3 = w & 0x00C000C0u;
+            }
+            mma_f16(acc[n], a[0], a[1], a[2], a[3], b0, b1);
+            mma_f16(acc[n], a[4], a[5], a[6], a[7], b2, b3);
         }
     }
+    // bias of this token group for head r lives in lane 4r + tg/2, column tg & 1
+    const float bsel = (tg & 1) ? bias[1] + bias[3] : bias[0] + bias[2];
+    const float bg = __shfl_sync(0xffffffffu, bsel, (lane & ~3) | (tg >> 1));
 #pragma unroll
-    for (int tg = 0; tg < C::TG; ++tg) {
-        float acc[C::NTG][4];
-#pragma unroll
-        for (int n = 0; n < C::NTG; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-#pragma unroll
-        for (int i = 0; i < C::CH; ++i) {               // two k-steps at a time
-            const uint4 qh = load_qchunk(sm, plane, i, lane), ql = load_qchunk(sm, plane + 1, i, lane);
-            // step pairs of k-steps 2i and 2i+1 in this arrangement
-            uint32_t sp[4];
-            const uint32_t* nat = reinterpret_cast<const uint32_t*>(kst + (tg * D + C::DT * t) * 2);
-            if (BITS == 8) {
-                const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
-                sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
-            } else if (BITS == 4) {                       // s = 2x+y with x = i: words 4i+y, 4i+y+2
-                const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
-                sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
-                sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
-            } else {                                      // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
-                const int x = i >> 1, y0 = 2 * (i & 1);
-                const uint2 va = *reinterpret_cast<const uint2*>(nat + 8 * x + y0);
-                const uint2 vb = *reinterpret_cast<const uint2*>(nat + 8 * x + y0 + 4);
-                sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
-                sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
-            }
-            uint32_t a[8];
-            mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
-            mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
-            mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
-            mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
-#pragma unroll
-            for (int n = 0; n < C::NTG; ++n) {
-                const int tok = (tg * C::NTG + n) * 8 + r;
-                const uint8_t* row = blk + tok * RB + t * TB;
-                uint32_t b0, b1, b2, b3;                  // B registers of k-steps 2i (b0,b1) and 2i+1 (b2,b3)
-                if (BITS == 8) {
-                    const uint2 w = *reinterpret_cast<const uint2*>(row + 8 * i);
-                    b0 = prmt(w.x, 0u, 0x4140); b1 = prmt(w.x, 0u, 0x4342);
-                    b2 = prmt(w.y, 0u, 0x4140); b3 = prmt(w.y, 0u, 0x4342);
-                } else if (BITS == 4) {
-                    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * i);
-                    const uint32_t u = w << 3, v = w >> 5;
-                    b0 = u & 0x00780078u; b1 = u & 0x07800780u;
-                    b2 = v & 0x00780078u; b3 = v & 0x07800780u;
-                } else {
-                    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * (i >> 1));
-                    if ((i & 1) == 0) {        // fields 0..3 (and 8..11) of the word
-                        const uint32_t u = w << 4;
-                        b0 = (w << 8) & 0x03000300u; b1 = u & 0x00C000C0u;
-                        b2 = u & 0x03000300u;        b3 = w & 0x00C000C0u;
-                    } else {                   // fields 4..7 (and 12..15)
-                        const uint32_t u = w >> 4;
-                        b0 = w & 0x03000300u; b1 = u & 0x00C000C0u;
-                        b2 = u & 0x03000300u; b3 = (w >> 8) & 0x00C000C0u;
-                    }
-                }
-                mma_f16(acc[n], a[0], a[1], a[2], a[3], b0, b1);
-                mma_f16(acc[n], a[4], a[5], a[6], a[7], b2, b3);
-            }
-        }
-        // bias of this token group for head r lives in lane 4r + tg/2, column tg & 1
-        const float bsel = (tg & 1) ? bias[1] + bias[3] : bias[0] + bias[2];
-        const float bg = __shfl_sync(0xffffffffu, bsel, (lane & ~3) | (tg >> 1));
-#pragma unroll
-        for (int n = 0; n < C::NTG; ++n) {
-            const int nt = tg * C::NTG + n;
-            z[2 * nt + 0] = fmaf(acc[n][0] + acc[n][2], k_unscale(BITS), bg) * f;
-            z[2 * nt + 1] = fmaf(acc[n][1] + acc[n][3], k_unscale(BITS), bg) * f;
-        }
+    for (int n = 0; n < UU::NU; ++n) {
+        z[2 * n + 0] = fmaf(acc[n][0] + acc[n][2], k_unscale(BITS), bg) * f;
+        z[2 * n + 1] = fmaf(acc[n][1] + acc[n][3], k_unscale(BITS), bg) * f;
     }
 }
 
 template <int D, int G>
-__device__ __forceinline__ void scores_bf16(const Smem<D, G>& sm, const uint8_t* blk, float (&z)[16], int lane) {
+__device__ __forceinline__ void scores_unit_bf16(const Smem<D, G>& sm, const uint8_t* blk, int tg,
+                                                 float (&z)[Unit<D, G>::ZN], int lane) {
     using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
     const int r = lane >> 2, t = lane & 3;
     const float f = sm.sf[r];
-    float acc[8][4];
+    const uint8_t* row0 = blk + ((tg * UU::U + r) * D + C::DT * t) * 2;
+    float acc[UU::NU][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-#pragma unroll
+    for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll 1
     for (int i = 0; i < C::CH; ++i) {
         const uint4 qh = load_qchunk(sm, 6, i, lane), ql = load_qchunk(sm, 7, i, lane);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const uint4 w = *reinterpret_cast<const uint4*>(blk + ((n * 8 + r) * D + C::DT * t) * 2 + 16 * i);
+        for (int n = 0; n < UU::NU; ++n) {
+            const uint4 w = *reinterpret_cast<const uint4*>(row0 + n * 8 * D * 2 + 16 * i);
             mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w.x, w.y);
             mma_bf16(acc[n], qh.z, ql.z, qh.w, ql.w, w.z, w.w);
         }
     }
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < UU::NU; ++n) {
         z[2 * n + 0] = (acc[n][0] + acc[n][2]) * f;
         z[2 * n + 1] = (acc[n][1] + acc[n][3]) * f;
     }
 }
 
-// ---- online-softmax update shared by all rungs --------------------------------------------------
-// z: scores of head r for tokens 8*nt + 2t + {0,1} (log2 domain).  Returns p in z.
+// ---- online-softmax update of one unit -----------------------------------------------------------
+// z: scores of head r for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid tokens
+// left in this unit (>= 1).  Returns p in z.
 template <int D, int G>
-__device__ __forceinline__ void softmax_update(WarpState<D, G>& st, float (&z)[16], int nvalid, int lane) {
+__device__ __forceinline__ void softmax_unit(WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel, int lane) {
     using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
     const int t = lane & 3;
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < UU::ZN; ++i) {
         const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
-        if (tok >= nvalid) z[i] = -INFINITY;
+        if (tok >= nrel) z[i] = -INFINITY;
         mx = fmaxf(mx, z[i]);
     }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float mnew = fmaxf(st.m, mx);            // finite: the caller guarantees nvalid >= 1
+    const float mnew = fmaxf(st.m, mx);
     const float corr = ex2(st.m - mnew);           // 0 when st.m = -inf
     st.m = mnew;
     float ls = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < UU::ZN; ++i) {
         z[i] = ex2(z[i] - mnew);
         ls += z[i];
     }
@@ -599,11 +612,35 @@ __device__ __forceinline__ void softmax_update(WarpState<D, G>& st, float (&z)[1
     }
 }
 
-// ---- V side of a quantised block ------------------------------------------------------------------
+// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane for every channel group cg.
+template <int GV>
+__device__ __forceinline__ void scale_pairs(const uint8_t* plane, int tok, uint32_t (&out)[GV]) {
+    const uint8_t* p = plane + tok * GV * 2;           // tok is even: two rows are 4*GV contiguous bytes
+    if (GV == 4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        out[0] = prmt(v.x, v.z, 0x5410); out[1] = prmt(v.x, v.z, 0x7632);
+        out[2 % GV] = prmt(v.y, v.w, 0x5410); out[3 % GV] = prmt(v.y, v.w, 0x7632);
+    } else if (GV == 2) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        out[0] = prmt(v.x, v.y, 0x5410); out[1 % GV] = prmt(v.x, v.y, 0x7632);
+    } else {
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
+#pragma unroll
+        for (int cg = 0; cg < GV; ++cg) out[cg] = (uint32_t)h[cg] | ((uint32_t)h[GV + cg] << 16);
+    }
+}
+
+// Zero the halves of a token pair (tok, tok+1) that lie at or beyond nvalid.
+__device__ __forceinline__ uint32_t pair_mask(int tok, int nvalid) {
+    return tok >= nvalid ? 0u : tok + 1 >= nvalid ? 0xffffu : 0xffffffffu;
+}
+
+// ---- V side of one unit of a quantised block -------------------------------------------------------
 template <int D, int G, int BITS>
-__device__ __forceinline__ void values_quant(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk,
-                                             const float (&pz)[16], int nvalid, int lane) {
+__device__ __forceinline__ void values_unit(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int unit,
+                                            float (&pz)[Unit<D, G>::ZN], int nvalid, int lane) {
     using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
     const int r = lane >> 2, t = lane & 3;
     constexpr int RB = D * BITS / 8;
     const uint8_t* vb = blk + kP * RB;
@@ -614,29 +651,28 @@ __device__ __forceinline__ void values_quant(const Smem<D, G>& sm, WarpState<D, 
     constexpr uint32_t MASK = (((1u << BITS) - 1u) << POS) * 0x00010001u;
     constexpr float PSCALE = (float)(256 >> POS);    // weights carry 2^(8-POS) so that every rung adds p*v*2^-16
     const __half2 lo_scale = __float2half2_rn((float)(1 << POS));
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-        const int ta = 16 * ks + 2 * t, tb = ta + 8;  // token pairs (ta, ta+1) and (tb, tb+1)
+#pragma unroll 1
+    for (int ku = 0; ku < UU::KU; ++ku) {
+        const int ta = unit * UU::U + 16 * ku + 2 * t, tb = ta + 8;   // token pairs (ta, ta+1) and (tb, tb+1)
         uint32_t ph[2], pl[2];
-        split_f16x2(pz[4 * ks + 0] * PSCALE, pz[4 * ks + 1] * PSCALE, ph[0], pl[0]);
-        split_f16x2(pz[4 * ks + 2] * PSCALE, pz[4 * ks + 3] * PSCALE, ph[1], pl[1]);
-        const bool ragged = nvalid < 16 * ks + 16;   // warp-uniform: some token of this k-step is masked
-        // V scale rows of the four tokens: [token][GV] halves
-        const uint16_t* st_a = reinterpret_cast<const uint16_t*>(vst) + ta * C::GV;
-        const uint16_t* st_b = reinterpret_cast<const uint16_t*>(vst) + tb * C::GV;
-        const uint16_t* lo_a = reinterpret_cast<const uint16_t*>(vlo) + ta * C::GV;
-        const uint16_t* lo_b = reinterpret_cast<const uint16_t*>(vlo) + tb * C::GV;
+        split_f16x2(pz[0] * PSCALE, pz[1] * PSCALE, ph[0], pl[0]);
+        split_f16x2(pz[2] * PSCALE, pz[3] * PSCALE, ph[1], pl[1]);
+#pragma unroll
+        for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];       // next k-step's weights move to the front
+        const bool ragged = nvalid < unit * UU::U + 16 * ku + 16;     // warp-uniform: a token of this k-step is masked
+        const uint32_t ma = ragged ? pair_mask(ta, nvalid) : 0xffffffffu;
+        const uint32_t mb = ragged ? pair_mask(tb, nvalid) : 0xffffffffu;
+        uint32_t sa[C::GV], sb[C::GV], la[C::GV], lb[C::GV];
+        scale_pairs<C::GV>(vst, ta, sa);
+        scale_pairs<C::GV>(vst, tb, sb);
+        scale_pairs<C::GV>(vlo, ta, la);
+        scale_pairs<C::GV>(vlo, tb, lb);
         // p . vlo: column n of this n-tile is channel group n
         {
             uint32_t b0 = 0, b1 = 0;
-            if (r < C::GV) {
-                b0 = (uint32_t)lo_a[r] | ((uint32_t)lo_a[C::GV + r] << 16);
-                b1 = (uint32_t)lo_b[r] | ((uint32_t)lo_b[C::GV + r] << 16);
-                if (ragged) {
-                    if (ta >= nvalid) b0 = 0; else if (ta + 1 >= nvalid) b0 &= 0xffffu;
-                    if (tb >= nvalid) b1 = 0; else if (tb + 1 >= nvalid) b1 &= 0xffffu;
-                }
-            }
+#pragma unroll
+            for (int cg = 0; cg < C::GV; ++cg)
+                if (r == cg) { b0 = la[cg] & ma; b1 = lb[cg] & mb; }
             if (POS) {                                 // keep the 2^8 scale of the p . vlo accumulator
                 b0 = h2_as_u32(__hmul2(u32_as_h2(b0), lo_scale));
                 b1 = h2_as_u32(__hmul2(u32_as_h2(b1), lo_scale));
@@ -645,15 +681,9 @@ __device__ __forceinline__ void values_quant(const Smem<D, G>& sm, WarpState<D, 
         }
 #pragma unroll
         for (int cg = 0; cg < C::GV; ++cg) {
-            uint32_t sa = (uint32_t)st_a[cg] | ((uint32_t)st_a[C::GV + cg] << 16);
-            uint32_t sb = (uint32_t)st_b[cg] | ((uint32_t)st_b[C::GV + cg] << 16);
-            if (ragged) {
-                if (ta >= nvalid) sa = 0; else if (ta + 1 >= nvalid) sa &= 0xffffu;
-                if (tb >= nvalid) sb = 0; else if (tb + 1 >= nvalid) sb &= 0xffffu;
-            }
             uint32_t a0, a1, a2, a3;
-            mul_split(ph[0], pl[0], sa, a0, a1);
-            mul_split(ph[1], pl[1], sb, a2, a3);
+            mul_split(ph[0], pl[0], sa[cg] & ma, a0, a1);
+            mul_split(ph[1], pl[1], sb[cg] & mb, a2, a3);
             // codes of this thread's NT channels for the four tokens
             const int bitoff = (G * cg + C::NT * r) * BITS;
             uint32_t x[4][(NB + 31) / 32];
@@ -687,24 +717,25 @@ __device__ __forceinline__ void values_quant(const Smem<D, G>& sm, WarpState<D, 
 }
 
 template <int D, int G>
-__device__ __forceinline__ void values_bf16(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk,
-                                            const float (&pz)[16], int nvalid, int lane) {
+__device__ __forceinline__ void values_unit_bf16(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int unit,
+                                                 float (&pz)[Unit<D, G>::ZN], int nvalid, int lane) {
     using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
     const int r = lane >> 2, t = lane & 3;
     const uint8_t* vb = blk + kP * D * 2;
     constexpr float kScale = 1.52587890625e-05f;      // 2^-16: same accumulator scale as the code path
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-        const int ta = 16 * ks + 2 * t, tb = ta + 8;
+#pragma unroll 1
+    for (int ku = 0; ku < UU::KU; ++ku) {
+        const int ta = unit * UU::U + 16 * ku + 2 * t, tb = ta + 8;
         uint32_t a0, a1, a2, a3;
-        split_bf16x2(pz[4 * ks + 0] * kScale, pz[4 * ks + 1] * kScale, a0, a1);
-        split_bf16x2(pz[4 * ks + 2] * kScale, pz[4 * ks + 3] * kScale, a2, a3);
-        const bool ragged = nvalid < 16 * ks + 16;
-        uint32_t ma = 0xffffffffu, mb = 0xffffffffu;   // masks zeroing rows beyond nvalid (they may hold anything)
-        if (ragged) {
-            ma = ta >= nvalid ? 0u : ta + 1 >= nvalid ? 0xffffu : 0xffffffffu;
-            mb = tb >= nvalid ? 0u : tb + 1 >= nvalid ? 0xffffu : 0xffffffffu;
-        }
+        split_bf16x2(pz[0] * kScale, pz[1] * kScale, a0, a1);
+        split_bf16x2(pz[2] * kScale, pz[3] * kScale, a2, a3);
+#pragma unroll
+        for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];
+        const bool ragged = nvalid < unit * UU::U + 16 * ku + 16;
+        // rows beyond nvalid may hold anything (even NaN patterns): zero them
+        const uint32_t ma = ragged ? pair_mask(ta, nvalid) : 0xffffffffu;
+        const uint32_t mb = ragged ? pair_mask(tb, nvalid) : 0xffffffffu;
 #pragma unroll
         for (int cg = 0; cg < C::GV; ++cg) {
             const int ch = G * cg + C::NT * r;
@@ -724,6 +755,38 @@ __device__ __forceinline__ void values_bf16(const Smem<D, G>& sm, WarpState<D, G
                 mma_bf16(st.o[cg * C::NT + i], a0, a1, a2, a3, b0, b1);
             }
         }
+    }
+}
+
+// One quantised block: bias once, then its units.
+template <int D, int G, int BITS>
+__device__ __forceinline__ void quant_block(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int nvalid, int lane) {
+    using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
+    float bias[4];
+    key_bias(sm, blk + 2 * (kP * D * BITS / 8), bias, lane);
+#pragma unroll 1
+    for (int unit = 0; unit < kP / UU::U; ++unit) {
+        const int nrel = nvalid - unit * UU::U;
+        if (nrel <= 0) break;
+        float z[UU::ZN];
+        scores_unit<D, G, BITS>(sm, blk, unit, bias, z, lane);
+        softmax_unit(st, z, nrel, lane);
+        values_unit<D, G, BITS>(sm, st, blk, unit, z, nvalid, lane);
+    }
+}
+
+template <int D, int G>
+__device__ __forceinline__ void bf16_block(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int nvalid, int lane) {
+    using UU = Unit<D, G>;
+#pragma unroll 1
+    for (int unit = 0; unit < kP / UU::U; ++unit) {
+        const int nrel = nvalid - unit * UU::U;
+        if (nrel <= 0) break;
+        float z[UU::ZN];
+        scores_unit_bf16(sm, blk, unit, z, lane);
+        softmax_unit(st, z, nrel, lane);
+        values_unit_bf16(sm, st, blk, unit, z, nvalid, lane);
     }
 }
 
@@ -795,20 +858,11 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
             const Desc d = sm.desc[slot];
             if (d.level) {
                 const uint8_t* blk = sm.ring + d.off;
-                float z[16];
-                if (d.level == 1) {
-                    centroid_block(sm, st, blk, d.nvalid, lane);
-                } else {
-                    if (d.level == 16) scores_bf16(sm, blk, z, lane);
-                    else if (d.level == 8) scores_quant<D, G, 8>(sm, blk, z, lane);
-                    else if (d.level == 4) scores_quant<D, G, 4>(sm, blk, z, lane);
-                    else scores_quant<D, G, 2>(sm, blk, z, lane);
-                    softmax_update(st, z, d.nvalid, lane);
-                    if (d.level == 16) values_bf16(sm, st, blk, z, d.nvalid, lane);
-                    else if (d.level == 8) values_quant<D, G, 8>(sm, st, blk, z, d.nvalid, lane);
-                    else if (d.level == 4) values_quant<D, G, 4>(sm, st, blk, z, d.nvalid, lane);
-                    else values_quant<D, G, 2>(sm, st, blk, z, d.nvalid, lane);
-                }
+                if (d.level == 1) centroid_block(sm, st, blk, d.nvalid, lane);
+                else if (d.level == 16) bf16_block(sm, st, blk, d.nvalid, lane);
+                else if (d.level == 8) quant_block<D, G, 8>(sm, st, blk, d.nvalid, lane);
+                else if (d.level == 4) quant_block<D, G, 4>(sm, st, blk, d.nvalid, lane);
+                else quant_block<D, G, 2>(sm, st, blk, d.nvalid, lane);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.empty[slot]);
