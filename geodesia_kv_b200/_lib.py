@@ -41,10 +41,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    import os
+    path = Path(os.environ.get("GKV_LIBRARY", LIB_PATH))    # a differently tuned build can be swapped in
+    if path == LIB_PATH and not LIB_PATH.exists():
         from . import build as _build
         _build.build()
-    lib = C.CDLL(str(LIB_PATH))
+    lib = C.CDLL(str(path))
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError here = header and library disagree
         fn.restype, fn.argtypes = res, args

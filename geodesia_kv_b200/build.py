@@ -42,17 +42,17 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, defines: tuple = (), out: Path = LIB) -> Path:
+    if not force and not is_stale() and out == LIB:
         return LIB
     cmd = [nvcc_path(), *ARCH, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-O3", "-shared",
-           "-Xptxas", "-v" if verbose else "-O3", "-o", str(LIB), *map(str, sources())]
+           "-Xptxas", "-v" if verbose else "-O3", *[f"-D{d}" for d in defines], "-o", str(out), *map(str, sources())]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr)
-    return LIB
+    return out
 
 
 if __name__ == "__main__":

@@ -82,12 +82,17 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
     Plan pl;
     pl.mma = allow_mma && mma_shape_ok(D, group, rep) && !force_generic();
     if (pl.mma) {
-        pl.grid = 2 * kNumSM;
+        pl.grid = mma::kCtasPerSM * kNumSM;
         const long total = (long)rows * nb;
+        const int nw = mma::kConsumerWarps;              // items are whole rounds of one block per warp
         int chunk = (int)(total / ((long)pl.grid * 8));
-        chunk = (chunk / 4) * 4;
-        if (chunk < 4) chunk = 4;
-        if (chunk > 32) chunk = 32;
+        chunk = (chunk / nw) * nw;
+        if (chunk < nw) chunk = nw;
+        if (chunk > 8 * nw) chunk = 8 * nw;
+        if (const char* e = getenv("GKV_DECODE_CHUNK")) {      // tuning knob: blocks per work item
+            const int v = atoi(e);
+            if (v >= 1 && v <= 1024) chunk = v;
+        }
         pl.bps = chunk;
         pl.nsplit = nb > 0 ? (nb + chunk - 1) / chunk : 1;
         const long items = (long)rows * pl.nsplit;

@@ -38,11 +38,21 @@
 namespace gkv {
 namespace mma {
 
-constexpr int kConsumerWarps = 4;
+#ifndef GKV_NW
+#define GKV_NW 4          // consumer warps per CTA
+#endif
+#ifndef GKV_CTAS
+#define GKV_CTAS 2        // CTAs per SM
+#endif
+#ifndef GKV_RING_KB
+#define GKV_RING_KB 72    // byte ring per CTA
+#endif
+constexpr int kConsumerWarps = GKV_NW;
+constexpr int kCtasPerSM = GKV_CTAS;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;
-constexpr int kNSlot = 16;                 // descriptor slots (blocks in flight per CTA)
-constexpr uint32_t kRingBytes = 72 * 1024; // byte ring per CTA
+constexpr int kNSlot = kConsumerWarps <= 4 ? 16 : 32;   // descriptor slots (blocks in flight per CTA)
+constexpr uint32_t kRingBytes = GKV_RING_KB * 1024;
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // every wait gives up after ~1 s, flags the error, returns
 
 struct Desc {           // one block in the ring
@@ -105,6 +115,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok) : "r"(a), "r"(parity) : "memory");
         if (ok) return true;
+        if (spin > 2) __nanosleep(spin < 64 ? 32 : 256);      // back off: spinning warps steal issue slots
         if ((spin & 63u) == 63u) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
@@ -112,6 +123,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         }
     }
 }
+// Shared-memory loads by 32-bit shared address (keeps the address arithmetic in 32 bits).
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) { uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) { uint32_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -405,8 +422,8 @@ __device__ bool prepare_query(const Params& p, Smem<D, G>& sm, int row, uint32_t
         sm.sq[i] = h < p.rep ? q[i] : 0.f;
     }
     if (!consumer_sync(sm.sync_bar, phase)) return false;
-    // per-head power-of-two scale bringing max|q| into [8, 16): two heads per warp
-    for (int h = warp * 2; h < warp * 2 + 2; ++h) {
+    // per-head power-of-two scale bringing max|q| into [8, 16): one head per warp at a time
+    for (int h = warp; h < 8; h += kConsumerWarps) {
         float mx = 0.f;
         for (int d = lane; d < D; d += 32) mx = fmaxf(mx, fabsf(sm.sq[h * D + d]));
 #pragma unroll
@@ -446,7 +463,8 @@ __device__ bool prepare_query(const Params& p, Smem<D, G>& sm, int row, uint32_t
 // the unit, online-softmax update, value product of the unit.  Loops over the contraction
 // (chunks of two k-steps on the K side, 16-token k-steps on the V side) are real loops, not
 // unrolled: the fully unrolled kernel was 130 KB of code and spent most of its time waiting
-// for instruction fetches.
+// for instruction fetches.  All shared-memory operands are addressed by 32-bit shared
+// addresses built from one per-thread base plus compile-time offsets.
 template <int D, int G>
 struct Unit {
     static constexpr int U = G;          // tokens
@@ -455,18 +473,30 @@ struct Unit {
     static constexpr int ZN = G / 4;     // scores held per thread
 };
 
+template <int D, int G>
+struct Ctx {                             // per-thread constants of the consumer role
+    uint32_t qprep;                      // shared address of this lane's first prepared-query chunk (plane 0)
+    uint32_t sq;                         // shared address of the fp32 query rows
+    float f;                             // 2^-eq * log2(e) of head r
+    int r, t, lane;
+};
+
+template <int D, int G>
+__device__ __forceinline__ uint4 qchunk(const Ctx<D, G>& c, int plane, int i) {
+    return lds_v4(c.qprep + (uint32_t)(plane * Cfg<D, G>::QPLANE * 2 + i * 512));
+}
+
 // ---- q . klo for every token group of a quantised block: one n-tile whose column n is group n ----
 template <int D, int G>
-__device__ __forceinline__ void key_bias(const Smem<D, G>& sm, const uint8_t* klo, float (&bias)[4], int lane) {
+__device__ __forceinline__ void key_bias(const Ctx<D, G>& c, uint32_t klo, float (&bias)[4]) {
     using C = Cfg<D, G>;
-    const int r = lane >> 2, t = lane & 3;
-    const bool live = r < C::TG;
-    const uint4* lo4 = reinterpret_cast<const uint4*>(klo + ((live ? r : 0) * D + C::DT * t) * 2);
+    const bool live = c.r < C::TG;
+    const uint32_t lo = klo + (uint32_t)(((live ? c.r : 0) * D + C::DT * c.t) * 2);
     bias[0] = bias[1] = bias[2] = bias[3] = 0.f;
 #pragma unroll
     for (int i = 0; i < C::CH; ++i) {
-        const uint4 qh = load_qchunk(sm, 0, i, lane), ql = load_qchunk(sm, 1, i, lane);
-        uint4 b = lo4[i];
+        const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
+        uint4 b = lds_v4(lo + 16 * i);
         if (!live) b = make_uint4(0, 0, 0, 0);
         mma_f16(bias, qh.x, ql.x, qh.y, ql.y, b.x, b.y);
         mma_f16(bias, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
@@ -475,37 +505,33 @@ __device__ __forceinline__ void key_bias(const Smem<D, G>& sm, const uint8_t* kl
 
 // ---- K side of one unit of a quantised block: scores in the log2 domain ---------------------------
 template <int D, int G, int BITS>
-__device__ __forceinline__ void scores_unit(const Smem<D, G>& sm, const uint8_t* blk, int tg, const float (&bias)[4],
-                                            float (&z)[Unit<D, G>::ZN], int lane) {
+__device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, int tg, const float (&bias)[4],
+                                            float (&z)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
-    const int r = lane >> 2, t = lane & 3;
     constexpr int RB = D * BITS / 8;                     // bytes per token row
     constexpr int TB = RB / 4;                           // bytes per thread per row
-    const uint8_t* kst = blk + 2 * (kP * RB) + C::KSCALE;
     constexpr int plane = BITS == 8 ? 0 : BITS == 4 ? 2 : 4;
-    const float f = sm.sf[r];
-    const uint32_t* nat = reinterpret_cast<const uint32_t*>(kst + (tg * D + C::DT * t) * 2);
-    const uint8_t* row0 = blk + (tg * UU::U + r) * RB + t * TB;
+    const uint32_t nat = blk + (uint32_t)(2 * (kP * RB) + C::KSCALE + (tg * D + C::DT * c.t) * 2);
+    const uint32_t row0 = blk + (uint32_t)((tg * UU::U + c.r) * RB + c.t * TB);
 
     float acc[UU::NU][4];
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 #pragma unroll 1
     for (int i = 0; i < C::CH; ++i) {                   // two k-steps at a time
-        const uint4 qh = load_qchunk(sm, plane, i, lane), ql = load_qchunk(sm, plane + 1, i, lane);
+        const uint4 qh = qchunk(c, plane, i), ql = qchunk(c, plane + 1, i);
         uint32_t sp[4];                                  // step pairs of k-steps 2i and 2i+1 in this arrangement
         if (BITS == 8) {
-            const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
+            const uint4 v = lds_v4(nat + 16 * i);
             sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
         } else if (BITS == 4) {                          // s = 2x+y with x = i: words 4i+y, 4i+y+2
-            const uint4 v = *reinterpret_cast<const uint4*>(nat + 4 * i);
+            const uint4 v = lds_v4(nat + 16 * i);
             sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
             sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
         } else {                                         // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
-            const int w0 = 8 * (i >> 1) + 2 * (i & 1);
-            const uint2 va = *reinterpret_cast<const uint2*>(nat + w0);
-            const uint2 vb = *reinterpret_cast<const uint2*>(nat + w0 + 4);
+            const uint32_t w0 = nat + (uint32_t)(32 * (i >> 1) + 8 * (i & 1));
+            const uint2 va = lds_v2(w0), vb = lds_v2(w0 + 16);
             sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
             sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
         }
@@ -514,22 +540,23 @@ __device__ __forceinline__ void scores_unit(const Smem<D, G>& sm, const uint8_t*
         mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
         mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
         mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
+        const uint32_t rowi = row0 + (uint32_t)(BITS == 8 ? 8 * i : BITS == 4 ? 4 * i : 4 * (i >> 1));
+        const int sh2 = 8 * (i & 1);
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) {
-            const uint8_t* row = row0 + n * 8 * RB;
             uint32_t b0, b1, b2, b3;                     // B registers of k-steps 2i (b0,b1) and 2i+1 (b2,b3)
             if (BITS == 8) {
-                const uint2 w = *reinterpret_cast<const uint2*>(row + 8 * i);
+                const uint2 w = lds_v2(rowi + n * 8 * RB);
                 b0 = prmt(w.x, 0u, 0x4140); b1 = prmt(w.x, 0u, 0x4342);
                 b2 = prmt(w.y, 0u, 0x4140); b3 = prmt(w.y, 0u, 0x4342);
             } else if (BITS == 4) {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * i);
+                const uint32_t w = lds_u32(rowi + n * 8 * RB);
                 const uint32_t u = w << 3, v = w >> 5;
                 b0 = u & 0x00780078u; b1 = u & 0x07800780u;
                 b2 = v & 0x00780078u; b3 = v & 0x07800780u;
             } else {
                 // fields 4h..4h+3 (and +8) of the word, h = i & 1, brought to bits 8-9 / 6-7
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 * (i >> 1)) >> (8 * (i & 1));
+                const uint32_t w = lds_u32(rowi + n * 8 * RB) >> sh2;
                 const uint32_t u = w << 4;
                 b0 = (w << 8) & 0x03000300u; b1 = u & 0x00C000C0u;
                 b2 = u & 0x03000300u;        b3 = w & 0x00C000C0u;
@@ -540,139 +567,140 @@ __device__ __forceinline__ void scores_unit(const Smem<D, G>& sm, const uint8_t*
     }
     // bias of this token group for head r lives in lane 4r + tg/2, column tg & 1
     const float bsel = (tg & 1) ? bias[1] + bias[3] : bias[0] + bias[2];
-    const float bg = __shfl_sync(0xffffffffu, bsel, (lane & ~3) | (tg >> 1));
+    const float bg = __shfl_sync(0xffffffffu, bsel, (c.lane & ~3) | (tg >> 1));
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) {
-        z[2 * n + 0] = fmaf(acc[n][0] + acc[n][2], k_unscale(BITS), bg) * f;
-        z[2 * n + 1] = fmaf(acc[n][1] + acc[n][3], k_unscale(BITS), bg) * f;
+        z[2 * n + 0] = fmaf(acc[n][0] + acc[n][2], k_unscale(BITS), bg) * c.f;
+        z[2 * n + 1] = fmaf(acc[n][1] + acc[n][3], k_unscale(BITS), bg) * c.f;
     }
 }
 
 template <int D, int G>
-__device__ __forceinline__ void scores_unit_bf16(const Smem<D, G>& sm, const uint8_t* blk, int tg,
-                                                 float (&z)[Unit<D, G>::ZN], int lane) {
+__device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t blk, int tg, float (&z)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
-    const int r = lane >> 2, t = lane & 3;
-    const float f = sm.sf[r];
-    const uint8_t* row0 = blk + ((tg * UU::U + r) * D + C::DT * t) * 2;
+    const uint32_t row0 = blk + (uint32_t)(((tg * UU::U + c.r) * D + C::DT * c.t) * 2);
     float acc[UU::NU][4];
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 #pragma unroll 1
     for (int i = 0; i < C::CH; ++i) {
-        const uint4 qh = load_qchunk(sm, 6, i, lane), ql = load_qchunk(sm, 7, i, lane);
+        const uint4 qh = qchunk(c, 6, i), ql = qchunk(c, 7, i);
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) {
-            const uint4 w = *reinterpret_cast<const uint4*>(row0 + n * 8 * D * 2 + 16 * i);
+            const uint4 w = lds_v4(row0 + 16 * i + n * 8 * D * 2);
             mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w.x, w.y);
             mma_bf16(acc[n], qh.z, ql.z, qh.w, ql.w, w.z, w.w);
         }
     }
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) {
-        z[2 * n + 0] = (acc[n][0] + acc[n][2]) * f;
-        z[2 * n + 1] = (acc[n][1] + acc[n][3]) * f;
+        z[2 * n + 0] = (acc[n][0] + acc[n][2]) * c.f;
+        z[2 * n + 1] = (acc[n][1] + acc[n][3]) * c.f;
     }
 }
 
-// ---- online-softmax update of one unit -----------------------------------------------------------
-// z: scores of head r for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid tokens
-// left in this unit (>= 1).  Returns p in z.
+// ---- online-softmax update ---------------------------------------------------------------------
+// The running reference m only moves when a score exceeds it by more than kLazy (log2 domain):
+// until then weights are taken against the stale reference and may reach 2^kLazy.  That keeps
+// the accumulator rescale (one FMUL per output register) off the common path; the fp16 weight
+// operands still fit (p * 2^8 * step < 65504 for any step < 16).
+constexpr float kLazy = 4.0f;
+
 template <int D, int G>
-__device__ __forceinline__ void softmax_unit(WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel, int lane) {
+__device__ __forceinline__ float move_reference(WarpState<D, G>& st, float mx) {
     using C = Cfg<D, G>;
-    using UU = Unit<D, G>;
-    const int t = lane & 3;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < UU::ZN; ++i) {
-        const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
-        if (tok >= nrel) z[i] = -INFINITY;
-        mx = fmaxf(mx, z[i]);
-    }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float mnew = fmaxf(st.m, mx);
-    const float corr = ex2(st.m - mnew);           // 0 when st.m = -inf
-    st.m = mnew;
-    float ls = 0.f;
-#pragma unroll
-    for (int i = 0; i < UU::ZN; ++i) {
-        z[i] = ex2(z[i] - mnew);
-        ls += z[i];
-    }
-    st.l = st.l * corr + ls;
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
+    const bool need = mx > st.m + kLazy || st.m == -INFINITY;   // per head (uniform over the quad)
+    if (__any_sync(0xffffffffu, need)) {
+        const float mnew = need ? mx : st.m;
+        const float corr = ex2(st.m - mnew);          // 0 when st.m = -inf, 1 for the heads that stay
+        st.m = mnew;
+        st.l *= corr;
 #pragma unroll
         for (int n = 0; n < C::NTILE; ++n) {
             st.o[n][0] *= corr; st.o[n][1] *= corr; st.o[n][2] *= corr; st.o[n][3] *= corr;
         }
         st.ob[0] *= corr; st.ob[1] *= corr; st.ob[2] *= corr; st.ob[3] *= corr;
     }
+    return st.m;
 }
 
-// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane for every channel group cg.
+// z: scores of head r for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid tokens
+// left in this unit (>= 1).  Returns the weights in z.
+template <int D, int G>
+__device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel) {
+    using UU = Unit<D, G>;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < UU::ZN; ++i) {
+        const int tok = (i >> 1) * 8 + 2 * c.t + (i & 1);
+        if (tok >= nrel) z[i] = -INFINITY;
+        mx = fmaxf(mx, z[i]);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m = move_reference(st, mx);
+    float ls = 0.f;
+#pragma unroll
+    for (int i = 0; i < UU::ZN; ++i) {
+        z[i] = ex2(z[i] - m);
+        ls += z[i];
+    }
+    st.l += ls;
+}
+
+// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane at shared address `row` (token `tok`, even).
 template <int GV>
-__device__ __forceinline__ void scale_pairs(const uint8_t* plane, int tok, uint32_t (&out)[GV]) {
-    const uint8_t* p = plane + tok * GV * 2;           // tok is even: two rows are 4*GV contiguous bytes
+__device__ __forceinline__ void scale_pairs(uint32_t row, uint32_t (&out)[GV]) {
     if (GV == 4) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint4 v = lds_v4(row);
         out[0] = prmt(v.x, v.z, 0x5410); out[1] = prmt(v.x, v.z, 0x7632);
         out[2 % GV] = prmt(v.y, v.w, 0x5410); out[3 % GV] = prmt(v.y, v.w, 0x7632);
     } else if (GV == 2) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const uint2 v = lds_v2(row);
         out[0] = prmt(v.x, v.y, 0x5410); out[1 % GV] = prmt(v.x, v.y, 0x7632);
     } else {
-        const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
 #pragma unroll
-        for (int cg = 0; cg < GV; ++cg) out[cg] = (uint32_t)h[cg] | ((uint32_t)h[GV + cg] << 16);
+        for (int cg = 0; cg < GV; ++cg) out[cg] = lds_u16(row + 2 * cg) | (lds_u16(row + 2 * (GV + cg)) << 16);
     }
-}
-
-// Zero the halves of a token pair (tok, tok+1) that lie at or beyond nvalid.
-__device__ __forceinline__ uint32_t pair_mask(int tok, int nvalid) {
-    return tok >= nvalid ? 0u : tok + 1 >= nvalid ? 0xffffu : 0xffffffffu;
 }
 
 // ---- V side of one unit of a quantised block -------------------------------------------------------
 template <int D, int G, int BITS>
-__device__ __forceinline__ void values_unit(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int unit,
-                                            float (&pz)[Unit<D, G>::ZN], int nvalid, int lane) {
+__device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int unit,
+                                            float (&pz)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
-    const int r = lane >> 2, t = lane & 3;
     constexpr int RB = D * BITS / 8;
-    const uint8_t* vb = blk + kP * RB;
-    const uint8_t* vlo = blk + 2 * (kP * RB) + 2 * C::KSCALE;
-    const uint8_t* vst = vlo + C::VSCALE;
     constexpr int NB = C::NT * BITS;                 // bits one thread reads per token per channel group
     constexpr int POS = v_pos(BITS);                 // codes are brought to bits [POS, POS+BITS) of each half
     constexpr uint32_t MASK = (((1u << BITS) - 1u) << POS) * 0x00010001u;
     constexpr float PSCALE = (float)(256 >> POS);    // weights carry 2^(8-POS) so that every rung adds p*v*2^-16
     const __half2 lo_scale = __float2half2_rn((float)(1 << POS));
+    const int tok0 = unit * UU::U + 2 * c.t;         // first token of this thread's pair in k-step 0
+    // codes of (token tok0, channels NT*r .. of group 0); scale rows of token tok0
+    uint32_t vrow = blk + (uint32_t)(kP * RB + tok0 * RB + (C::NT * c.r * BITS) / 8);
+    uint32_t srow = blk + (uint32_t)(2 * (kP * RB) + 2 * C::KSCALE + tok0 * C::GV * 2);
+    constexpr int SUB = ((C::NT * BITS) % 8) ? 1 : 0;  // thread's field starts inside a byte (g=16, 2-bit)
+    const int subshift = SUB ? ((C::NT * c.r * BITS) & 7) : 0;
 #pragma unroll 1
-    for (int ku = 0; ku < UU::KU; ++ku) {
-        const int ta = unit * UU::U + 16 * ku + 2 * t, tb = ta + 8;   // token pairs (ta, ta+1) and (tb, tb+1)
+    for (int ku = 0; ku < UU::KU; ++ku, vrow += 16 * RB, srow += 16 * C::GV * 2) {
         uint32_t ph[2], pl[2];
         split_f16x2(pz[0] * PSCALE, pz[1] * PSCALE, ph[0], pl[0]);
         split_f16x2(pz[2] * PSCALE, pz[3] * PSCALE, ph[1], pl[1]);
 #pragma unroll
         for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];       // next k-step's weights move to the front
-        const bool ragged = nvalid < unit * UU::U + 16 * ku + 16;     // warp-uniform: a token of this k-step is masked
-        const uint32_t ma = ragged ? pair_mask(ta, nvalid) : 0xffffffffu;
-        const uint32_t mb = ragged ? pair_mask(tb, nvalid) : 0xffffffffu;
         uint32_t sa[C::GV], sb[C::GV], la[C::GV], lb[C::GV];
-        scale_pairs<C::GV>(vst, ta, sa);
-        scale_pairs<C::GV>(vst, tb, sb);
-        scale_pairs<C::GV>(vlo, ta, la);
-        scale_pairs<C::GV>(vlo, tb, lb);
+        scale_pairs<C::GV>(srow + C::VSCALE, sa);                     // vstep, tokens (ta, ta+1)
+        scale_pairs<C::GV>(srow + C::VSCALE + 8 * C::GV * 2, sb);     // vstep, tokens (tb, tb+1)
+        scale_pairs<C::GV>(srow, la);                                 // vlo
+        scale_pairs<C::GV>(srow + 8 * C::GV * 2, lb);
         // p . vlo: column n of this n-tile is channel group n
         {
             uint32_t b0 = 0, b1 = 0;
 #pragma unroll
             for (int cg = 0; cg < C::GV; ++cg)
-                if (r == cg) { b0 = la[cg] & ma; b1 = lb[cg] & mb; }
+                if (c.r == cg) { b0 = la[cg]; b1 = lb[cg]; }
             if (POS) {                                 // keep the 2^8 scale of the p . vlo accumulator
                 b0 = h2_as_u32(__hmul2(u32_as_h2(b0), lo_scale));
                 b1 = h2_as_u32(__hmul2(u32_as_h2(b1), lo_scale));
@@ -682,22 +710,20 @@ __device__ __forceinline__ void values_unit(const Smem<D, G>& sm, WarpState<D, G
 #pragma unroll
         for (int cg = 0; cg < C::GV; ++cg) {
             uint32_t a0, a1, a2, a3;
-            mul_split(ph[0], pl[0], sa[cg] & ma, a0, a1);
-            mul_split(ph[1], pl[1], sb[cg] & mb, a2, a3);
-            // codes of this thread's NT channels for the four tokens
-            const int bitoff = (G * cg + C::NT * r) * BITS;
+            mul_split(ph[0], pl[0], sa[cg], a0, a1);
+            mul_split(ph[1], pl[1], sb[cg], a2, a3);
+            // codes of this thread's NT channels for the four tokens ta, ta+1, tb, tb+1
             uint32_t x[4][(NB + 31) / 32];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int tok = (k & 2 ? tb : ta) + (k & 1);
-                const uint8_t* src = vb + tok * RB + bitoff / 8;
+                const uint32_t src = vrow + (uint32_t)(((k & 2) ? 8 : 0) * RB + (k & 1) * RB + (G * cg * BITS) / 8);
                 if (NB >= 32) {
 #pragma unroll
-                    for (int w = 0; w < (NB + 31) / 32; ++w) x[k][w] = reinterpret_cast<const uint32_t*>(src)[w];
+                    for (int w = 0; w < (NB + 31) / 32; ++w) x[k][w] = lds_u32(src + 4 * w);
                 } else if (NB == 16) {
-                    x[k][0] = *reinterpret_cast<const uint16_t*>(src);
+                    x[k][0] = lds_u16(src);
                 } else {
-                    x[k][0] = (uint32_t)(*src) >> (bitoff % 8);
+                    x[k][0] = lds_u8(src) >> subshift;
                 }
             }
 #pragma unroll
@@ -717,118 +743,138 @@ __device__ __forceinline__ void values_unit(const Smem<D, G>& sm, WarpState<D, G
 }
 
 template <int D, int G>
-__device__ __forceinline__ void values_unit_bf16(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int unit,
-                                                 float (&pz)[Unit<D, G>::ZN], int nvalid, int lane) {
+__device__ __forceinline__ void values_unit_bf16(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int unit,
+                                                 float (&pz)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
-    const int r = lane >> 2, t = lane & 3;
-    const uint8_t* vb = blk + kP * D * 2;
     constexpr float kScale = 1.52587890625e-05f;      // 2^-16: same accumulator scale as the code path
+    uint32_t vrow = blk + (uint32_t)(kP * D * 2 + ((unit * UU::U + 2 * c.t) * D + C::NT * c.r) * 2);
 #pragma unroll 1
-    for (int ku = 0; ku < UU::KU; ++ku) {
-        const int ta = unit * UU::U + 16 * ku + 2 * t, tb = ta + 8;
+    for (int ku = 0; ku < UU::KU; ++ku, vrow += 16 * D * 2) {
         uint32_t a0, a1, a2, a3;
         split_bf16x2(pz[0] * kScale, pz[1] * kScale, a0, a1);
         split_bf16x2(pz[2] * kScale, pz[3] * kScale, a2, a3);
 #pragma unroll
         for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];
-        const bool ragged = nvalid < unit * UU::U + 16 * ku + 16;
-        // rows beyond nvalid may hold anything (even NaN patterns): zero them
-        const uint32_t ma = ragged ? pair_mask(ta, nvalid) : 0xffffffffu;
-        const uint32_t mb = ragged ? pair_mask(tb, nvalid) : 0xffffffffu;
 #pragma unroll
         for (int cg = 0; cg < C::GV; ++cg) {
-            const int ch = G * cg + C::NT * r;
             uint32_t x[4][C::NT / 2];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int tok = (k & 2 ? tb : ta) + (k & 1);
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(vb + (tok * D + ch) * 2);
+                const uint32_t src = vrow + (uint32_t)((((k & 2) ? 8 : 0) + (k & 1)) * D * 2 + G * cg * 2);
 #pragma unroll
-                for (int w = 0; w < C::NT / 2; ++w) x[k][w] = src[w];
+                for (int w = 0; w < C::NT / 2; ++w) x[k][w] = lds_u32(src + 4 * w);
             }
 #pragma unroll
             for (int i = 0; i < C::NT; ++i) {
                 const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-                const uint32_t b0 = prmt(x[0][i / 2], x[1][i / 2], sel) & ma;
-                const uint32_t b1 = prmt(x[2][i / 2], x[3][i / 2], sel) & mb;
+                const uint32_t b0 = prmt(x[0][i / 2], x[1][i / 2], sel);
+                const uint32_t b1 = prmt(x[2][i / 2], x[3][i / 2], sel);
                 mma_bf16(st.o[cg * C::NT + i], a0, a1, a2, a3, b0, b1);
             }
         }
     }
 }
 
+// A block whose tail is not valid: clear what the value product would otherwise read for the
+// tokens beyond nvalid (those bytes may hold anything, even NaN patterns), so that the main
+// path needs no masks.  Scores of such tokens are forced to -inf by the softmax.
+template <int D, int G>
+__device__ __forceinline__ void clear_invalid_tail(uint8_t* blk, int level, int nvalid, int lane) {
+    using C = Cfg<D, G>;
+    if (level == 16) {
+        uint32_t* v = reinterpret_cast<uint32_t*>(blk + kP * D * 2 + nvalid * D * 2);
+        for (int i = lane; i < (kP - nvalid) * D / 2; i += 32) v[i] = 0u;
+    } else {
+        const int RB = D * level / 8;
+        uint16_t* lo = reinterpret_cast<uint16_t*>(blk + 2 * kP * RB + 2 * C::KSCALE);
+        for (int i = nvalid * C::GV + lane; i < kP * C::GV; i += 32) { lo[i] = 0; lo[C::VSCALE / 2 + i] = 0; }
+    }
+    __syncwarp();
+}
+
 // One quantised block: bias once, then its units.
 template <int D, int G, int BITS>
-__device__ __forceinline__ void quant_block(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int nvalid, int lane) {
+__device__ __forceinline__ void quant_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
     float bias[4];
-    key_bias(sm, blk + 2 * (kP * D * BITS / 8), bias, lane);
+    key_bias(c, blk + 2 * (kP * D * BITS / 8), bias);
 #pragma unroll 1
     for (int unit = 0; unit < kP / UU::U; ++unit) {
         const int nrel = nvalid - unit * UU::U;
         if (nrel <= 0) break;
         float z[UU::ZN];
-        scores_unit<D, G, BITS>(sm, blk, unit, bias, z, lane);
-        softmax_unit(st, z, nrel, lane);
-        values_unit<D, G, BITS>(sm, st, blk, unit, z, nvalid, lane);
+        scores_unit<D, G, BITS>(c, blk, unit, bias, z);
+        softmax_unit(c, st, z, nrel);
+        values_unit<D, G, BITS>(c, st, blk, unit, z);
     }
 }
 
 template <int D, int G>
-__device__ __forceinline__ void bf16_block(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk, int nvalid, int lane) {
+__device__ __forceinline__ void bf16_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid) {
     using UU = Unit<D, G>;
 #pragma unroll 1
     for (int unit = 0; unit < kP / UU::U; ++unit) {
         const int nrel = nvalid - unit * UU::U;
         if (nrel <= 0) break;
         float z[UU::ZN];
-        scores_unit_bf16(sm, blk, unit, z, lane);
-        softmax_unit(st, z, nrel, lane);
-        values_unit_bf16(sm, st, blk, unit, z, nvalid, lane);
+        scores_unit_bf16(c, blk, unit, z);
+        softmax_unit(c, st, z, nrel);
+        values_unit_bf16(c, st, blk, unit, z);
     }
 }
 
 // ---- a centroid block: one key and one value stand for nvalid tokens ------------------------------
 template <int D, int G>
-__device__ __forceinline__ void centroid_block(const Smem<D, G>& sm, WarpState<D, G>& st, const uint8_t* blk,
-                                               int nvalid, int lane) {
+__device__ __forceinline__ void centroid_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid) {
     using C = Cfg<D, G>;
-    const int r = lane >> 2, t = lane & 3;
-    const __half2* ck = reinterpret_cast<const __half2*>(blk) + (C::DT * t) / 2;
-    const float* q = sm.sq + r * D + C::DT * t;
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < C::DT / 2; ++i) {
-        const float2 k2 = __half22float2(ck[i]);
-        s = fmaf(q[2 * i], k2.x, s);
-        s = fmaf(q[2 * i + 1], k2.y, s);
+    for (int i = 0; i < C::DT / 8; ++i) {
+        const uint4 k8 = lds_v4(blk + (uint32_t)(C::DT * c.t * 2 + 16 * i));
+        const uint4 qa = lds_v4(c.sq + (uint32_t)((c.r * D + C::DT * c.t + 8 * i) * 4));
+        const uint4 qb = lds_v4(c.sq + (uint32_t)((c.r * D + C::DT * c.t + 8 * i + 4) * 4));
+        const float2 k0 = __half22float2(u32_as_h2(k8.x)), k1 = __half22float2(u32_as_h2(k8.y));
+        const float2 k2 = __half22float2(u32_as_h2(k8.z)), k3 = __half22float2(u32_as_h2(k8.w));
+        s = fmaf(__uint_as_float(qa.x), k0.x, s); s = fmaf(__uint_as_float(qa.y), k0.y, s);
+        s = fmaf(__uint_as_float(qa.z), k1.x, s); s = fmaf(__uint_as_float(qa.w), k1.y, s);
+        s = fmaf(__uint_as_float(qb.x), k2.x, s); s = fmaf(__uint_as_float(qb.y), k2.y, s);
+        s = fmaf(__uint_as_float(qb.z), k3.x, s); s = fmaf(__uint_as_float(qb.w), k3.y, s);
     }
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     const float z = s * 1.4426950408889634f;
-    const float mnew = fmaxf(st.m, z);
-    const float corr = ex2(st.m - mnew);
-    st.m = mnew;
-    const float w = ex2(z - mnew) * (float)nvalid;
-    st.l = st.l * corr + (t == 0 ? w : 0.f);
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-        for (int n = 0; n < C::NTILE; ++n) {
-            st.o[n][0] *= corr; st.o[n][1] *= corr; st.o[n][2] *= corr; st.o[n][3] *= corr;
-        }
-        st.ob[0] *= corr; st.ob[1] *= corr; st.ob[2] *= corr; st.ob[3] *= corr;
-    }
-    const __half* cv = reinterpret_cast<const __half*>(blk + D * 2);
+    const float m = move_reference(st, z);
+    const float w = ex2(z - m) * (float)nvalid;
+    if (c.t == 0) st.l += w;
     const float ws = w * 1.52587890625e-05f;
+    const uint32_t cv = blk + (uint32_t)(D * 2);
 #pragma unroll
-    for (int cg = 0; cg < C::GV; ++cg)
+    for (int cg = 0; cg < C::GV; ++cg) {
+        // this thread's output columns of group cg: channels NT*(2t) .. and NT*(2t+1) .., 2*NT contiguous halves
+        uint32_t h[C::NT];
+        const uint32_t src = cv + (uint32_t)((G * cg + C::NT * 2 * c.t) * 2);
+        if (C::NT == 2) {
+            const uint2 v = lds_v2(src);
+            h[0] = v.x; h[1 % C::NT] = v.y;
+        } else {
+#pragma unroll
+            for (int w = 0; w < C::NT / 4; ++w) {
+                const uint4 v = lds_v4(src + 16 * w);
+                h[(4 * w) % C::NT] = v.x; h[(4 * w + 1) % C::NT] = v.y; h[(4 * w + 2) % C::NT] = v.z; h[(4 * w + 3) % C::NT] = v.w;
+            }
+        }
+        // h holds 2*NT halves: first NT for column 2t, next NT for column 2t+1
 #pragma unroll
         for (int i = 0; i < C::NT; ++i) {
-            st.o[cg * C::NT + i][0] = fmaf(ws, __half2float(cv[G * cg + C::NT * (2 * t) + i]), st.o[cg * C::NT + i][0]);
-            st.o[cg * C::NT + i][1] = fmaf(ws, __half2float(cv[G * cg + C::NT * (2 * t + 1) + i]), st.o[cg * C::NT + i][1]);
+            const uint32_t w0 = h[i / 2], w1 = h[(C::NT + i) / 2];
+            const float v0 = __half2float(__ushort_as_half((uint16_t)((i & 1) ? (w0 >> 16) : (w0 & 0xffffu))));
+            const float v1 = __half2float(__ushort_as_half((uint16_t)(((C::NT + i) & 1) ? (w1 >> 16) : (w1 & 0xffffu))));
+            st.o[cg * C::NT + i][0] = fmaf(ws, v0, st.o[cg * C::NT + i][0]);
+            st.o[cg * C::NT + i][1] = fmaf(ws, v1, st.o[cg * C::NT + i][1]);
         }
+    }
 }
 
 template <int D, int G>
@@ -837,6 +883,11 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane >> 2, t = lane & 3;
     WarpState<D, G> st;
+    Ctx<D, G> c;
+    c.qprep = smem_u32(sm.qprep) + (uint32_t)lane * 16u;
+    c.sq = smem_u32(sm.sq);
+    c.r = r; c.t = t; c.lane = lane; c.f = 0.f;
+    const uint32_t ring = smem_u32(sm.ring);
     uint32_t sync_phase = 0;
     int seq = warp;
     int code = 0;                                   // non-zero: a wait gave up
@@ -851,18 +902,20 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         st.ob[0] = st.ob[1] = st.ob[2] = st.ob[3] = 0.f;
         st.m = -INFINITY;
         st.l = 0.f;
+        c.f = sm.sf[r];
 
         for (int round = 0; round < it.rounds; ++round, seq += kConsumerWarps) {
             const int slot = seq % kNSlot;
             if (!mbar_wait(&sm.full[slot], (uint32_t)(seq / kNSlot) & 1u)) { code = 4; break; }
             const Desc d = sm.desc[slot];
             if (d.level) {
-                const uint8_t* blk = sm.ring + d.off;
-                if (d.level == 1) centroid_block(sm, st, blk, d.nvalid, lane);
-                else if (d.level == 16) bf16_block(sm, st, blk, d.nvalid, lane);
-                else if (d.level == 8) quant_block<D, G, 8>(sm, st, blk, d.nvalid, lane);
-                else if (d.level == 4) quant_block<D, G, 4>(sm, st, blk, d.nvalid, lane);
-                else quant_block<D, G, 2>(sm, st, blk, d.nvalid, lane);
+                const uint32_t blk = ring + d.off;
+                if (d.nvalid < kP && d.level != 1) clear_invalid_tail<D, G>(sm.ring + d.off, d.level, d.nvalid, lane);
+                if (d.level == 1) centroid_block(c, st, blk, d.nvalid);
+                else if (d.level == 16) bf16_block(c, st, blk, d.nvalid);
+                else if (d.level == 8) quant_block<D, G, 8>(c, st, blk, d.nvalid);
+                else if (d.level == 4) quant_block<D, G, 4>(c, st, blk, d.nvalid);
+                else quant_block<D, G, 2>(c, st, blk, d.nvalid);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.empty[slot]);
@@ -927,7 +980,7 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(Params p) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int abort_flag;
     Smem<D, G> sm(smem_raw);
