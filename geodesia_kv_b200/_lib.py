@@ -23,6 +23,7 @@ SIGNATURES = {
     "gkv_decode_workspace_bytes": (_sz, [_i] * 5),
     "gkv_mixed_attn_decode": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_partial": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
+    "gkv_mixed_attn_decode_static": (_i, [_vp] * 10 + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_combine_partials": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "gkv_pack_blocks": (_i, [_vp, _vp, _i, _vp, _vp] + [_vp] * 4 + [_vp, _vp] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_demote_blocks": (_i, [_vp] * 6 + [_vp] * 4 + [_i] * 5 + [_i64, _i64, _i, _vp]),

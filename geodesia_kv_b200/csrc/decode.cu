@@ -222,6 +222,7 @@ const char* gkv_error_string(int code) {
         case GKV_E_WORKSPACE: return "workspace missing, misaligned or too small";
         case GKV_E_CUDA: return "a CUDA call failed (see gkv_last_cuda_error)";
         case GKV_E_ARG: return "an argument is out of range";
+        case GKV_E_STATIC_SCRATCH: return "problem too large for the built-in scratch of gkv_mixed_attn_decode_static";
         default: return "unknown error code";
     }
 }
@@ -259,6 +260,36 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     gkv::combine_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
+}
+
+// ---- decode without any allocation by anyone ------------------------------------------------------
+// Scratch for gkv_mixed_attn_decode_static.  It lives in the library image: every GPU that loads
+// the library carries these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[GKV_STATIC_SCRATCH_BYTES];
+
+int gkv_mixed_attn_decode_static(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
+                                 const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
+                                 const int32_t* valid, float* out, int B, int Hq, int Hkv, int D, int nb,
+                                 int block, int group, int64_t stride_bh, int meta_rows, void* stream) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || nb < 0 || Hq % Hkv != 0) return GKV_E_SHAPE;
+    const size_t need = gkv::workspace_bytes(B, Hq, Hkv, D, nb);
+    if (need > (size_t)GKV_STATIC_SCRATCH_BYTES) return GKV_E_STATIC_SCRATCH;
+    // `g_static_scratch` is only a host-side handle here; the device address has to be asked for,
+    // once per device, with that device current.
+    constexpr int kMaxDevices = 64;
+    static void* device_ptr[kMaxDevices] = {nullptr};
+    int dev = 0;
+    GKV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return GKV_E_ARG;
+    if (!device_ptr[dev]) {
+        void* ptr = nullptr;
+        GKV_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (!ptr) return GKV_E_CUDA;
+        device_ptr[dev] = ptr;
+    }
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, device_ptr[dev],
+                            (size_t)GKV_STATIC_SCRATCH_BYTES, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows,
+                            stream);
 }
 
 }  // extern "C"

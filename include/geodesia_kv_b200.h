@@ -38,6 +38,7 @@ extern "C" {
 #define GKV_E_WORKSPACE (-4) /* workspace missing, misaligned or too small                */
 #define GKV_E_CUDA (-5)      /* a CUDA call failed; see gkv_last_cuda_error()             */
 #define GKV_E_ARG (-6)       /* an argument is out of range                               */
+#define GKV_E_STATIC_SCRATCH (-7) /* gkv_mixed_attn_decode_static: problem exceeds the built-in scratch */
 
 int gkv_abi_version(void);
 const char *gkv_error_string(int code); /* host string, static storage */
@@ -81,6 +82,31 @@ int gkv_mixed_attn_decode_partial(const float *q, const uint8_t *data, const int
                                   void *workspace, size_t workspace_bytes,
                                   int B, int Hq, int Hkv, int D, int nb, int block, int group,
                                   int64_t stride_bh, int meta_rows, void *stream);
+
+/* Decode attention for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference: the reference's launcher allocates its split buffers through torch on every call.
+ * Some hosts of this library cannot do that — a serving loop that has handed all of HBM to its
+ * own pool, a plugin called from inside a region where the CUDA allocator must not be entered,
+ * a runtime without torch at all — and gkv_mixed_attn_decode still asks them for a workspace.
+ * This variant takes none: its split records and work counter live in a fixed array inside the
+ * library image (GKV_STATIC_SCRATCH_BYTES per GPU that loads the library, held until exit), and
+ * it calls no cudaMalloc, cudaFree or any allocating library routine.  Same arguments and result
+ * as gkv_mixed_attn_decode otherwise.
+ *  - Limit: gkv_decode_workspace_bytes(B, Hq, Hkv, D, nb) must not exceed
+ *    GKV_STATIC_SCRATCH_BYTES, else GKV_E_STATIC_SCRATCH is returned and nothing is launched.
+ *  - The first call on each device looks up the array's device address (one host-side runtime
+ *    query, no allocation); make that first call outside any stream capture.
+ *  - All calls on a device share the one array, which keeps the previous call's contents (the
+ *    part that must start at zero is cleared on the stream at each call).  Two calls whose
+ *    kernels can overlap on the GPU — different streams without an ordering between them —
+ *    race on it; serialise them.
+ */
+#define GKV_STATIC_SCRATCH_BYTES (8u << 20)
+int gkv_mixed_attn_decode_static(const float *q, const uint8_t *data, const int64_t *offs,
+                                 const void *klo, const void *kstep, const void *vlo, const void *vstep,
+                                 const int32_t *level, const int32_t *valid, float *out,
+                                 int B, int Hq, int Hkv, int D, int nb, int block, int group,
+                                 int64_t stride_bh, int meta_rows, void *stream);
 
 /* LSE merge of `parts` records per output row (mixed_attn.cu:171-200):
  * partials (parts, rows, D+2) fp32 -> out (rows, D) fp32, rows = B*Hq.       */
