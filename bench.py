@@ -43,7 +43,7 @@ WORKLOADS = {
                        name="profiling-sized slice of the qwen3-8b-shape workload: 2 layers, 8 seq x 16384 tok"),
     "cfg0": dict(layers=64, Hq=16, Hkv=2, D=128, B=1, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
                  name="qwen2.5-3b-shape single-sequence layer, 64 distinct layer buffers of 16384 tok"),
-    "cfg3": dict(layers=28, Hq=28, Hkv=4, D=128, B=1, T=1048576, probs=(0.02, 0.08, 0.30, 0.40, 0.20),
+    "cfg3": dict(layers=28, Hq=28, Hkv=4, D=128, B=1, T=1048576, probs=(0.02, 0.08, 0.30, 0.40, 0.20), split=True,
                  name="qwen2.5-7b-1m-shape decode attention, 28 layers, 1 seq x 1048576 tok"),
 }
 GROUP = 32
@@ -112,13 +112,43 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_layers(w, rank, device):
-    """Seeded packed caches, one per layer, built by the GPU pack kernel."""
+def build_layers(w, rank, device, world=1):
+    """Seeded packed caches, one per layer, built by the GPU pack kernel.
+
+    Independent-sequence workloads give every rank its own batch (seeded by rank).  The
+    single-sequence workload (`split`) is cut over the ranks: all ranks draw the same rungs and
+    the same K/V stream, and each keeps only its byte-balanced range of blocks."""
     import torch
     from geodesia_kv_b200.pack_layout import pack_cache
     caches = []
     nb = w["T"] // 64
+    split = bool(w.get("split")) and world > 1
     for layer in range(w["layers"]):
+        if split:
+            from geodesia_kv_b200.distributed import block_cost_bytes, split_blocks
+            level = draw_levels(1000 + layer, w["B"], w["Hkv"], nb, w["probs"])
+            cost = torch.zeros(nb, dtype=torch.int64)
+            for h in range(w["Hkv"]):
+                cost += torch.tensor(block_cost_bytes(level[0, h].tolist(), w["D"], GROUP))
+            # balance on the summed cost of the KV heads: the same cut for every head
+            bounds, acc, tot = [0], 0, int(cost.sum())
+            csum = torch.cumsum(cost, 0)
+            for r in range(1, world):
+                bounds.append(int(torch.searchsorted(csum, tot * r // world)))
+            bounds.append(nb)
+            lo, hi = bounds[rank], bounds[rank + 1]
+            gen = torch.Generator(device=device).manual_seed(1000 + layer)
+            # the whole stream is drawn (so every rank sees the same sequence) one head at a time, the slice kept
+            k = torch.empty(w["B"], w["Hkv"], (hi - lo) * 64, w["D"], device=device, dtype=torch.bfloat16)
+            v = torch.empty_like(k)
+            for h in range(w["Hkv"]):
+                kh = torch.randn(w["T"], w["D"], device=device, dtype=torch.bfloat16, generator=gen)
+                vh = torch.randn(w["T"], w["D"], device=device, dtype=torch.bfloat16, generator=gen)
+                k[0, h], v[0, h] = kh[lo * 64:hi * 64], vh[lo * 64:hi * 64]
+                del kh, vh
+            caches.append(pack_cache(k, v, level[..., lo:hi].to(device), GROUP))
+            del k, v
+            continue
         gen = torch.Generator(device=device).manual_seed(1000 + layer + 100003 * rank)
         # K ~ N(0,1) with 4 outlier channels per head scaled x8, V ~ N(0,1); one (B, Hkv) slab at a time
         k = torch.randn(w["B"], w["Hkv"], w["T"], w["D"], device=device, dtype=torch.bfloat16, generator=gen)
@@ -152,16 +182,24 @@ def run_gpu(args):
         raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
 
     w = WORKLOADS[args.workload]
-    caches = build_layers(w, rank, device)
+    caches = build_layers(w, rank, device, world)
+    split = bool(w.get("split")) and world > 1
+    if split:
+        from geodesia_kv_b200.distributed import sequence_split_decode
     L, B, Hq, D = w["layers"], w["B"], w["Hq"], w["D"]
-    gen = torch.Generator(device=device).manual_seed(5 + rank)
+    gen = torch.Generator(device=device).manual_seed(5 + (0 if split else rank))
     qs = [torch.randn(B, Hq, D, device=device, generator=gen) * D ** -0.5 for _ in range(L)]
     alg_bytes = [c.algorithmic_bytes() + 2 * 4 * B * Hq * D for c in caches]
     cache_bytes = sum(c.data.numel() for c in caches)
 
+    def attend(q, c):
+        if split:          # this rank's blocks -> (m, l, o) records -> all-gather -> local LSE merge
+            return sequence_split_decode(q, c, 0, c.nb)
+        return ext.mixed_attn_decode(q, *c.kernel_args())
+
     def step_resident():
         for c, q in zip(caches, qs):
-            ext.mixed_attn_decode(q, *c.kernel_args())
+            attend(q, c)
 
     q_host = [q.cpu().pin_memory() for q in qs]
     o_host = [torch.empty(B, Hq, D).pin_memory() for _ in range(L)]
@@ -170,7 +208,7 @@ def run_gpu(args):
     def step_e2e():
         for i, c in enumerate(caches):
             q_dev[i].copy_(q_host[i], non_blocking=True)
-            out = ext.mixed_attn_decode(q_dev[i], *c.kernel_args())
+            out = attend(q_dev[i], c)
             o_host[i].copy_(out, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -204,28 +242,29 @@ def run_gpu(args):
     ms_e2e = timed(step_e2e, args.steps)
 
     ms_step = ms_total / args.steps
-    tokens_per_step = world * B * w["T"]
+    tokens_per_step = (1 if split else world) * B * w["T"]
     value = tokens_per_step / (ms_step / 1e3)
     peak, peak_kind = measured_peak_gbs()
     launches = args.steps * L
     avg_launch_s = (ms_total / 1e3) / launches
-    bytes_per_launch = sum(alg_bytes) / L
+    bytes_per_launch = sum(alg_bytes) / L          # this rank's bytes (ranks are byte-balanced)
     achieved = bytes_per_launch / avg_launch_s / 1e9
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if split else "weak",
         "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
         "config": {"workload": w["name"], "layers": L, "q_heads": Hq, "kv_heads": w["Hkv"], "head_dim": D,
                    "sequences_per_gpu": B, "context_tokens": w["T"], "group": GROUP,
-                   "rung_mix_16_8_4_2_c": list(w["probs"]), "sharding": f"dp{world}: independent sequences, no collective",
+                   "rung_mix_16_8_4_2_c": list(w["probs"]), "sharding": (f"sp{world}: one sequence cut into byte-balanced block ranges, one all-gather of Hq*(D+2) floats per layer"
+                                if split else f"dp{world}: independent sequences, no collective"),
                    "l2": f"inputs larger than L2: {cache_bytes / 1e9:.1f} GB of packed cache per GPU, each layer read once per step"},
         "per_gpu": value / world,
         "hbm_gbs_per_gpu": achieved,
         "e2e": {"value": tokens_per_step / (ms_e2e / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": L * B * Hq * D * 4, "d2h_bytes_per_step": L * B * Hq * D * 4,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": 2 * launches,
+        "gpu_launches": (3 if split else 2) * launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "traffic": None,
                      "kernel": "decode split kernel (+ its LSE combine, timed together)",
@@ -309,7 +348,7 @@ def run_reference(args):
               f"scaled to a {w['layers']}-layer step")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * w["layers"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp64 accumulate (C oracle)",
+            "higher_is_better": True, "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "fp64 accumulate (C oracle)",
             "data": "synthetic",
             "config": {"workload": w["name"], "layers": w["layers"], "q_heads": w["Hq"], "kv_heads": w["Hkv"],
                        "head_dim": w["D"], "context_tokens": w["T"], "group": GROUP},

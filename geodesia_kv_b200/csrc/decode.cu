@@ -24,8 +24,15 @@ struct CombineParams {
     const int* status;   // when non-null and non-zero the producing kernel gave up: poison the output
 };
 
-__global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
+constexpr int kCombineThreads = 256;
+
+// One CTA per output row.  The records of a row are shared out over the 8 warps (record s goes
+// to warp s mod 8, whose lanes read it coalesced), each warp keeps a running (m, l, o) of its
+// records, and the 8 states are merged through shared memory — the same recurrence at both levels.
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams p) {
+    __shared__ float sm_m[8], sm_l[8], sm_o[8][kMaxD];
     const int orow = blockIdx.x, D = p.D;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* base;
     int64_t stride;
     if (p.rep > 0) {
@@ -37,26 +44,51 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
         stride = p.stride_s;
     }
     const float poison = (p.status && *p.status) ? __int_as_float(0x7fc00000) : 0.f;
-    float m = -INFINITY;
-    for (int s = 0; s < p.parts; ++s) m = fmaxf(m, base[s * stride]);
-    float l = 0.f;
-    for (int s = 0; s < p.parts; ++s) {
-        const float ms = base[s * stride];
-        if (ms > -INFINITY) l += base[s * stride + 1] * expf(ms - m);
-    }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float a = 0.f;
-        for (int s = 0; s < p.parts; ++s) {
-            const float ms = base[s * stride];
-            if (ms > -INFINITY) a += base[s * stride + 2 + d] * expf(ms - m);
+    constexpr int kPer = kMaxD / 32;                  // channels per lane
+    float m = -INFINITY, l = 0.f, o[kPer];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) o[i] = 0.f;
+    for (int s = warp; s < p.parts; s += 8) {
+        const float* rec = base + s * stride;
+        const float ms = rec[0];
+        if (!(ms > -INFINITY)) continue;             // empty slice (warp-uniform)
+        const float mn = fmaxf(m, ms);
+        const float a = expf(m - mn), b = expf(ms - mn);   // a = 0 while m = -inf
+        l = l * a + rec[1] * b;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) o[i] = o[i] * a + rec[2 + d] * b;
         }
+        m = mn;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) sm_o[warp][d] = o[i];
+    }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) M = fmaxf(M, sm_m[w]);
+    float L = 0.f, wgt[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        wgt[w] = (sm_m[w] > -INFINITY) ? expf(sm_m[w] - M) : 0.f;
+        L += sm_l[w] * wgt[w];
+    }
+    for (int d = threadIdx.x; d < D; d += kCombineThreads) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) a += sm_o[w][d] * wgt[w];
         a += poison;
-        if (p.normalise) p.out[(size_t)orow * D + d] = a / fmaxf(l, 1e-20f);
+        if (p.normalise) p.out[(size_t)orow * D + d] = a / fmaxf(L, 1e-20f);
         else p.out[(size_t)orow * (D + 2) + 2 + d] = a;
     }
     if (!p.normalise && threadIdx.x == 0) {
-        p.out[(size_t)orow * (D + 2) + 0] = m;
-        p.out[(size_t)orow * (D + 2) + 1] = l;
+        p.out[(size_t)orow * (D + 2) + 0] = M;
+        p.out[(size_t)orow * (D + 2) + 1] = L;
     }
 }
 
@@ -200,7 +232,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     CombineParams c;
     c.rec = records; c.out = out; c.parts = pl.nsplit; c.D = D; c.rep = rep; c.nsplit = pl.nsplit;
     c.stride_s = 0; c.normalise = normalise; c.status = pl.mma ? header + 1 : nullptr;
-    combine_kernel<<<B * Hq, 128, 0, stream>>>(c);
+    combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }
@@ -257,7 +289,7 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     gkv::CombineParams c;
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
     c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr;
-    gkv::combine_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    gkv::combine_kernel<<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }

@@ -279,6 +279,25 @@ def main() -> None:
     blob["nquant"] = np.int64(len(pk.quant))
     np.savez_compressed(HERE / "format_a.npz", seed=700, P=P, D=D, group=group, **blob)
 
+    # ---- I. a decode trajectory through Policy.attend (policies.py:602-908): rungs per step and outputs
+    P, D, group = 64, 64, 32
+    T0, steps, stride = 592, 32, 16      # T reaches every multiple of 64: the reference only refreshes the block being written
+    rng = np.random.default_rng(800)
+    bf = lambda a: torch.from_numpy(a).to(torch.bfloat16).float()           # bf16-representable inputs
+    kfull = bf(rng.standard_normal((T0 + steps * stride, D), dtype=np.float32))
+    vfull = bf(rng.standard_normal((T0 + steps * stride, D), dtype=np.float32))
+    kfull[:, rng.permutation(D)[:2]] *= 8.0
+    qall = bf(rng.standard_normal((steps, D), dtype=np.float32))
+    pol = rpol.Policy(name="geodesia", budget_bits=3.0, block=P, group=group, window=128, sinks=4, validate=False)
+    blob = {"meta": np.array([P, D, group, T0, steps, stride], np.int64), "budget": np.float64(3.0)}
+    for s in range(steps):
+        T = T0 + s * stride
+        out = pol.attend(qall[s:s + 1], kfull[:T], vfull[:T], D ** -0.5, q_offset=T - 1, hid=(0, 0, 0))
+        blob[f"level_{s}"] = pol.state[(0, 0, 0)]["level"].numpy().astype(np.int32)
+        blob[f"out_{s}"] = out.numpy()
+    blob["bits_per_value"] = np.float64(pol.report.bits_per_value)
+    np.savez_compressed(HERE / "policy_decode.npz", seed=800, **blob)
+
     for f in sorted(HERE.glob("*.npz")):
         print(f"{f.name:28s} {f.stat().st_size / 1024:8.1f} KiB")
 
