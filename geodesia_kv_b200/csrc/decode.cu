@@ -116,14 +116,13 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
     if (pl.mma) {
         pl.grid = mma::kCtasPerSM * kNumSM;
         const long total = (long)rows * nb;
-        const int nw = mma::kConsumerWarps;              // items are whole rounds of one block per warp
+        const int nw = mma::kConsumerWarps;
         int chunk = (int)(total / ((long)pl.grid * 8));
-        chunk = (chunk / nw) * nw;
         if (chunk < nw) chunk = nw;
-        if (chunk > 8 * nw) chunk = 8 * nw;
+        if (chunk > 32) chunk = 32;                      // the producer's metadata table holds 32 blocks
         if (const char* e = getenv("GKV_DECODE_CHUNK")) {      // tuning knob: blocks per work item
             const int v = atoi(e);
-            if (v >= 1 && v <= 1024) chunk = v;
+            if (v >= 1 && v <= 32) chunk = v;
         }
         pl.bps = chunk;
         pl.nsplit = nb > 0 ? (nb + chunk - 1) / chunk : 1;

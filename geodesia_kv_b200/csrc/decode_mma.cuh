@@ -65,7 +65,7 @@ struct Desc {           // one block in the ring
 struct ItemDesc {       // one work item; published before any of its blocks so that the four
     int32_t item;       // consumer warps can meet at the item start without waiting for data
     int32_t row;
-    int32_t rounds;     // every warp consumes exactly one slot per round
+    int32_t end_seq;    // the item's blocks are the stream positions up to (not including) this one
     int32_t exit;
 };
 
@@ -115,7 +115,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok) : "r"(a), "r"(parity) : "memory");
         if (ok) return true;
+#ifndef GKV_NO_BACKOFF
         if (spin > 2) __nanosleep(spin < 64 ? 32 : 256);      // back off: spinning warps steal issue slots
+#endif
         if ((spin & 63u) == 63u) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
@@ -254,18 +256,24 @@ struct Smem {
 };
 
 // ================================ producer ====================================================
+// One lane does the streaming.  Per work item all 32 lanes fetch the metadata of the item's
+// (<= 32) blocks in one coalesced pass and park it in a small shared table; lane 0 then walks
+// the table: ring allocation, slot descriptor, expect-tx and the bulk copies of the block and
+// of its four scale planes.  (An earlier version broadcast every block's metadata with warp
+// shuffles; under the consumers' shared-memory traffic those cost ~1700 cycles per block and
+// capped the whole kernel at 2.3 TB/s.)
 template <int D, int G>
 __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     const int lane = threadIdx.x & 31;
+    __shared__ uint4 meta_tab[32];            // per block of the item: src offset (64 bit), level | nvalid << 8, bytes
     uint32_t head = 0, used = 0;
     int seq_alloc = 0, seq_free = 0;
-    __shared__ uint32_t slot_bytes[kNSlot];
 
-    auto release_oldest = [&]() -> bool {
+    auto release_oldest = [&]() -> bool {     // lane 0 only
         const int s = seq_free % kNSlot;
         if (!mbar_wait(&sm.empty[s], (uint32_t)(seq_free / kNSlot) & 1u)) return false;
-        used -= slot_bytes[s];
+        used -= (uint32_t)sm.desc[s].pad;
         ++seq_free;
         return true;
     };
@@ -280,102 +288,89 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         if (!done && lane == 0) next_item = atomicAdd(p.counter, 1);   // prefetch the next item id
         const int row = done ? 0 : item / p.items_per_row;
         const int b_lo = done ? 0 : (item % p.items_per_row) * p.chunk;
-        const int nblk = done ? 0 : min(p.chunk, p.nb - b_lo);
+        const int nblk = done ? 0 : min(p.chunk, p.nb - b_lo);        // <= 32
         const int mrow = p.per_row_meta ? row : 0;
-        const int rounds = (nblk + kConsumerWarps - 1) / kConsumerWarps;
-        // the item descriptor goes out first, through its own double buffer
+        if (lane < nblk) {
+            const size_t mi = (size_t)mrow * p.nb + b_lo + lane;
+            int lv = p.level[mi];
+            const int nv = min(p.valid[mi], kP);
+            if (!level_ok(lv) || nv <= 0) lv = 0;
+            const unsigned long long src = (unsigned long long)row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[mi];
+            const bool quant = lv == 8 || lv == 4 || lv == 2;
+            const uint32_t bytes = (lv ? 2u * (uint32_t)half_bytes(lv, D) : 0u) + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u);
+            meta_tab[lane] = make_uint4((uint32_t)src, (uint32_t)(src >> 32), (uint32_t)lv | ((uint32_t)max(nv, 0) << 8), bytes);
+        }
+        __syncwarp();
         if (lane == 0) {
+            // the item descriptor goes out first, through its own double buffer
             const int ib = iseq & 1;
             if (iseq >= 2) ok = mbar_wait(&sm.item_empty[ib], (uint32_t)((iseq >> 1) - 1) & 1u);
             if (ok) {
                 ItemDesc it;
-                it.item = item; it.row = row; it.rounds = rounds; it.exit = done ? 1 : 0;
+                it.item = item; it.row = row; it.end_seq = seq_alloc + nblk; it.exit = done ? 1 : 0;
                 sm.item[ib] = it;
                 mbar_arrive(&sm.item_full[ib]);
             }
-        }
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok || done) break;
-        // metadata of up to 32 blocks at a time, one per lane
-        for (int base = 0; base < rounds * kConsumerWarps && ok; base += 32) {
-            int lv = 0, nv = 0;
-            int64_t off = 0;
-            const int k = base + lane;
-            if (k < nblk) {
-                const size_t mi = (size_t)mrow * p.nb + b_lo + k;
-                lv = p.level[mi];
-                nv = min(p.valid[mi], kP);
-                off = p.offs[mi];
-                if (!level_ok(lv) || nv <= 0) lv = 0;
-            }
-            const int cnt = min(32, rounds * kConsumerWarps - base);
-            for (int j = 0; j < cnt && ok; ++j) {
-                const int lvj = __shfl_sync(0xffffffffu, lv, j);
-                const int nvj = __shfl_sync(0xffffffffu, nv, j);
-                const int64_t offj = __shfl_sync(0xffffffffu, off, j);
-                const int kk = base + j;
-                const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
-                const uint32_t dbytes = lvj ? 2u * (uint32_t)half_bytes(lvj, D) : 0u;
-                const uint32_t sbytes = quant ? 2u * (C::KSCALE + C::VSCALE) : 0u;
-                const uint32_t need = (dbytes + sbytes + 127u) & ~127u;
+            const size_t sb0 = (size_t)row * p.nb + b_lo;
+            uint4 e = meta_tab[0];
+            for (int j = 0; j < nblk && ok; ++j) {
+                const uint4 cur = e;
+                if (j + 1 < nblk) e = meta_tab[j + 1];
+                const int lvj = (int)(cur.z & 0xffu), nvj = (int)(cur.z >> 8);
+                const uint32_t bytes = cur.w;
+                const uint32_t need = (bytes + 127u) & ~127u;
                 const int slot = seq_alloc % kNSlot;
-                uint32_t dst = 0;
-                if (lane == 0) {
-                    while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
-                    const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
-                    while (ok && used + waste + need > kRingBytes) ok = release_oldest();
-                    dst = waste ? 0u : head;
-                    used += waste + need;
-                    head = dst + need;
-                    if (head >= kRingBytes) head = 0;
-                    slot_bytes[slot] = waste + need;
-                }
-                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
+                const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
+                while (ok && used + waste + need > kRingBytes) ok = release_oldest();
                 if (!ok) break;
-                dst = __shfl_sync(0xffffffffu, dst, 0);
-                if (lane == 0) {
-                    Desc d;
-                    d.off = dst; d.level = lvj; d.nvalid = nvj; d.pad = 0;
-                    sm.desc[slot] = d;
-                }
+                const uint32_t dst = waste ? 0u : head;
+                used += waste + need;
+                head = dst + need;
+                if (head >= kRingBytes) head = 0;
+                Desc d;
+                d.off = dst; d.level = lvj; d.nvalid = nvj; d.pad = (int32_t)(waste + need);
+                sm.desc[slot] = d;
                 if (lvj) {
-                    const size_t sb = (size_t)row * p.nb + b_lo + kk;
-                    const uint8_t* src = p.data + (size_t)row * p.stride_bh + offj;
+                    const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
+                    const uint32_t dbytes = 2u * (uint32_t)half_bytes(lvj, D);
+                    const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
                     uint8_t* d0 = sm.ring + dst;
-                    const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-                    if (aligned) {
-                        if (lane == 0) {
-                            mbar_arrive_tx(&sm.full[slot], dbytes + sbytes);
-                            bulk_g2s(d0, src, dbytes, &sm.full[slot]);
-                            if (quant) {
-                                bulk_g2s(d0 + dbytes, p.klo + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
-                                bulk_g2s(d0 + dbytes + C::KSCALE, p.kstep + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
-                                bulk_g2s(d0 + dbytes + 2 * C::KSCALE, p.vlo + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
-                                bulk_g2s(d0 + dbytes + 2 * C::KSCALE + C::VSCALE, p.vstep + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
-                            }
+                    const size_t sb = sb0 + j;
+#ifdef GKV_DBG_NOLOAD
+                    if (true) { mbar_arrive(&sm.full[slot]); } else
+#endif
+                    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                        mbar_arrive_tx(&sm.full[slot], bytes);
+                        bulk_g2s(d0, src, dbytes, &sm.full[slot]);
+                        if (quant) {
+                            bulk_g2s(d0 + dbytes, p.klo + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
+                            bulk_g2s(d0 + dbytes + C::KSCALE, p.kstep + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
+                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE, p.vlo + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
+                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE + C::VSCALE, p.vstep + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
                         }
                     } else {
-                        // block start not 16-byte aligned: the whole warp copies it by hand
-                        for (uint32_t i = lane; i < dbytes; i += 32) d0[i] = src[i];
+                        // block start not 16-byte aligned (a cache row at an odd address): bulk copies
+                        // cannot be used; this lane copies the block by hand, scale planes by bulk copy
+                        for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
+                        __threadfence_block();
+                        mbar_arrive_tx(&sm.full[slot], bytes - dbytes);    // the slot's single arrival
                         if (quant) {
-                            const uint16_t* s0 = reinterpret_cast<const uint16_t*>(p.klo + sb * (C::KSCALE / 2));
-                            const uint16_t* s1 = reinterpret_cast<const uint16_t*>(p.kstep + sb * (C::KSCALE / 2));
-                            const uint16_t* s2 = reinterpret_cast<const uint16_t*>(p.vlo + sb * (C::VSCALE / 2));
-                            const uint16_t* s3 = reinterpret_cast<const uint16_t*>(p.vstep + sb * (C::VSCALE / 2));
-                            uint16_t* o = reinterpret_cast<uint16_t*>(d0 + dbytes);
-                            for (int i = lane; i < C::KSCALE / 2; i += 32) { o[i] = s0[i]; o[C::KSCALE / 2 + i] = s1[i]; }
-                            o += C::KSCALE;
-                            for (int i = lane; i < C::VSCALE / 2; i += 32) { o[i] = s2[i]; o[C::VSCALE / 2 + i] = s3[i]; }
+                            bulk_g2s(d0 + dbytes, p.klo + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
+                            bulk_g2s(d0 + dbytes + C::KSCALE, p.kstep + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
+                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE, p.vlo + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
+                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE + C::VSCALE, p.vstep + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
                         }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&sm.full[slot]);
                     }
-                } else if (lane == 0) {
+                } else {
                     mbar_arrive(&sm.full[slot]);
                 }
                 ++seq_alloc;
             }
         }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        seq_alloc = __shfl_sync(0xffffffffu, seq_alloc, 0);
+        if (!ok || done) break;
         item = __shfl_sync(0xffffffffu, next_item, 0);
     }
     if (!ok && lane == 0) {
@@ -878,7 +873,7 @@ __device__ __forceinline__ void centroid_block(const Ctx<D, G>& c, WarpState<D, 
 }
 
 template <int D, int G>
-__device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
+__device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag, int* next_seq) {
     using C = Cfg<D, G>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane >> 2, t = lane & 3;
@@ -889,14 +884,23 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     c.r = r; c.t = t; c.lane = lane; c.f = 0.f;
     const uint32_t ring = smem_u32(sm.ring);
     uint32_t sync_phase = 0;
-    int seq = warp;
+    // Blocks are taken from the stream dynamically: whichever warp is free grabs the next
+    // position (block sizes span 64x, a fixed round-robin left warps idle at every item end).
+    auto grab = [&]() -> int {
+        int v = 0;
+        if (lane == 0) v = atomicAdd(next_seq, 1);
+        return __shfl_sync(0xffffffffu, v, 0);
+    };
+    int seq = grab();
     int code = 0;                                   // non-zero: a wait gave up
     for (int iseq = 0; code == 0; ++iseq) {
         const int ib = iseq & 1;
         if (!mbar_wait(&sm.item_full[ib], (uint32_t)(iseq >> 1) & 1u)) { code = 2; break; }
         const ItemDesc it = sm.item[ib];
         if (it.exit) return;
+#ifndef GKV_DBG_NOITEM
         if (!prepare_query(p, sm, it.row, sync_phase)) { code = 3; break; }
+#endif
 #pragma unroll
         for (int n = 0; n < C::NTILE; ++n) st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.f;
         st.ob[0] = st.ob[1] = st.ob[2] = st.ob[3] = 0.f;
@@ -904,11 +908,15 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         st.l = 0.f;
         c.f = sm.sf[r];
 
-        for (int round = 0; round < it.rounds; ++round, seq += kConsumerWarps) {
+        for (; seq < it.end_seq; seq = grab()) {
             const int slot = seq % kNSlot;
             if (!mbar_wait(&sm.full[slot], (uint32_t)(seq / kNSlot) & 1u)) { code = 4; break; }
             const Desc d = sm.desc[slot];
+#ifdef GKV_DBG_NOCOMPUTE
+            if (false) {
+#else
             if (d.level) {
+#endif
                 const uint32_t blk = ring + d.off;
                 if (d.nvalid < kP && d.level != 1) clear_invalid_tail<D, G>(sm.ring + d.off, d.level, d.nvalid, lane);
                 if (d.level == 1) centroid_block(c, st, blk, d.nvalid);
@@ -922,6 +930,10 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         }
         if (code) break;
 
+#ifdef GKV_DBG_NOITEM
+        if (tid == 0) mbar_arrive(&sm.item_empty[ib]);
+        continue;
+#endif
         // ---- merge the four warp states of this item and write its record ----------------------
         float l = st.l;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -982,10 +994,11 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    __shared__ int abort_flag;
+    __shared__ int abort_flag, next_seq;
     Smem<D, G> sm(smem_raw);
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        next_seq = 0;
         for (int s = 0; s < kNSlot; ++s) {
             mbar_init(&sm.full[s], 1);
             mbar_init(&sm.empty[s], 1);
@@ -999,7 +1012,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params
     }
     __syncthreads();
     if (threadIdx.x >= kConsumers) producer_loop<D, G>(p, sm, &abort_flag);
-    else consumer_loop<D, G>(p, sm, &abort_flag);
+    else consumer_loop<D, G>(p, sm, &abort_flag, &next_seq);
 }
 
 }  // namespace mma
