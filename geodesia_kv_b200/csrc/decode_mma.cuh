@@ -266,7 +266,7 @@ template <int D, int G>
 __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     const int lane = threadIdx.x & 31;
-    __shared__ uint4 meta_tab[32];            // per block of the item: src offset (64 bit), level | nvalid << 8, bytes
+    __shared__ uint4 meta_tab[32];            // per block of the item: src offset (64 bit), level | nvalid << 8 | index << 16, bytes
     uint32_t head = 0, used = 0;
     int seq_alloc = 0, seq_free = 0;
 
@@ -290,15 +290,33 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         const int b_lo = done ? 0 : (item % p.items_per_row) * p.chunk;
         const int nblk = done ? 0 : min(p.chunk, p.nb - b_lo);        // <= 32
         const int mrow = p.per_row_meta ? row : 0;
-        if (lane < nblk) {
-            const size_t mi = (size_t)mrow * p.nb + b_lo + lane;
-            int lv = p.level[mi];
-            const int nv = min(p.valid[mi], kP);
-            if (!level_ok(lv) || nv <= 0) lv = 0;
-            const unsigned long long src = (unsigned long long)row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[mi];
-            const bool quant = lv == 8 || lv == 4 || lv == 2;
-            const uint32_t bytes = (lv ? 2u * (uint32_t)half_bytes(lv, D) : 0u) + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u);
-            meta_tab[lane] = make_uint4((uint32_t)src, (uint32_t)(src >> 32), (uint32_t)lv | ((uint32_t)max(nv, 0) << 8), bytes);
+        // Blocks of an item are streamed sorted by rung (softmax does not care about the order):
+        // the consumer warps of an SM then run the same unpack path at the same time, which
+        // keeps the instruction cache warm.
+        {
+            int lv = 0, nv = 0;
+            unsigned long long src = 0;
+            if (lane < nblk) {
+                const size_t mi = (size_t)mrow * p.nb + b_lo + lane;
+                lv = p.level[mi];
+                nv = min(p.valid[mi], kP);
+                if (!level_ok(lv) || nv <= 0) lv = 0;
+                src = (unsigned long long)row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[mi];
+            }
+            const int cls = lane >= nblk ? 6 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
+            int rank = 0;
+#pragma unroll
+            for (int c = 0; c < 6; ++c) {
+                const unsigned m = __ballot_sync(0xffffffffu, cls == c);
+                if (c < cls) rank += __popc(m);
+                else if (c == cls) rank += __popc(m & ((1u << lane) - 1u));
+            }
+            if (lane < nblk) {
+                const bool quant = lv == 8 || lv == 4 || lv == 2;
+                const uint32_t bytes = (lv ? 2u * (uint32_t)half_bytes(lv, D) : 0u) + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u);
+                meta_tab[rank] = make_uint4((uint32_t)src, (uint32_t)(src >> 32),
+                                            (uint32_t)lv | ((uint32_t)max(nv, 0) << 8) | ((uint32_t)lane << 16), bytes);
+            }
         }
         __syncwarp();
         if (lane == 0) {
@@ -316,7 +334,7 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
             for (int j = 0; j < nblk && ok; ++j) {
                 const uint4 cur = e;
                 if (j + 1 < nblk) e = meta_tab[j + 1];
-                const int lvj = (int)(cur.z & 0xffu), nvj = (int)(cur.z >> 8);
+                const int lvj = (int)(cur.z & 0xffu), nvj = (int)((cur.z >> 8) & 0xffu), orig = (int)(cur.z >> 16);
                 const uint32_t bytes = cur.w;
                 const uint32_t need = (bytes + 127u) & ~127u;
                 const int slot = seq_alloc % kNSlot;
@@ -336,7 +354,7 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
                     const uint32_t dbytes = 2u * (uint32_t)half_bytes(lvj, D);
                     const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
                     uint8_t* d0 = sm.ring + dst;
-                    const size_t sb = sb0 + j;
+                    const size_t sb = sb0 + orig;
 #ifdef GKV_DBG_NOLOAD
                     if (true) { mbar_arrive(&sm.full[slot]); } else
 #endif
