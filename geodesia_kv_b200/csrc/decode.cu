@@ -22,6 +22,8 @@ struct CombineParams {
     int64_t stride_s;    // external layout (parts, rows, D+2) when rep == 0
     int normalise;
     const int* status;   // when non-null and non-zero the producing kernel gave up: poison the output
+    int segs;            // > 1: blockIdx.y merges records [y*per_seg, (y+1)*per_seg) into record y of
+    int per_seg;         //      an external-layout (segs, rows, D+2) buffer (normalise must be 0)
 };
 
 constexpr int kCombineThreads = 256;
@@ -48,7 +50,10 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     float m = -INFINITY, l = 0.f, o[kPer];
 #pragma unroll
     for (int i = 0; i < kPer; ++i) o[i] = 0.f;
-    for (int s = warp; s < p.parts; s += 8) {
+    const int s_lo = p.segs > 1 ? (int)blockIdx.y * p.per_seg : 0;
+    const int s_hi = p.segs > 1 ? min(p.parts, s_lo + p.per_seg) : p.parts;
+    const size_t out_row = p.segs > 1 ? (size_t)blockIdx.y * gridDim.x + orow : (size_t)orow;
+    for (int s = s_lo + warp; s < s_hi; s += 8) {
         const float* rec = base + s * stride;
         const float ms = rec[0];
         if (!(ms > -INFINITY)) continue;             // empty slice (warp-uniform)
@@ -83,23 +88,27 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
 #pragma unroll
         for (int w = 0; w < 8; ++w) a += sm_o[w][d] * wgt[w];
         a += poison;
-        if (p.normalise) p.out[(size_t)orow * D + d] = a / fmaxf(L, 1e-20f);
-        else p.out[(size_t)orow * (D + 2) + 2 + d] = a;
+        if (p.normalise) p.out[out_row * D + d] = a / fmaxf(L, 1e-20f);
+        else p.out[out_row * (D + 2) + 2 + d] = a;
     }
     if (!p.normalise && threadIdx.x == 0) {
-        p.out[(size_t)orow * (D + 2) + 0] = M;
-        p.out[(size_t)orow * (D + 2) + 1] = L;
+        p.out[out_row * (D + 2) + 0] = M;
+        p.out[out_row * (D + 2) + 1] = L;
     }
 }
 
 // ---- split plan -------------------------------------------------------------------------------
 struct Plan {
-    int nsplit, bps;      // records per cache row, blocks per record
+    int nsplit, bps;      // work items per cache row, blocks per item
+    int parts;            // records per cache row and query head (the tensor-core kernel writes one per consumer warp)
+    int segs;             // > 1: the merge runs in two levels, `segs` partial merges per output row first
     bool mma;             // tensor-core kernel (persistent, work items of `bps` blocks)
     int grid;
 };
 
 constexpr size_t kHeaderBytes = 256;   // work counter + status word in front of the records
+constexpr int kCombineDirect = 64;     // up to this many records per output row one CTA merges them all
+constexpr int kCombineSegs = 32;       // above it: this many CTAs per row merge a slice each, then one merges those
 
 static bool mma_shape_ok(int D, int group, int rep) {
     return (D == 64 || D == 128) && (group == 16 || group == 32 || group == 64) && D % group == 0 && rep <= 8;
@@ -126,6 +135,8 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
         }
         pl.bps = chunk;
         pl.nsplit = nb > 0 ? (nb + chunk - 1) / chunk : 1;
+        pl.parts = pl.nsplit * mma::kConsumerWarps;
+        pl.segs = pl.parts > kCombineDirect ? kCombineSegs : 1;
         const long items = (long)rows * pl.nsplit;
         if (items < pl.grid) pl.grid = (int)(items > 0 ? items : 1);
         return pl;
@@ -136,12 +147,14 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
     if (nsplit < 1) nsplit = 1;
     pl.bps = nb > 0 ? (nb + nsplit - 1) / nsplit : 1;
     pl.nsplit = nb > 0 ? (nb + pl.bps - 1) / pl.bps : 1;
+    pl.parts = pl.nsplit;
+    pl.segs = 1;
     pl.grid = 0;
     return pl;
 }
 
 static size_t records_bytes(int B, int Hq, const Plan& pl, int D) {
-    return (size_t)B * Hq * pl.nsplit * (D + 2) * sizeof(float);
+    return (size_t)B * Hq * ((size_t)pl.parts + (pl.segs > 1 ? pl.segs : 0)) * (D + 2) * sizeof(float);
 }
 
 // Upper bound over both kernels, so the caller's buffer fits whichever is dispatched.
@@ -229,8 +242,18 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     }
 
     CombineParams c;
-    c.rec = records; c.out = out; c.parts = pl.nsplit; c.D = D; c.rep = rep; c.nsplit = pl.nsplit;
+    c.rec = records; c.out = out; c.parts = pl.parts; c.D = D; c.rep = rep; c.nsplit = pl.parts;
     c.stride_s = 0; c.normalise = normalise; c.status = pl.mma ? header + 1 : nullptr;
+    c.segs = 1; c.per_seg = 0;
+    if (pl.segs > 1) {
+        // level 1: (rows, parts, rep, D+2) -> (segs, B*Hq, D+2) behind the records
+        float* mid = records + (size_t)B * Hq * pl.parts * (D + 2);
+        c.out = mid; c.normalise = 0; c.segs = pl.segs; c.per_seg = (pl.parts + pl.segs - 1) / pl.segs;
+        combine_kernel<<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
+        GKV_LAUNCH_CHECK();
+        c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0;
+        c.stride_s = (int64_t)B * Hq * (D + 2); c.normalise = normalise; c.segs = 1; c.per_seg = 0;
+    }
     combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
@@ -287,7 +310,7 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     if (parts <= 0 || rows <= 0 || D <= 0) return GKV_E_SHAPE;
     gkv::CombineParams c;
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
-    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr;
+    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr; c.segs = 1; c.per_seg = 0;
     gkv::combine_kernel<<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;

@@ -8,14 +8,20 @@
 // memory, which is why this is mma.sync and not tcgen05 (whose operands must be staged in
 // shared memory in canonical layout at 2 B per code).
 //
-// Structure (one CTA = 4 consumer warps + 1 producer warp, two CTAs per SM, persistent):
+// Structure (one CTA = 4 consumer warps + a producer warp + a query warp, two CTAs per SM,
+// persistent):
 //   * work items are (cache row, chunk of consecutive blocks), handed out by an atomic
-//     counter; every item ends in one (m, l, o) record per query head of the row;
+//     counter; every item ends in one (m, l, o) record per consumer warp and query head;
 //   * the producer warp streams each block's bytes and its four scale planes into a byte
 //     ring in shared memory with cp.async.bulk + mbarrier (non-multicast), several blocks
-//     ahead of the consumers;
-//   * consumer warp w takes the blocks whose position in the stream is w mod 4 and runs a
-//     private online softmax over them; the four states are merged at the end of the item.
+//     ahead of the consumers, and announces every item one item early;
+//   * the query warp turns the next item's query rows into MMA A-fragment planes (double
+//     buffered), so the consumers never stop at an item boundary;
+//   * consumer warps work in pairs: a pair takes every second block of the stream and each of
+//     its warps one half of the block's tokens, with a private online softmax.  A block is
+//     therefore resident for half as long, which doubles the part of the ring that is free
+//     for copies in flight.  Nothing is merged inside the CTA: the combine kernel merges the
+//     per-warp records together with the split records.
 //
 // Arithmetic.  Integer codes are fed to the MMA as fp16 values from the LINEAR range of the
 // format: bit patterns 0..2047 (subnormals and the first binade) are worth pattern * 2^-24, so a
@@ -45,14 +51,16 @@ namespace mma {
 #define GKV_CTAS 2        // CTAs per SM
 #endif
 #ifndef GKV_RING_KB
-#define GKV_RING_KB 72    // byte ring per CTA
+#define GKV_RING_KB 71    // byte ring per CTA
 #endif
 constexpr int kConsumerWarps = GKV_NW;
 constexpr int kCtasPerSM = GKV_CTAS;
 constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = kConsumers + 32;
+constexpr int kThreads = kConsumers + 64;    // + producer warp + query warp
+static_assert(kConsumerWarps % 2 == 0, "consumer warps work in pairs");
 constexpr int kNSlot = kConsumerWarps <= 4 ? 16 : 32;   // descriptor slots (blocks in flight per CTA)
 constexpr uint32_t kRingBytes = GKV_RING_KB * 1024;
+constexpr int kItemSlots = 4;           // item descriptors in flight: finishing, current, announced, spare
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // every wait gives up after ~1 s, flags the error, returns
 
 struct Desc {           // one block in the ring
@@ -62,8 +70,8 @@ struct Desc {           // one block in the ring
     int32_t pad;
 };
 
-struct ItemDesc {       // one work item; published before any of its blocks so that the four
-    int32_t item;       // consumer warps can meet at the item start without waiting for data
+struct ItemDesc {       // one work item; published one item ahead of its blocks (ring of kItemSlots)
+    int32_t item;
     int32_t row;
     int32_t end_seq;    // the item's blocks are the stream positions up to (not including) this one
     int32_t exit;
@@ -79,7 +87,7 @@ struct Params {
     const __half* vstep;
     const int32_t* level;
     const int32_t* valid;
-    float* part;        // (items, rep, D+2)
+    float* part;        // (items, consumer warps, rep, D+2)
     int* counter;       // work-item counter (zeroed before launch)
     int* status;        // error word (zeroed before launch)
     int B, Hq, Hkv, nb, rep;
@@ -134,6 +142,14 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t a) { uint4 v; asm volatile("ld.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// Arrives on the barrier (without adding to its expected count) when all earlier cp.async of this thread have landed.
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -218,9 +234,10 @@ struct Cfg {
     static constexpr int QPLANE = CH * 32 * 8;
     // planes: 0/1 arr8 hi/lo, 2/3 arr4 hi/lo, 4/5 arr2 hi/lo, 6/7 bf16 hi/lo
     static constexpr int QPREP_BYTES = 8 * QPLANE * 2;
-    static constexpr int STAGE_FLOATS = kConsumerWarps * 8 * (D + 2);
-    static constexpr size_t SMEM = kRingBytes + QPREP_BYTES + 8 * D * 4 + 64 + STAGE_FLOATS * 4 +
-                                   kNSlot * sizeof(Desc) + 2 * kNSlot * 8 + 2 * sizeof(ItemDesc) + 5 * 8 + 64;
+    static constexpr int SQ_BYTES = 8 * D * 4;
+    static constexpr size_t SMEM = kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
+                                   kNSlot * sizeof(Desc) + 2 * kNSlot * 8 + kItemSlots * sizeof(ItemDesc) +
+                                   (2 * kItemSlots + 2) * 8 + 64;
     static_assert(D % 32 == 0 && (G == 16 || G == 32 || G == 64) && D % G == 0, "unsupported shape");
 };
 
@@ -228,30 +245,28 @@ template <int D, int G>
 struct Smem {
     using C = Cfg<D, G>;
     uint8_t* ring;
-    __half* qprep;
-    float* sq;        // [8][D] raw query (fp32, softmax scale included)
-    float* sf;        // [8] per-head factor 2^-eq * log2(e); [8..16) unused
-    float* stage;
+    __half* qprep;         // [2] prepared-query planes (item parity)
+    float* sq;             // [2][8][D] raw query (fp32, softmax scale included)
+    float* sf;             // [2][16]: per-head factor 2^-eq * log2(e), then 2^eq
     Desc* desc;
     uint64_t* full;
     uint64_t* empty;
-    ItemDesc* item;        // [2]
-    uint64_t* item_full;   // [2]
-    uint64_t* item_empty;  // [2]
-    uint64_t* sync_bar;    // consumer rendezvous (4 arrivals: one per warp)
+    ItemDesc* item;        // [kItemSlots]
+    uint64_t* item_full;   // [kItemSlots] producer -> query warp and consumers
+    uint64_t* item_empty;  // [kItemSlots] one arrival per consumer warp that finished the item
+    uint64_t* qready;      // [2] query warp -> consumers
     __device__ explicit Smem(uint8_t* base) {
         ring = base;
         qprep = reinterpret_cast<__half*>(base + kRingBytes);
-        sq = reinterpret_cast<float*>(base + kRingBytes + C::QPREP_BYTES);
-        sf = sq + 8 * D;
-        stage = sf + 16;
-        desc = reinterpret_cast<Desc*>(stage + C::STAGE_FLOATS);
+        sq = reinterpret_cast<float*>(base + kRingBytes + 2 * C::QPREP_BYTES);
+        sf = sq + 2 * 8 * D;
+        desc = reinterpret_cast<Desc*>(sf + 32);
         full = reinterpret_cast<uint64_t*>(desc + kNSlot);
         empty = full + kNSlot;
         item_full = empty + kNSlot;
-        item_empty = item_full + 2;
-        sync_bar = item_empty + 2;
-        item = reinterpret_cast<ItemDesc*>(sync_bar + 1);
+        item_empty = item_full + kItemSlots;
+        qready = item_empty + kItemSlots;
+        item = reinterpret_cast<ItemDesc*>(qready + 2);
     }
 };
 
@@ -262,13 +277,26 @@ struct Smem {
 // of its four scale planes.  (An earlier version broadcast every block's metadata with warp
 // shuffles; under the consumers' shared-memory traffic those cost ~1700 cycles per block and
 // capped the whole kernel at 2.3 TB/s.)
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+#ifndef GKV_L2_AHEAD
+#define GKV_L2_AHEAD 0
+#endif
+constexpr int kL2Ahead = GKV_L2_AHEAD;       // blocks of look-ahead of the L2 prefetch (0: none)
+
 template <int D, int G>
 __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     const int lane = threadIdx.x & 31;
-    __shared__ uint4 meta_tab[32];            // per block of the item: src offset (64 bit), level | nvalid << 8 | index << 16, bytes
+    // per block of an item: src offset (64 bit), level | nvalid << 8 | index << 16, bytes; two items
+    __shared__ uint4 meta_tab[2][32];
     uint32_t head = 0, used = 0;
     int seq_alloc = 0, seq_free = 0;
+#ifdef GKV_DBG_TIMING
+    long long p_all = clock64(), p_wait = 0, p_issue = 0, p_meta = 0, p_scale = 0, p_n = 0;
+#endif
 
     auto release_oldest = [&]() -> bool {     // lane 0 only
         const int s = seq_free % kNSlot;
@@ -277,120 +305,202 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         ++seq_free;
         return true;
     };
+    struct Span { int row, b_lo, nblk; };
+    auto span_of = [&](int it) -> Span {
+        if (it >= p.items) return Span{0, 0, 0};
+        const int b_lo = (it % p.items_per_row) * p.chunk;
+        return Span{it / p.items_per_row, b_lo, min(p.chunk, p.nb - b_lo)};     // nblk <= 32
+    };
+    // All lanes: metadata of an item's blocks into a table, sorted by rung (softmax does not care
+    // about the order): the consumer warps of an SM then run the same unpack path at the same
+    // time, which keeps the instruction cache warm.
+    auto build_table = [&](uint4* tab, const Span& sp) {
+        int lv = 0, nv = 0;
+        unsigned long long src = 0;
+        if (lane < sp.nblk) {
+            const size_t mi = (size_t)(p.per_row_meta ? sp.row : 0) * p.nb + sp.b_lo + lane;
+            lv = p.level[mi];
+            nv = min(p.valid[mi], kP);
+            if (!level_ok(lv) || nv <= 0) lv = 0;
+            src = (unsigned long long)sp.row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[mi];
+        }
+        const int cls = lane >= sp.nblk ? 6 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
+        int rank = 0;
+#pragma unroll
+        for (int c = 0; c < 6; ++c) {
+            const unsigned m = __ballot_sync(0xffffffffu, cls == c);
+            if (c < cls) rank += __popc(m);
+            else if (c == cls) rank += __popc(m & ((1u << lane) - 1u));
+        }
+        if (lane < sp.nblk) {
+            const bool quant = lv == 8 || lv == 4 || lv == 2;
+            const uint32_t bytes = (lv ? 2u * (uint32_t)half_bytes(lv, D) : 0u) + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u);
+            tab[rank] = make_uint4((uint32_t)src, (uint32_t)(src >> 32),
+                                   (uint32_t)lv | ((uint32_t)max(nv, 0) << 8) | ((uint32_t)lane << 16), bytes);
+        }
+    };
+    // Lane 0: ask for a block's bytes to be brought into L2 ahead of its bulk copy (build-time
+    // option, off by default: it helped while the consumers stalled at item boundaries, and
+    // costs a few percent now that they do not).
+    auto prefetch_block = [&](const uint4& e) {
+        const int lv = (int)(e.z & 0xffu);
+        if (!lv) return;
+        const uint8_t* src = p.data + (((unsigned long long)e.y << 32) | e.x);
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) l2_prefetch(src, 2u * (uint32_t)half_bytes(lv, D));
+    };
 
-    int item = 0;
-    if (lane == 0) item = atomicAdd(p.counter, 1);
+    // Lane 0: announce item number j of this CTA (its descriptor slot is free once the consumers
+    // finished item j - kItemSlots, long ago in practice).
+    auto announce = [&](int j, int id, const Span& sp, int end_seq) -> bool {
+        const int s = j % kItemSlots;
+        if (j >= kItemSlots && !mbar_wait(&sm.item_empty[s], (uint32_t)(j / kItemSlots - 1) & 1u)) return false;
+        ItemDesc it;
+        it.item = id; it.row = sp.row; it.end_seq = end_seq; it.exit = id >= p.items ? 1 : 0;
+        sm.item[s] = it;
+        mbar_arrive(&sm.item_full[s]);
+        return true;
+    };
+
+    int item = 0, next_item = 0;
+    if (lane == 0) { item = atomicAdd(p.counter, 1); next_item = atomicAdd(p.counter, 1); }
     item = __shfl_sync(0xffffffffu, item, 0);
+    next_item = __shfl_sync(0xffffffffu, next_item, 0);
+    build_table(meta_tab[0], span_of(item));
     bool ok = true;
+    if (lane == 0) ok = announce(0, item, span_of(item), span_of(item).nblk);
     for (int iseq = 0; ok; ++iseq) {
         const bool done = item >= p.items;
-        int next_item = 0;
-        if (!done && lane == 0) next_item = atomicAdd(p.counter, 1);   // prefetch the next item id
-        const int row = done ? 0 : item / p.items_per_row;
-        const int b_lo = done ? 0 : (item % p.items_per_row) * p.chunk;
-        const int nblk = done ? 0 : min(p.chunk, p.nb - b_lo);        // <= 32
-        const int mrow = p.per_row_meta ? row : 0;
-        // Blocks of an item are streamed sorted by rung (softmax does not care about the order):
-        // the consumer warps of an SM then run the same unpack path at the same time, which
-        // keeps the instruction cache warm.
-        {
-            int lv = 0, nv = 0;
-            unsigned long long src = 0;
-            if (lane < nblk) {
-                const size_t mi = (size_t)mrow * p.nb + b_lo + lane;
-                lv = p.level[mi];
-                nv = min(p.valid[mi], kP);
-                if (!level_ok(lv) || nv <= 0) lv = 0;
-                src = (unsigned long long)row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[mi];
-            }
-            const int cls = lane >= nblk ? 6 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
-            int rank = 0;
-#pragma unroll
-            for (int c = 0; c < 6; ++c) {
-                const unsigned m = __ballot_sync(0xffffffffu, cls == c);
-                if (c < cls) rank += __popc(m);
-                else if (c == cls) rank += __popc(m & ((1u << lane) - 1u));
-            }
-            if (lane < nblk) {
-                const bool quant = lv == 8 || lv == 4 || lv == 2;
-                const uint32_t bytes = (lv ? 2u * (uint32_t)half_bytes(lv, D) : 0u) + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u);
-                meta_tab[rank] = make_uint4((uint32_t)src, (uint32_t)(src >> 32),
-                                            (uint32_t)lv | ((uint32_t)max(nv, 0) << 8) | ((uint32_t)lane << 16), bytes);
-            }
-        }
+        int next2 = 0;
+#ifdef GKV_DBG_TIMING
+        const long long _pm0 = clock64();
+#endif
+        if (!done && lane == 0) next2 = atomicAdd(p.counter, 1);       // item id two ahead
+        const Span cs = span_of(item), ns = done ? Span{0, 0, 0} : span_of(next_item);
+        const int row = cs.row, b_lo = cs.b_lo, nblk = cs.nblk;
+        uint4* tab = meta_tab[iseq & 1];
+        uint4* ntab = meta_tab[(iseq + 1) & 1];
+        build_table(ntab, ns);
         __syncwarp();
         if (lane == 0) {
-            // the item descriptor goes out first, through its own double buffer
-            const int ib = iseq & 1;
-            if (iseq >= 2) ok = mbar_wait(&sm.item_empty[ib], (uint32_t)((iseq >> 1) - 1) & 1u);
-            if (ok) {
-                ItemDesc it;
-                it.item = item; it.row = row; it.end_seq = seq_alloc + nblk; it.exit = done ? 1 : 0;
-                sm.item[ib] = it;
-                mbar_arrive(&sm.item_full[ib]);
+            // the next item goes out now, a whole item early: the query warp needs the time
+            if (!done) ok = announce(iseq + 1, next_item, ns, seq_alloc + nblk + ns.nblk);
+            if (kL2Ahead > 0 && ns.nblk) {      // scale planes of the whole next item -> L2
+                const size_t nb0 = (size_t)ns.row * p.nb + ns.b_lo;
+                l2_prefetch(p.klo + nb0 * (C::KSCALE / 2), (uint32_t)ns.nblk * C::KSCALE);
+                l2_prefetch(p.kstep + nb0 * (C::KSCALE / 2), (uint32_t)ns.nblk * C::KSCALE);
+                l2_prefetch(p.vlo + nb0 * (C::VSCALE / 2), (uint32_t)ns.nblk * C::VSCALE);
+                l2_prefetch(p.vstep + nb0 * (C::VSCALE / 2), (uint32_t)ns.nblk * C::VSCALE);
             }
-            const size_t sb0 = (size_t)row * p.nb + b_lo;
-            uint4 e = meta_tab[0];
-            for (int j = 0; j < nblk && ok; ++j) {
-                const uint4 cur = e;
-                if (j + 1 < nblk) e = meta_tab[j + 1];
-                const int lvj = (int)(cur.z & 0xffu), nvj = (int)((cur.z >> 8) & 0xffu), orig = (int)(cur.z >> 16);
-                const uint32_t bytes = cur.w;
-                const uint32_t need = (bytes + 127u) & ~127u;
-                const int slot = seq_alloc % kNSlot;
+            if (iseq == 0)
+                for (int j = 0; j < kL2Ahead && j < nblk; ++j) prefetch_block(tab[j]);
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        // The block loop runs on all lanes: lane 0 waits for room, allocates and starts the bulk
+        // copy of the block's bytes; the four scale planes (a few hundred bytes each) are then
+        // fetched by all 32 lanes with 16-byte asynchronous copies that report to the same
+        // barrier.  (Five bulk copies per block from one lane cost ~600 cycles of issue time per
+        // block and made the producer the slowest stage.)
+        const size_t sb0 = (size_t)row * p.nb + b_lo;
+#ifdef GKV_DBG_TIMING
+        p_meta += clock64() - _pm0;
+#endif
+        for (int j = 0; j < nblk && ok; ++j, ++seq_alloc) {
+            const uint4 cur = tab[j];
+            const int lvj = (int)(cur.z & 0xffu), nvj = (int)((cur.z >> 8) & 0xffu), orig = (int)(cur.z >> 16);
+            const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
+            const uint32_t dbytes = lvj ? 2u * (uint32_t)half_bytes(lvj, D) : 0u;
+            const int slot = seq_alloc % kNSlot;
+            uint32_t res = 0;                                   // lane 0: ring offset | 1 << 31
+            if (lane == 0) {
+                if (kL2Ahead > 0) {
+                    const int ja = j + kL2Ahead;
+                    if (ja < nblk) prefetch_block(tab[ja]);
+                    else if (ja - nblk < ns.nblk) prefetch_block(ntab[ja - nblk]);
+                }
+                const uint32_t need = (cur.w + 127u) & ~127u;
+#ifdef GKV_DBG_TIMING
+                const long long _pw0 = clock64();
+#endif
                 while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
                 const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
                 while (ok && used + waste + need > kRingBytes) ok = release_oldest();
-                if (!ok) break;
-                const uint32_t dst = waste ? 0u : head;
-                used += waste + need;
-                head = dst + need;
-                if (head >= kRingBytes) head = 0;
-                Desc d;
-                d.off = dst; d.level = lvj; d.nvalid = nvj; d.pad = (int32_t)(waste + need);
-                sm.desc[slot] = d;
-                if (lvj) {
-                    const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
-                    const uint32_t dbytes = 2u * (uint32_t)half_bytes(lvj, D);
+#ifdef GKV_DBG_TIMING
+                const long long _pi0 = clock64();
+                p_wait += _pi0 - _pw0; ++p_n;
+#endif
+                if (ok) {
+                    const uint32_t dst = waste ? 0u : head;
+                    used += waste + need;
+                    head = dst + need;
+                    if (head >= kRingBytes) head = 0;
+                    Desc d;
+                    d.off = dst; d.level = lvj; d.nvalid = nvj; d.pad = (int32_t)(waste + need);
+                    sm.desc[slot] = d;
                     const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
                     uint8_t* d0 = sm.ring + dst;
-                    const size_t sb = sb0 + orig;
 #ifdef GKV_DBG_NOLOAD
                     if (true) { mbar_arrive(&sm.full[slot]); } else
 #endif
-                    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                        mbar_arrive_tx(&sm.full[slot], bytes);
+                    if (lvj && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                        mbar_arrive_tx(&sm.full[slot], dbytes);
                         bulk_g2s(d0, src, dbytes, &sm.full[slot]);
-                        if (quant) {
-                            bulk_g2s(d0 + dbytes, p.klo + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
-                            bulk_g2s(d0 + dbytes + C::KSCALE, p.kstep + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
-                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE, p.vlo + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
-                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE + C::VSCALE, p.vstep + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
-                        }
                     } else {
-                        // block start not 16-byte aligned (a cache row at an odd address): bulk copies
-                        // cannot be used; this lane copies the block by hand, scale planes by bulk copy
+                        // block start not 16-byte aligned (a cache row at an odd address): no bulk copy,
+                        // this lane copies the bytes by hand
                         for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
                         __threadfence_block();
-                        mbar_arrive_tx(&sm.full[slot], bytes - dbytes);    // the slot's single arrival
-                        if (quant) {
-                            bulk_g2s(d0 + dbytes, p.klo + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
-                            bulk_g2s(d0 + dbytes + C::KSCALE, p.kstep + sb * (C::KSCALE / 2), C::KSCALE, &sm.full[slot]);
-                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE, p.vlo + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
-                            bulk_g2s(d0 + dbytes + 2 * C::KSCALE + C::VSCALE, p.vstep + sb * (C::VSCALE / 2), C::VSCALE, &sm.full[slot]);
-                        }
+                        mbar_arrive(&sm.full[slot]);
                     }
-                } else {
-                    mbar_arrive(&sm.full[slot]);
+                    res = dst | 0x80000000u;
                 }
-                ++seq_alloc;
+#ifdef GKV_DBG_TIMING
+                p_issue += clock64() - _pi0;
+#endif
             }
+#ifdef GKV_DBG_TIMING
+            const long long _ps0 = clock64();
+#endif
+            res = __shfl_sync(0xffffffffu, res, 0);
+            if (!(res >> 31)) { ok = false; break; }
+#ifndef GKV_DBG_NOLOAD
+            if (quant) {
+                const uint32_t sdst = smem_u32(sm.ring) + (res & 0x7fffffffu) + dbytes;
+                const size_t sb = sb0 + orig;
+                const uint8_t* klo = reinterpret_cast<const uint8_t*>(p.klo) + sb * C::KSCALE;
+                const uint8_t* kst = reinterpret_cast<const uint8_t*>(p.kstep) + sb * C::KSCALE;
+                const uint8_t* vlo = reinterpret_cast<const uint8_t*>(p.vlo) + sb * C::VSCALE;
+                const uint8_t* vst = reinterpret_cast<const uint8_t*>(p.vstep) + sb * C::VSCALE;
+                constexpr int K = C::KSCALE, V = C::VSCALE;
+#pragma unroll
+                for (int o0 = 0; o0 < 2 * (K + V); o0 += 512) {
+                    const int o = o0 + lane * 16;
+                    if (o < 2 * (K + V)) {
+                        const uint8_t* src = o < K ? klo + o : o < 2 * K ? kst + (o - K) : o < 2 * K + V ? vlo + (o - 2 * K) : vst + (o - 2 * K - V);
+                        cp_async16(sdst + (uint32_t)o, src);
+                    }
+                }
+            }
+#endif
+            cp_async_arrive(&sm.full[slot]);                    // one arrival per lane once its copies have landed
+#ifdef GKV_DBG_TIMING
+            p_scale += clock64() - _ps0;
+#endif
         }
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        seq_alloc = __shfl_sync(0xffffffffu, seq_alloc, 0);
         if (!ok || done) break;
-        item = __shfl_sync(0xffffffffu, next_item, 0);
+        item = next_item;
+        next_item = __shfl_sync(0xffffffffu, next2, 0);
     }
+#ifdef GKV_DBG_TIMING
+    if (lane == 0) {
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.counter) + 4;
+        atomicAdd(dbg + 0, (unsigned long long)(clock64() - p_all));
+        atomicAdd(dbg + 1, (unsigned long long)p_wait);
+        atomicAdd(dbg + 2, (unsigned long long)p_issue);
+        atomicAdd(dbg + 3, (unsigned long long)p_meta);
+        atomicAdd(dbg + 4, (unsigned long long)p_scale);
+        atomicAdd(dbg + 5, (unsigned long long)p_n);
+    }
+#endif
     if (!ok && lane == 0) {
         atomicExch(p.status, 1);
         atomicExch(abort_flag, 1);
@@ -407,69 +517,71 @@ struct WarpState {
     float l;              // this thread's share of the running sum
 };
 
-// Prepared-query fragment loader: plane pl, returns the 4 registers of chunk i (k-steps 2i, 2i+1).
+// ================================ query warp ==================================================
+// For every announced item: the row's query heads as fp32 (for the centroid path), a per-head
+// power-of-two scale, and the MMA A-fragment planes of every channel arrangement, into the
+// buffer of the item's parity.  Runs one item ahead of the consumers.
 template <int D, int G>
-__device__ __forceinline__ uint4 load_qchunk(const Smem<D, G>& sm, int plane, int i, int lane) {
+__device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
-    return *reinterpret_cast<const uint4*>(sm.qprep + (size_t)plane * C::QPLANE + ((size_t)i * 32 + lane) * 8);
-}
-
-// Rendezvous of the four consumer warps on an mbarrier (bounded, unlike bar.sync).
-__device__ __forceinline__ bool consumer_sync(uint64_t* bar, uint32_t& phase) {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
-    const bool ok = mbar_wait(bar, phase);
-    phase ^= 1u;
-    return ok;
-}
-
-// Build the prepared query planes for the current row (all 128 consumer threads).
-template <int D, int G>
-__device__ bool prepare_query(const Params& p, Smem<D, G>& sm, int row, uint32_t& phase) {
-    using C = Cfg<D, G>;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b = row / p.Hkv, hk = row % p.Hkv;
-    const float* q = p.q + ((size_t)b * p.Hq + (size_t)hk * p.rep) * D;
-    for (int i = tid; i < 8 * D; i += kConsumers) {
-        const int h = i / D;
-        sm.sq[i] = h < p.rep ? q[i] : 0.f;
-    }
-    if (!consumer_sync(sm.sync_bar, phase)) return false;
-    // per-head power-of-two scale bringing max|q| into [8, 16): one head per warp at a time
-    for (int h = warp; h < 8; h += kConsumerWarps) {
-        float mx = 0.f;
-        for (int d = lane; d < D; d += 32) mx = fmaxf(mx, fabsf(sm.sq[h * D + d]));
+    const int lane = threadIdx.x & 31;
+    int code = 0;
+    for (int j = 0;; ++j) {
+        const int s = j % kItemSlots, ib = j & 1;
+        if (!mbar_wait(&sm.item_full[s], (uint32_t)(j / kItemSlots) & 1u)) { code = 7; break; }
+        const ItemDesc it = sm.item[s];
+        if (it.exit) return;
+        // the buffer was last used by item j-2: wait until every consumer warp has left it
+        if (j >= 2 && !mbar_wait(&sm.item_empty[(j - 2) % kItemSlots], (uint32_t)((j - 2) / kItemSlots) & 1u)) { code = 8; break; }
+        float* sq = sm.sq + ib * 8 * D;
+        float* sf = sm.sf + ib * 16;
+        __half* qp = sm.qprep + (size_t)ib * (C::QPREP_BYTES / 2);
+        const int b = it.row / p.Hkv, hk = it.row % p.Hkv;
+        const float* q = p.q + ((size_t)b * p.Hq + (size_t)hk * p.rep) * D;
+        for (int i = lane; i < 8 * D; i += 32) sq[i] = (i / D) < p.rep ? q[i] : 0.f;
+        __syncwarp();
+        // per-head power-of-two scale bringing max|q| into [8, 16)
+        for (int h = 0; h < 8; ++h) {
+            float mx = 0.f;
+            for (int d = lane; d < D; d += 32) mx = fmaxf(mx, fabsf(sq[h * D + d]));
 #pragma unroll
-        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        int eq = 0;
-        if (mx > 0.f && mx < INFINITY) eq = 3 - ilogbf(mx);
-        eq = max(-100, min(100, eq));
-        if (lane == 0) {
-            sm.sf[h] = ldexpf(1.4426950408889634f, -eq);
-            sm.sf[8 + h] = ldexpf(1.0f, eq);
+            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            int eq = 0;
+            if (mx > 0.f && mx < INFINITY) eq = 3 - ilogbf(mx);
+            eq = max(-100, min(100, eq));
+            if (lane == 0) {
+                sf[h] = ldexpf(1.4426950408889634f, -eq);
+                sf[8 + h] = ldexpf(1.0f, eq);
+            }
         }
-    }
-    if (!consumer_sync(sm.sync_bar, phase)) return false;
-    // every thread fills entries (chunk i, lane l, half j) of each plane
-    for (int idx = tid; idx < C::CH * 32 * 8; idx += kConsumers) {
-        const int j = idx & 7, l = (idx >> 3) & 31, i = idx >> 8;
-        const int r = l >> 2, t = l & 3;
-        const int s = 2 * i + (j >> 2), e = j & 3;
-        const float sc = sm.sf[8 + r];
+        __syncwarp();
+        // entries (chunk i, lane l, half jj) of each plane
+        for (int idx = lane; idx < C::CH * 32 * 8; idx += 32) {
+            const int jj = idx & 7, l = (idx >> 3) & 31, i = idx >> 8;
+            const int r = l >> 2, t = l & 3;
+            const int ks = 2 * i + (jj >> 2), e = jj & 3;
+            const float sc = sf[8 + r];
+            const float* qr = sq + r * D + C::DT * t;
 #pragma unroll
-        for (int a = 0; a < 3; ++a) {
-            const int bits = a == 0 ? 8 : a == 1 ? 4 : 2;
-            const float x = sm.sq[r * D + C::DT * t + arr_chan(bits, s, e)] * sc * arr_scale(bits, e);
-            const __half h = __float2half_rn(x);
-            sm.qprep[(2 * a) * C::QPLANE + idx] = h;
-            sm.qprep[(2 * a + 1) * C::QPLANE + idx] = __float2half_rn(x - __half2float(h));
+            for (int a = 0; a < 3; ++a) {
+                const int bits = a == 0 ? 8 : a == 1 ? 4 : 2;
+                const float x = qr[arr_chan(bits, ks, e)] * sc * arr_scale(bits, e);
+                const __half h = __float2half_rn(x);
+                qp[(2 * a) * C::QPLANE + idx] = h;
+                qp[(2 * a + 1) * C::QPLANE + idx] = __float2half_rn(x - __half2float(h));
+            }
+            const float x = qr[arr_chan(16, ks, e)] * sc;
+            const __nv_bfloat16 hb = __float2bfloat16_rn(x);
+            reinterpret_cast<__nv_bfloat16*>(qp)[6 * C::QPLANE + idx] = hb;
+            reinterpret_cast<__nv_bfloat16*>(qp)[7 * C::QPLANE + idx] = __float2bfloat16_rn(x - __bfloat162float(hb));
         }
-        const float x = sm.sq[r * D + C::DT * t + arr_chan(16, s, e)] * sc;
-        const __nv_bfloat16 hb = __float2bfloat16_rn(x);
-        reinterpret_cast<__nv_bfloat16*>(sm.qprep)[6 * C::QPLANE + idx] = hb;
-        reinterpret_cast<__nv_bfloat16*>(sm.qprep)[7 * C::QPLANE + idx] = __float2bfloat16_rn(x - __bfloat162float(hb));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.qready[ib]);
     }
-    return consumer_sync(sm.sync_bar, phase);
+    if (lane == 0) {
+        atomicExch(p.status, code);
+        atomicExch(abort_flag, 1);
+    }
 }
 
 // The blocks are processed in UNITS of G tokens (one token group of the K scales): scores of
@@ -506,14 +618,16 @@ __device__ __forceinline__ void key_bias(const Ctx<D, G>& c, uint32_t klo, float
     const bool live = c.r < C::TG;
     const uint32_t lo = klo + (uint32_t)(((live ? c.r : 0) * D + C::DT * c.t) * 2);
     bias[0] = bias[1] = bias[2] = bias[3] = 0.f;
+    float bias2[4] = {0.f, 0.f, 0.f, 0.f};            // second chain: back-to-back MMAs into one accumulator serialise
 #pragma unroll
     for (int i = 0; i < C::CH; ++i) {
         const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
         uint4 b = lds_v4(lo + 16 * i);
         if (!live) b = make_uint4(0, 0, 0, 0);
         mma_f16(bias, qh.x, ql.x, qh.y, ql.y, b.x, b.y);
-        mma_f16(bias, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
+        mma_f16(bias2, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
     }
+    bias[0] += bias2[0]; bias[1] += bias2[1]; bias[2] += bias2[2]; bias[3] += bias2[3];
 }
 
 // ---- K side of one unit of a quantised block: scores in the log2 domain ---------------------------
@@ -555,28 +669,31 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
         mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
         const uint32_t rowi = row0 + (uint32_t)(BITS == 8 ? 8 * i : BITS == 4 ? 4 * i : 4 * (i >> 1));
         const int sh2 = 8 * (i & 1);
+        uint32_t bb[UU::NU][4];                          // B registers of k-steps 2i (0,1) and 2i+1 (2,3)
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) {
-            uint32_t b0, b1, b2, b3;                     // B registers of k-steps 2i (b0,b1) and 2i+1 (b2,b3)
             if (BITS == 8) {
                 const uint2 w = lds_v2(rowi + n * 8 * RB);
-                b0 = prmt(w.x, 0u, 0x4140); b1 = prmt(w.x, 0u, 0x4342);
-                b2 = prmt(w.y, 0u, 0x4140); b3 = prmt(w.y, 0u, 0x4342);
+                bb[n][0] = prmt(w.x, 0u, 0x4140); bb[n][1] = prmt(w.x, 0u, 0x4342);
+                bb[n][2] = prmt(w.y, 0u, 0x4140); bb[n][3] = prmt(w.y, 0u, 0x4342);
             } else if (BITS == 4) {
                 const uint32_t w = lds_u32(rowi + n * 8 * RB);
                 const uint32_t u = w << 3, v = w >> 5;
-                b0 = u & 0x00780078u; b1 = u & 0x07800780u;
-                b2 = v & 0x00780078u; b3 = v & 0x07800780u;
+                bb[n][0] = u & 0x00780078u; bb[n][1] = u & 0x07800780u;
+                bb[n][2] = v & 0x00780078u; bb[n][3] = v & 0x07800780u;
             } else {
                 // fields 4h..4h+3 (and +8) of the word, h = i & 1, brought to bits 8-9 / 6-7
                 const uint32_t w = lds_u32(rowi + n * 8 * RB) >> sh2;
                 const uint32_t u = w << 4;
-                b0 = (w << 8) & 0x03000300u; b1 = u & 0x00C000C0u;
-                b2 = u & 0x03000300u;        b3 = w & 0x00C000C0u;
+                bb[n][0] = (w << 8) & 0x03000300u; bb[n][1] = u & 0x00C000C0u;
+                bb[n][2] = u & 0x03000300u;        bb[n][3] = w & 0x00C000C0u;
             }
-            mma_f16(acc[n], a[0], a[1], a[2], a[3], b0, b1);
-            mma_f16(acc[n], a[4], a[5], a[6], a[7], b2, b3);
         }
+        // k-step major: the two MMAs of an n-tile are NU issues apart, which hides the MMA latency
+#pragma unroll
+        for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[0], a[1], a[2], a[3], bb[n][0], bb[n][1]);
+#pragma unroll
+        for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[4], a[5], a[6], a[7], bb[n][2], bb[n][3]);
     }
     // bias of this token group for head r lives in lane 4r + tg/2, column tg & 1
     const float bsel = (tg & 1) ? bias[1] + bias[3] : bias[0] + bias[2];
@@ -599,12 +716,13 @@ __device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t bl
 #pragma unroll 1
     for (int i = 0; i < C::CH; ++i) {
         const uint4 qh = qchunk(c, 6, i), ql = qchunk(c, 7, i);
+        uint4 w[UU::NU];
 #pragma unroll
-        for (int n = 0; n < UU::NU; ++n) {
-            const uint4 w = lds_v4(row0 + 16 * i + n * 8 * D * 2);
-            mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w.x, w.y);
-            mma_bf16(acc[n], qh.z, ql.z, qh.w, ql.w, w.z, w.w);
-        }
+        for (int n = 0; n < UU::NU; ++n) w[n] = lds_v4(row0 + 16 * i + n * 8 * D * 2);
+#pragma unroll
+        for (int n = 0; n < UU::NU; ++n) mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w[n].x, w[n].y);
+#pragma unroll
+        for (int n = 0; n < UU::NU; ++n) mma_bf16(acc[n], qh.z, ql.z, qh.w, ql.w, w[n].z, w[n].w);
     }
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) {
@@ -806,29 +924,38 @@ __device__ __forceinline__ void clear_invalid_tail(uint8_t* blk, int level, int 
     __syncwarp();
 }
 
-// One quantised block: bias once, then its units.
+// One quantised block, units [u0, u1): bias once, then the units.
 template <int D, int G, int BITS>
-__device__ __forceinline__ void quant_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid) {
+__device__ __forceinline__ void quant_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid, int u0, int u1) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
+    if (u1 <= u0 || nvalid <= u0 * UU::U) return;
     float bias[4];
     key_bias(c, blk + 2 * (kP * D * BITS / 8), bias);
 #pragma unroll 1
-    for (int unit = 0; unit < kP / UU::U; ++unit) {
+    for (int unit = u0; unit < u1; ++unit) {
         const int nrel = nvalid - unit * UU::U;
         if (nrel <= 0) break;
         float z[UU::ZN];
+#ifdef GKV_DBG_NOK
+        for (int i = 0; i < UU::ZN; ++i) z[i] = bias[0] + (float)i;
+#else
         scores_unit<D, G, BITS>(c, blk, unit, bias, z);
+#endif
         softmax_unit(c, st, z, nrel);
+#ifndef GKV_DBG_NOV
         values_unit<D, G, BITS>(c, st, blk, unit, z);
+#else
+        st.l += z[0];
+#endif
     }
 }
 
 template <int D, int G>
-__device__ __forceinline__ void bf16_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid) {
+__device__ __forceinline__ void bf16_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid, int u0, int u1) {
     using UU = Unit<D, G>;
 #pragma unroll 1
-    for (int unit = 0; unit < kP / UU::U; ++unit) {
+    for (int unit = u0; unit < u1; ++unit) {
         const int nrel = nvalid - unit * UU::U;
         if (nrel <= 0) break;
         float z[UU::ZN];
@@ -891,116 +1018,124 @@ __device__ __forceinline__ void centroid_block(const Ctx<D, G>& c, WarpState<D, 
 }
 
 template <int D, int G>
-__device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag, int* next_seq) {
+__device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane >> 2, t = lane & 3;
     WarpState<D, G> st;
     Ctx<D, G> c;
-    c.qprep = smem_u32(sm.qprep) + (uint32_t)lane * 16u;
-    c.sq = smem_u32(sm.sq);
     c.r = r; c.t = t; c.lane = lane; c.f = 0.f;
     const uint32_t ring = smem_u32(sm.ring);
-    uint32_t sync_phase = 0;
-    // Blocks are taken from the stream dynamically: whichever warp is free grabs the next
-    // position (block sizes span 64x, a fixed round-robin left warps idle at every item end).
-    auto grab = [&]() -> int {
-        int v = 0;
-        if (lane == 0) v = atomicAdd(next_seq, 1);
-        return __shfl_sync(0xffffffffu, v, 0);
-    };
-    int seq = grab();
+    // A pair of warps takes every (kConsumerWarps/2)-th block of the stream; inside the block the
+    // two warps share out the units of G tokens (a block with a single unit goes to the first).
+    constexpr int kPairs = kConsumerWarps / 2;
+    constexpr int UPB = kP / UU::U;                 // units per block
+    const int pair = warp >> 1, half = warp & 1;
+    const int u0 = UPB >= 2 ? half * (UPB / 2) : 0;
+    const int u1 = UPB >= 2 ? u0 + UPB / 2 : (half == 0 ? 1 : 0);
+    int seq = pair;
     int code = 0;                                   // non-zero: a wait gave up
-    for (int iseq = 0; code == 0; ++iseq) {
-        const int ib = iseq & 1;
-        if (!mbar_wait(&sm.item_full[ib], (uint32_t)(iseq >> 1) & 1u)) { code = 2; break; }
-        const ItemDesc it = sm.item[ib];
-        if (it.exit) return;
-#ifndef GKV_DBG_NOITEM
-        if (!prepare_query(p, sm, it.row, sync_phase)) { code = 3; break; }
+#ifdef GKV_DBG_TIMING
+    long long c_all = clock64(), c_wait = 0, c_comp = 0, c_item = 0, c_n = 0;
 #endif
+    for (int iseq = 0; code == 0; ++iseq) {
+        const int is = iseq % kItemSlots, ib = iseq & 1;
+#ifdef GKV_DBG_TIMING
+        long long _ci0 = clock64();
+#endif
+        if (!mbar_wait(&sm.item_full[is], (uint32_t)(iseq / kItemSlots) & 1u)) { code = 2; break; }
+        const ItemDesc it = sm.item[is];
+        if (it.exit) {
+#ifdef GKV_DBG_TIMING
+            if (lane == 0) {
+                unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.counter) + 12;
+                atomicAdd(dbg + 0, (unsigned long long)(clock64() - c_all));
+                atomicAdd(dbg + 1, (unsigned long long)c_wait);
+                atomicAdd(dbg + 2, (unsigned long long)c_comp);
+                atomicAdd(dbg + 3, (unsigned long long)c_item);
+                atomicAdd(dbg + 4, (unsigned long long)c_n);
+            }
+#endif
+            return;
+        }
+        if (!mbar_wait(&sm.qready[ib], (uint32_t)(iseq >> 1) & 1u)) { code = 3; break; }
+        c.qprep = smem_u32(sm.qprep) + (uint32_t)(ib * C::QPREP_BYTES) + (uint32_t)lane * 16u;
+        c.sq = smem_u32(sm.sq) + (uint32_t)(ib * C::SQ_BYTES);
+        c.f = sm.sf[ib * 16 + r];
 #pragma unroll
         for (int n = 0; n < C::NTILE; ++n) st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.f;
         st.ob[0] = st.ob[1] = st.ob[2] = st.ob[3] = 0.f;
         st.m = -INFINITY;
         st.l = 0.f;
-        c.f = sm.sf[r];
+#ifdef GKV_DBG_TIMING
+        c_item += clock64() - _ci0;
+#endif
 
-        for (; seq < it.end_seq; seq = grab()) {
+        for (; seq < it.end_seq; seq += kPairs) {
             const int slot = seq % kNSlot;
+#ifdef GKV_DBG_TIMING
+            long long _cw0 = clock64();
+#endif
             if (!mbar_wait(&sm.full[slot], (uint32_t)(seq / kNSlot) & 1u)) { code = 4; break; }
             const Desc d = sm.desc[slot];
+#ifdef GKV_DBG_TIMING
+            { const long long now = clock64(); c_wait += now - _cw0; _cw0 = now; ++c_n; }
+#endif
 #ifdef GKV_DBG_NOCOMPUTE
             if (false) {
 #else
             if (d.level) {
 #endif
                 const uint32_t blk = ring + d.off;
-                if (d.nvalid < kP && d.level != 1) clear_invalid_tail<D, G>(sm.ring + d.off, d.level, d.nvalid, lane);
-                if (d.level == 1) centroid_block(c, st, blk, d.nvalid);
-                else if (d.level == 16) bf16_block(c, st, blk, d.nvalid);
-                else if (d.level == 8) quant_block<D, G, 8>(c, st, blk, d.nvalid);
-                else if (d.level == 4) quant_block<D, G, 4>(c, st, blk, d.nvalid);
-                else quant_block<D, G, 2>(c, st, blk, d.nvalid);
+                if (d.level == 1) {
+                    if (half == 0) centroid_block(c, st, blk, d.nvalid);
+                } else {
+                    // both warps of the pair clear the tail (same zeros, so the overlap is harmless)
+                    if (d.nvalid < kP) clear_invalid_tail<D, G>(sm.ring + d.off, d.level, d.nvalid, lane);
+                    if (d.level == 16) bf16_block(c, st, blk, d.nvalid, u0, u1);
+                    else if (d.level == 8) quant_block<D, G, 8>(c, st, blk, d.nvalid, u0, u1);
+                    else if (d.level == 4) quant_block<D, G, 4>(c, st, blk, d.nvalid, u0, u1);
+                    else quant_block<D, G, 2>(c, st, blk, d.nvalid, u0, u1);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.empty[slot]);
+#ifdef GKV_DBG_TIMING
+            c_comp += clock64() - _cw0;
+#endif
         }
         if (code) break;
-
-#ifdef GKV_DBG_NOITEM
-        if (tid == 0) mbar_arrive(&sm.item_empty[ib]);
-        continue;
+#ifdef GKV_DBG_TIMING
+        _ci0 = clock64();
 #endif
-        // ---- merge the four warp states of this item and write its record ----------------------
+        // ---- this warp's record of the item (natural-log domain, like the generic kernel's) ----
         float l = st.l;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        float* mine = sm.stage + (size_t)warp * 8 * (D + 2) + (size_t)r * (D + 2);
-        if (t == 0) { mine[0] = st.m; mine[1] = l; }
+        float* rec = p.part + (((size_t)it.item * kConsumerWarps + warp) * p.rep + r) * (D + 2);
+        const bool live = r < p.rep;
+        if (live && t == 0) { rec[0] = st.m * 0.6931471805599453f; rec[1] = l; }
         // p . vlo of channel group cg sits in lane 4r + cg/2, column cg & 1, scaled 2^8
         const float ob_even = st.ob[0] + st.ob[2], ob_odd = st.ob[1] + st.ob[3];
 #pragma unroll
         for (int cg = 0; cg < C::GV; ++cg) {
             const float src = (cg & 1) ? ob_odd : ob_even;
             const float bias = __shfl_sync(0xffffffffu, src, (lane & ~3) | (cg >> 1)) * 0.00390625f;
+            if (live) {
 #pragma unroll
-            for (int i = 0; i < C::NT; ++i) {
-                const int n = cg * C::NT + i;
-                mine[2 + G * cg + C::NT * (2 * t) + i] = fmaf(st.o[n][0] + st.o[n][2], 65536.f, bias);
-                mine[2 + G * cg + C::NT * (2 * t + 1) + i] = fmaf(st.o[n][1] + st.o[n][3], 65536.f, bias);
+                for (int i = 0; i < C::NT; ++i) {
+                    const int n = cg * C::NT + i;
+                    rec[2 + G * cg + C::NT * (2 * t) + i] = fmaf(st.o[n][0] + st.o[n][2], 65536.f, bias);
+                    rec[2 + G * cg + C::NT * (2 * t + 1) + i] = fmaf(st.o[n][1] + st.o[n][3], 65536.f, bias);
+                }
             }
         }
-        if (!consumer_sync(sm.sync_bar, sync_phase)) { code = 5; break; }
-        float* rec = p.part + (size_t)it.item * p.rep * (D + 2);
-        for (int h = warp; h < p.rep; h += kConsumerWarps) {
-            float mw[kConsumerWarps], mmax = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) {
-                mw[w] = sm.stage[(size_t)w * 8 * (D + 2) + (size_t)h * (D + 2)];
-                mmax = fmaxf(mmax, mw[w]);
-            }
-            float lsum = 0.f, wgt[kConsumerWarps];
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) {
-                wgt[w] = (mw[w] == -INFINITY) ? 0.f : ex2(mw[w] - mmax);
-                lsum += wgt[w] * sm.stage[(size_t)w * 8 * (D + 2) + (size_t)h * (D + 2) + 1];
-            }
-            for (int dd = lane; dd < D; dd += 32) {
-                float a = 0.f;
-#pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w)
-                    a = fmaf(wgt[w], sm.stage[(size_t)w * 8 * (D + 2) + (size_t)h * (D + 2) + 2 + dd], a);
-                rec[(size_t)h * (D + 2) + 2 + dd] = a;
-            }
-            if (lane == 0) {
-                // records are kept in the natural-log domain like the generic kernel's
-                rec[(size_t)h * (D + 2) + 0] = mmax * 0.6931471805599453f;
-                rec[(size_t)h * (D + 2) + 1] = lsum;
-            }
-        }
-        if (!consumer_sync(sm.sync_bar, sync_phase)) { code = 6; break; }
-        if (tid == 0) mbar_arrive(&sm.item_empty[ib]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.item_empty[is]);
+#ifdef GKV_DBG_TIMING
+        c_item += clock64() - _ci0;
+#endif
         if (*reinterpret_cast<volatile int*>(abort_flag)) return;
     }
     if (code && lane == 0) {
@@ -1012,25 +1147,26 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag, 
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    __shared__ int abort_flag, next_seq;
+    __shared__ int abort_flag;
     Smem<D, G> sm(smem_raw);
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        next_seq = 0;
         for (int s = 0; s < kNSlot; ++s) {
-            mbar_init(&sm.full[s], 1);
-            mbar_init(&sm.empty[s], 1);
+            mbar_init(&sm.full[s], 1 + 32);         // lane 0's arrival (+ bulk-copy bytes) and 32 scale-copy arrivals
+            mbar_init(&sm.empty[s], 2);             // the two warps of a pair
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kItemSlots; ++s) {
             mbar_init(&sm.item_full[s], 1);
-            mbar_init(&sm.item_empty[s], 1);
+            mbar_init(&sm.item_empty[s], kConsumerWarps);
         }
-        mbar_init(sm.sync_bar, kConsumerWarps);
+        mbar_init(&sm.qready[0], 1);
+        mbar_init(&sm.qready[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (threadIdx.x >= kConsumers) producer_loop<D, G>(p, sm, &abort_flag);
-    else consumer_loop<D, G>(p, sm, &abort_flag, &next_seq);
+    if (threadIdx.x < kConsumers) consumer_loop<D, G>(p, sm, &abort_flag);
+    else if (threadIdx.x < kConsumers + 32) producer_loop<D, G>(p, sm, &abort_flag);
+    else query_loop<D, G>(p, sm, &abort_flag);
 }
 
 }  // namespace mma
