@@ -157,13 +157,16 @@ static size_t records_bytes(int B, int Hq, const Plan& pl, int D) {
     return (size_t)B * Hq * ((size_t)pl.parts + (pl.segs > 1 ? pl.segs : 0)) * (D + 2) * sizeof(float);
 }
 
+// the tensor-core kernel's rung-sorted block lists: one int32 per block of every metadata row
+static size_t perm_bytes(int rows, int nb) { return (((size_t)rows * nb * sizeof(int32_t)) + 255) & ~(size_t)255; }
+
 // Upper bound over both kernels, so the caller's buffer fits whichever is dispatched.
 static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
     const int rows = B * Hkv, rep = Hq / (Hkv > 0 ? Hkv : 1);
     size_t need = records_bytes(B, Hq, make_plan(rows, nb, D, 32, rep, false), D);
     const size_t alt = records_bytes(B, Hq, make_plan(rows, nb, 128, 32, 1, true), D);
     if (alt > need) need = alt;
-    return (kHeaderBytes + need + 255) & ~(size_t)255;
+    return ((kHeaderBytes + need + 255) & ~(size_t)255) + perm_bytes(rows, nb);
 }
 
 template <int D, int G>
@@ -204,7 +207,14 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
 
     if (pl.mma) {
         GKV_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, stream));
+        // the block lists sit at the end of the workspace, behind the records of either kernel
+        int32_t* perm = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + need - perm_bytes(rows, nb));
+        int plan_threads = ((nb + 3) / 4 + 31) & ~31;           // ~4 blocks per thread
+        plan_threads = plan_threads < 32 ? 32 : plan_threads > mma::kPlanMaxThreads ? mma::kPlanMaxThreads : plan_threads;
+        mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, perm, nb);
+        GKV_LAUNCH_CHECK();
         mma::Params mp;
+        mp.perm = perm; mp.rows = rows;
         mp.q = q; mp.data = data; mp.offs = offs;
         mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
         mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);

@@ -87,13 +87,15 @@ struct Params {
     const __half* vstep;
     const int32_t* level;
     const int32_t* valid;
-    float* part;        // (items, consumer warps, rep, D+2)
+    const int32_t* perm; // (metadata rows, nb) block indices of every row sorted by rung, from plan_kernel
+    float* part;        // (rows, items per row, consumer warps, rep, D+2)
     int* counter;       // work-item counter (zeroed before launch)
     int* status;        // error word (zeroed before launch)
     int B, Hq, Hkv, nb, rep;
     int chunk;          // blocks per item
     int items_per_row, items;
     int per_row_meta;
+    int rows;
     int64_t stride_bh;
 };
 
@@ -237,7 +239,7 @@ struct Cfg {
     static constexpr int SQ_BYTES = 8 * D * 4;
     static constexpr size_t SMEM = kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
                                    kNSlot * sizeof(Desc) + 2 * kNSlot * 8 + kItemSlots * sizeof(ItemDesc) +
-                                   (2 * kItemSlots + 2) * 8 + 64;
+                                   (2 * kItemSlots + 4) * 8 + 2 * 32 * 16 + 64;
     static_assert(D % 32 == 0 && (G == 16 || G == 32 || G == 64) && D % G == 0, "unsupported shape");
 };
 
@@ -255,6 +257,8 @@ struct Smem {
     uint64_t* item_full;   // [kItemSlots] producer -> query warp and consumers
     uint64_t* item_empty;  // [kItemSlots] one arrival per consumer warp that finished the item
     uint64_t* qready;      // [2] query warp -> consumers
+    uint64_t* tab_ready;   // [2] query warp -> producer
+    uint4* meta_tab;       // [2][32] block tables of the current and the next item
     __device__ explicit Smem(uint8_t* base) {
         ring = base;
         qprep = reinterpret_cast<__half*>(base + kRingBytes);
@@ -266,32 +270,102 @@ struct Smem {
         item_full = empty + kNSlot;
         item_empty = item_full + kItemSlots;
         qready = item_empty + kItemSlots;
-        item = reinterpret_cast<ItemDesc*>(qready + 2);
+        tab_ready = qready + 2;
+        item = reinterpret_cast<ItemDesc*>(tab_ready + 2);
+        meta_tab = reinterpret_cast<uint4*>(item + kItemSlots);
     }
 };
 
 // ================================ producer ====================================================
-// One lane does the streaming.  Per work item all 32 lanes fetch the metadata of the item's
-// (<= 32) blocks in one coalesced pass and park it in a small shared table; lane 0 then walks
-// the table: ring allocation, slot descriptor, expect-tx and the bulk copies of the block and
-// of its four scale planes.  (An earlier version broadcast every block's metadata with warp
-// shuffles; under the consumers' shared-memory traffic those cost ~1700 cycles per block and
-// capped the whole kernel at 2.3 TB/s.)
-__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+// Work items are numbered chunk-major: item = chunk * rows + row, and a chunk is a run of p.chunk
+// consecutive entries of the row's rung-sorted block list.  The whole grid therefore walks the
+// ladder together — all bf16 blocks first, the centroids last: the warps that share an SM run
+// the same unpack code at the same time (with the rungs interleaved the kernel spent ~15 % of
+// its time refetching instructions), and the cheapest items come last, which trims the tail.
+struct Span { int row, b_lo, nblk; };
+__device__ __forceinline__ Span span_of(const Params& p, int it) {
+    if (it >= p.items) return Span{0, 0, 0};
+    const int b_lo = (it / p.rows) * p.chunk;
+    return Span{it % p.rows, b_lo, min(p.chunk, p.nb - b_lo)};     // nblk <= 32
 }
 
-#ifndef GKV_L2_AHEAD
-#define GKV_L2_AHEAD 0
-#endif
-constexpr int kL2Ahead = GKV_L2_AHEAD;       // blocks of look-ahead of the L2 prefetch (0: none)
+// Table of an item's blocks, one uint4 per block: source offset (64 bit), level | nvalid << 8,
+// block index in the row.  Built by a full warp in one coalesced pass over the metadata.
+template <int D, int G>
+__device__ __forceinline__ void build_table(const Params& p, uint4* tab, const Span& sp, int lane) {
+    if (lane < sp.nblk) {
+        const size_t m0 = (size_t)(p.per_row_meta ? sp.row : 0) * p.nb;
+        const int blk = p.perm[m0 + sp.b_lo + lane];
+        int lv = p.level[m0 + blk];
+        const int nv = min(p.valid[m0 + blk], kP);
+        if (!level_ok(lv) || nv <= 0) lv = 0;
+        const unsigned long long src = (unsigned long long)sp.row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[m0 + blk];
+        tab[lane] = make_uint4((uint32_t)src, (uint32_t)(src >> 32), (uint32_t)lv | ((uint32_t)max(nv, 0) << 8), (uint32_t)blk);
+    }
+}
 
+// ---- rung-sorted block lists -----------------------------------------------------------------------
+// One CTA per metadata row: a stable counting sort of the row's block indices by rung (16, 8, 4, 2,
+// centroid, then blocks with nothing to do).  Every thread owns a contiguous run of blocks, counts
+// its classes, an in-order scan over (class, thread) gives it a write cursor per class, and it
+// walks its run once more.  Deterministic: no atomics.
+constexpr int kPlanMaxThreads = 1024;
+__device__ __forceinline__ int rung_class(int lv, int nv) {
+    return nv <= 0 ? 5 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
+}
+__global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* level, const int32_t* valid, int32_t* perm, int nb) {
+    __shared__ int wsum[kPlanMaxThreads / 32][6];   // per-warp class totals, then their exclusive scan
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const int32_t* lv = level + (size_t)blockIdx.x * nb;
+    const int32_t* nv = valid + (size_t)blockIdx.x * nb;
+    int32_t* out = perm + (size_t)blockIdx.x * nb;
+    const int per = (nb + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int lo = min(nb, tid * per), hi = min(nb, lo + per);
+    int cnt[6] = {0, 0, 0, 0, 0, 0};
+    for (int b = lo; b < hi; ++b) {
+        const int c = rung_class(lv[b], nv[b]);
+#pragma unroll
+        for (int k = 0; k < 6; ++k) cnt[k] += (c == k);
+    }
+    int cur[6];                                     // exclusive prefix inside the warp
+#pragma unroll
+    for (int k = 0; k < 6; ++k) {
+        int x = cnt[k];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, x, o);
+            if (lane >= o) x += y;
+        }
+        cur[k] = x - cnt[k];
+        if (lane == 31) wsum[warp][k] = x;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int k = 0; k < 6; ++k)
+            for (int w = 0; w < nwarp; ++w) { const int t = wsum[w][k]; wsum[w][k] = run; run += t; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 6; ++k) cur[k] += wsum[warp][k];
+    for (int b = lo; b < hi; ++b) {
+        const int c = rung_class(lv[b], nv[b]);
+#pragma unroll
+        for (int k = 0; k < 6; ++k)
+            if (c == k) out[cur[k]++] = b;
+    }
+}
+
+// The producer warp announces items (one item ahead), and for every block of the current item's
+// table (built by the query warp) lane 0 waits for room in the ring, allocates, publishes the slot
+// descriptor and starts the bulk copy of the block's bytes; the four scale planes (a few hundred
+// bytes each) are then fetched by all 32 lanes with 16-byte asynchronous copies that report to the
+// same barrier.  (Five bulk copies per block from one lane cost ~600 cycles of issue time per
+// block and made the producer the slowest stage; so did building the tables here.)
 template <int D, int G>
 __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     const int lane = threadIdx.x & 31;
-    // per block of an item: src offset (64 bit), level | nvalid << 8 | index << 16, bytes; two items
-    __shared__ uint4 meta_tab[2][32];
     uint32_t head = 0, used = 0;
     int seq_alloc = 0, seq_free = 0;
 #ifdef GKV_DBG_TIMING
@@ -305,50 +379,6 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         ++seq_free;
         return true;
     };
-    struct Span { int row, b_lo, nblk; };
-    auto span_of = [&](int it) -> Span {
-        if (it >= p.items) return Span{0, 0, 0};
-        const int b_lo = (it % p.items_per_row) * p.chunk;
-        return Span{it / p.items_per_row, b_lo, min(p.chunk, p.nb - b_lo)};     // nblk <= 32
-    };
-    // All lanes: metadata of an item's blocks into a table, sorted by rung (softmax does not care
-    // about the order): the consumer warps of an SM then run the same unpack path at the same
-    // time, which keeps the instruction cache warm.
-    auto build_table = [&](uint4* tab, const Span& sp) {
-        int lv = 0, nv = 0;
-        unsigned long long src = 0;
-        if (lane < sp.nblk) {
-            const size_t mi = (size_t)(p.per_row_meta ? sp.row : 0) * p.nb + sp.b_lo + lane;
-            lv = p.level[mi];
-            nv = min(p.valid[mi], kP);
-            if (!level_ok(lv) || nv <= 0) lv = 0;
-            src = (unsigned long long)sp.row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[mi];
-        }
-        const int cls = lane >= sp.nblk ? 6 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
-        int rank = 0;
-#pragma unroll
-        for (int c = 0; c < 6; ++c) {
-            const unsigned m = __ballot_sync(0xffffffffu, cls == c);
-            if (c < cls) rank += __popc(m);
-            else if (c == cls) rank += __popc(m & ((1u << lane) - 1u));
-        }
-        if (lane < sp.nblk) {
-            const bool quant = lv == 8 || lv == 4 || lv == 2;
-            const uint32_t bytes = (lv ? 2u * (uint32_t)half_bytes(lv, D) : 0u) + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u);
-            tab[rank] = make_uint4((uint32_t)src, (uint32_t)(src >> 32),
-                                   (uint32_t)lv | ((uint32_t)max(nv, 0) << 8) | ((uint32_t)lane << 16), bytes);
-        }
-    };
-    // Lane 0: ask for a block's bytes to be brought into L2 ahead of its bulk copy (build-time
-    // option, off by default: it helped while the consumers stalled at item boundaries, and
-    // costs a few percent now that they do not).
-    auto prefetch_block = [&](const uint4& e) {
-        const int lv = (int)(e.z & 0xffu);
-        if (!lv) return;
-        const uint8_t* src = p.data + (((unsigned long long)e.y << 32) | e.x);
-        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) l2_prefetch(src, 2u * (uint32_t)half_bytes(lv, D));
-    };
-
     // Lane 0: announce item number j of this CTA (its descriptor slot is free once the consumers
     // finished item j - kItemSlots, long ago in practice).
     auto announce = [&](int j, int id, const Span& sp, int end_seq) -> bool {
@@ -365,59 +395,44 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     if (lane == 0) { item = atomicAdd(p.counter, 1); next_item = atomicAdd(p.counter, 1); }
     item = __shfl_sync(0xffffffffu, item, 0);
     next_item = __shfl_sync(0xffffffffu, next_item, 0);
-    build_table(meta_tab[0], span_of(item));
     bool ok = true;
-    if (lane == 0) ok = announce(0, item, span_of(item), span_of(item).nblk);
+    if (lane == 0) ok = announce(0, item, span_of(p, item), span_of(p, item).nblk);
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
     for (int iseq = 0; ok; ++iseq) {
         const bool done = item >= p.items;
         int next2 = 0;
 #ifdef GKV_DBG_TIMING
         const long long _pm0 = clock64();
 #endif
-        if (!done && lane == 0) next2 = atomicAdd(p.counter, 1);       // item id two ahead
-        const Span cs = span_of(item), ns = done ? Span{0, 0, 0} : span_of(next_item);
-        const int row = cs.row, b_lo = cs.b_lo, nblk = cs.nblk;
-        uint4* tab = meta_tab[iseq & 1];
-        uint4* ntab = meta_tab[(iseq + 1) & 1];
-        build_table(ntab, ns);
-        __syncwarp();
-        if (lane == 0) {
+        const Span cs = span_of(p, item), ns = done ? Span{0, 0, 0} : span_of(p, next_item);
+        const int row = cs.row, nblk = cs.nblk;
+        if (lane == 0 && !done) {
+            next2 = atomicAdd(p.counter, 1);       // item id two ahead
             // the next item goes out now, a whole item early: the query warp needs the time
-            if (!done) ok = announce(iseq + 1, next_item, ns, seq_alloc + nblk + ns.nblk);
-            if (kL2Ahead > 0 && ns.nblk) {      // scale planes of the whole next item -> L2
-                const size_t nb0 = (size_t)ns.row * p.nb + ns.b_lo;
-                l2_prefetch(p.klo + nb0 * (C::KSCALE / 2), (uint32_t)ns.nblk * C::KSCALE);
-                l2_prefetch(p.kstep + nb0 * (C::KSCALE / 2), (uint32_t)ns.nblk * C::KSCALE);
-                l2_prefetch(p.vlo + nb0 * (C::VSCALE / 2), (uint32_t)ns.nblk * C::VSCALE);
-                l2_prefetch(p.vstep + nb0 * (C::VSCALE / 2), (uint32_t)ns.nblk * C::VSCALE);
-            }
-            if (iseq == 0)
-                for (int j = 0; j < kL2Ahead && j < nblk; ++j) prefetch_block(tab[j]);
+            ok = announce(iseq + 1, next_item, ns, seq_alloc + nblk + ns.nblk);
         }
+        if (done) break;
+        // this item's table comes from the query warp
+        if (ok && !mbar_wait(&sm.tab_ready[iseq & 1], (uint32_t)(iseq >> 1) & 1u)) ok = false;
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        // The block loop runs on all lanes: lane 0 waits for room, allocates and starts the bulk
-        // copy of the block's bytes; the four scale planes (a few hundred bytes each) are then
-        // fetched by all 32 lanes with 16-byte asynchronous copies that report to the same
-        // barrier.  (Five bulk copies per block from one lane cost ~600 cycles of issue time per
-        // block and made the producer the slowest stage.)
-        const size_t sb0 = (size_t)row * p.nb + b_lo;
+        const uint4* tab = sm.meta_tab + (iseq & 1) * 32;
+        const size_t sb0 = (size_t)row * p.nb;
+        const uint8_t* klo0 = reinterpret_cast<const uint8_t*>(p.klo) + sb0 * C::KSCALE;
+        const uint8_t* kst0 = reinterpret_cast<const uint8_t*>(p.kstep) + sb0 * C::KSCALE;
+        const uint8_t* vlo0 = reinterpret_cast<const uint8_t*>(p.vlo) + sb0 * C::VSCALE;
+        const uint8_t* vst0 = reinterpret_cast<const uint8_t*>(p.vstep) + sb0 * C::VSCALE;
 #ifdef GKV_DBG_TIMING
         p_meta += clock64() - _pm0;
 #endif
         for (int j = 0; j < nblk && ok; ++j, ++seq_alloc) {
             const uint4 cur = tab[j];
-            const int lvj = (int)(cur.z & 0xffu), nvj = (int)((cur.z >> 8) & 0xffu), orig = (int)(cur.z >> 16);
+            const int lvj = (int)(cur.z & 0xffu), orig = (int)cur.w;
             const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
             const uint32_t dbytes = lvj ? 2u * (uint32_t)half_bytes(lvj, D) : 0u;
             const int slot = seq_alloc % kNSlot;
             uint32_t res = 0;                                   // lane 0: ring offset | 1 << 31
             if (lane == 0) {
-                if (kL2Ahead > 0) {
-                    const int ja = j + kL2Ahead;
-                    if (ja < nblk) prefetch_block(tab[ja]);
-                    else if (ja - nblk < ns.nblk) prefetch_block(ntab[ja - nblk]);
-                }
-                const uint32_t need = (cur.w + 127u) & ~127u;
+                const uint32_t need = (dbytes + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u) + 127u) & ~127u;
 #ifdef GKV_DBG_TIMING
                 const long long _pw0 = clock64();
 #endif
@@ -434,7 +449,7 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
                     head = dst + need;
                     if (head >= kRingBytes) head = 0;
                     Desc d;
-                    d.off = dst; d.level = lvj; d.nvalid = nvj; d.pad = (int32_t)(waste + need);
+                    d.off = dst; d.level = lvj; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)(waste + need);
                     sm.desc[slot] = d;
                     const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
                     uint8_t* d0 = sm.ring + dst;
@@ -465,17 +480,14 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
 #ifndef GKV_DBG_NOLOAD
             if (quant) {
                 const uint32_t sdst = smem_u32(sm.ring) + (res & 0x7fffffffu) + dbytes;
-                const size_t sb = sb0 + orig;
-                const uint8_t* klo = reinterpret_cast<const uint8_t*>(p.klo) + sb * C::KSCALE;
-                const uint8_t* kst = reinterpret_cast<const uint8_t*>(p.kstep) + sb * C::KSCALE;
-                const uint8_t* vlo = reinterpret_cast<const uint8_t*>(p.vlo) + sb * C::VSCALE;
-                const uint8_t* vst = reinterpret_cast<const uint8_t*>(p.vstep) + sb * C::VSCALE;
+                const size_t ko = (size_t)orig * C::KSCALE, vo = (size_t)orig * C::VSCALE;
                 constexpr int K = C::KSCALE, V = C::VSCALE;
 #pragma unroll
                 for (int o0 = 0; o0 < 2 * (K + V); o0 += 512) {
                     const int o = o0 + lane * 16;
                     if (o < 2 * (K + V)) {
-                        const uint8_t* src = o < K ? klo + o : o < 2 * K ? kst + (o - K) : o < 2 * K + V ? vlo + (o - 2 * K) : vst + (o - 2 * K - V);
+                        const uint8_t* src = o < K ? klo0 + ko + o : o < 2 * K ? kst0 + ko + (o - K)
+                                           : o < 2 * K + V ? vlo0 + vo + (o - 2 * K) : vst0 + vo + (o - 2 * K - V);
                         cp_async16(sdst + (uint32_t)o, src);
                     }
                 }
@@ -486,7 +498,7 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
             p_scale += clock64() - _ps0;
 #endif
         }
-        if (!ok || done) break;
+        if (!ok) break;
         item = next_item;
         next_item = __shfl_sync(0xffffffffu, next2, 0);
     }
@@ -531,7 +543,12 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
         if (!mbar_wait(&sm.item_full[s], (uint32_t)(j / kItemSlots) & 1u)) { code = 7; break; }
         const ItemDesc it = sm.item[s];
         if (it.exit) return;
-        // the buffer was last used by item j-2: wait until every consumer warp has left it
+        // the item's block table for the producer (its buffer was last read for item j-2, which the
+        // producer had finished before it announced this item)
+        build_table<D, G>(p, sm.meta_tab + ib * 32, span_of(p, it.item), lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.tab_ready[ib]);
+        // the query buffer was last used by item j-2: wait until every consumer warp has left it
         if (j >= 2 && !mbar_wait(&sm.item_empty[(j - 2) % kItemSlots], (uint32_t)((j - 2) / kItemSlots) & 1u)) { code = 8; break; }
         float* sq = sm.sq + ib * 8 * D;
         float* sf = sm.sf + ib * 16;
@@ -1038,6 +1055,7 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     int code = 0;                                   // non-zero: a wait gave up
 #ifdef GKV_DBG_TIMING
     long long c_all = clock64(), c_wait = 0, c_comp = 0, c_item = 0, c_n = 0;
+    const unsigned long long t_begin = global_ns();
 #endif
     for (int iseq = 0; code == 0; ++iseq) {
         const int is = iseq % kItemSlots, ib = iseq & 1;
@@ -1050,6 +1068,11 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
 #ifdef GKV_DBG_TIMING
             if (lane == 0) {
                 unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.counter) + 12;
+                const unsigned long long tnow = global_ns();
+                atomicMax(dbg + 8, ~tnow);                        // earliest warp exit (complemented)
+                atomicMax(dbg + 9, tnow);                         // latest warp exit
+                atomicAdd(dbg + 10, tnow - t_begin);              // sum of warp lifetimes (ns)
+                atomicMax(dbg + 11, ~t_begin);                    // earliest start (complemented)
                 atomicAdd(dbg + 0, (unsigned long long)(clock64() - c_all));
                 atomicAdd(dbg + 1, (unsigned long long)c_wait);
                 atomicAdd(dbg + 2, (unsigned long long)c_comp);
@@ -1113,7 +1136,8 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         float l = st.l;
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        float* rec = p.part + (((size_t)it.item * kConsumerWarps + warp) * p.rep + r) * (D + 2);
+        const size_t rec_idx = (size_t)it.row * p.items_per_row + (size_t)(it.item / p.rows);
+        float* rec = p.part + ((rec_idx * kConsumerWarps + warp) * p.rep + r) * (D + 2);
         const bool live = r < p.rep;
         if (live && t == 0) { rec[0] = st.m * 0.6931471805599453f; rec[1] = l; }
         // p . vlo of channel group cg sits in lane 4r + cg/2, column cg & 1, scaled 2^8
@@ -1161,6 +1185,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params
         }
         mbar_init(&sm.qready[0], 1);
         mbar_init(&sm.qready[1], 1);
+        mbar_init(&sm.tab_ready[0], 1);
+        mbar_init(&sm.tab_ready[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
