@@ -157,8 +157,8 @@ static size_t records_bytes(int B, int Hq, const Plan& pl, int D) {
     return (size_t)B * Hq * ((size_t)pl.parts + (pl.segs > 1 ? pl.segs : 0)) * (D + 2) * sizeof(float);
 }
 
-// the tensor-core kernel's rung-sorted block lists: one int32 per block of every metadata row
-static size_t perm_bytes(int rows, int nb) { return (((size_t)rows * nb * sizeof(int32_t)) + 255) & ~(size_t)255; }
+// the tensor-core kernel's rung-sorted block lists: one 16-byte entry per block of every metadata row
+static size_t perm_bytes(int rows, int nb) { return (((size_t)rows * nb * sizeof(uint4)) + 255) & ~(size_t)255; }
 
 // Upper bound over both kernels, so the caller's buffer fits whichever is dispatched.
 static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
@@ -208,13 +208,13 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     if (pl.mma) {
         GKV_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, stream));
         // the block lists sit at the end of the workspace, behind the records of either kernel
-        int32_t* perm = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + need - perm_bytes(rows, nb));
+        uint4* plan = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + need - perm_bytes(rows, nb));
         int plan_threads = ((nb + 3) / 4 + 31) & ~31;           // ~4 blocks per thread
         plan_threads = plan_threads < 32 ? 32 : plan_threads > mma::kPlanMaxThreads ? mma::kPlanMaxThreads : plan_threads;
-        mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, perm, nb);
+        mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, offs, plan, nb);
         GKV_LAUNCH_CHECK();
         mma::Params mp;
-        mp.perm = perm; mp.rows = rows;
+        mp.plan = plan; mp.rows = rows;
         mp.q = q; mp.data = data; mp.offs = offs;
         mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
         mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);

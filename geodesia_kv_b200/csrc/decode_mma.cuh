@@ -87,7 +87,7 @@ struct Params {
     const __half* vstep;
     const int32_t* level;
     const int32_t* valid;
-    const int32_t* perm; // (metadata rows, nb) block indices of every row sorted by rung, from plan_kernel
+    const uint4* plan;  // (metadata rows, nb) block entries of every row sorted by rung, from plan_kernel
     float* part;        // (rows, items per row, consumer warps, rep, D+2)
     int* counter;       // work-item counter (zeroed before launch)
     int* status;        // error word (zeroed before launch)
@@ -239,7 +239,7 @@ struct Cfg {
     static constexpr int SQ_BYTES = 8 * D * 4;
     static constexpr size_t SMEM = kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
                                    kNSlot * sizeof(Desc) + 2 * kNSlot * 8 + kItemSlots * sizeof(ItemDesc) +
-                                   (2 * kItemSlots + 4) * 8 + 2 * 32 * 16 + 64;
+                                   (2 * kItemSlots + 2) * 8 + 32 * 16 + 64;
     static_assert(D % 32 == 0 && (G == 16 || G == 32 || G == 64) && D % G == 0, "unsupported shape");
 };
 
@@ -257,8 +257,7 @@ struct Smem {
     uint64_t* item_full;   // [kItemSlots] producer -> query warp and consumers
     uint64_t* item_empty;  // [kItemSlots] one arrival per consumer warp that finished the item
     uint64_t* qready;      // [2] query warp -> consumers
-    uint64_t* tab_ready;   // [2] query warp -> producer
-    uint4* meta_tab;       // [2][32] block tables of the current and the next item
+    uint4* meta_tab;       // [32] block table of the producer's current item
     __device__ explicit Smem(uint8_t* base) {
         ring = base;
         qprep = reinterpret_cast<__half*>(base + kRingBytes);
@@ -270,8 +269,7 @@ struct Smem {
         item_full = empty + kNSlot;
         item_empty = item_full + kItemSlots;
         qready = item_empty + kItemSlots;
-        tab_ready = qready + 2;
-        item = reinterpret_cast<ItemDesc*>(tab_ready + 2);
+        item = reinterpret_cast<ItemDesc*>(qready + 2);
         meta_tab = reinterpret_cast<uint4*>(item + kItemSlots);
     }
 };
@@ -289,36 +287,24 @@ __device__ __forceinline__ Span span_of(const Params& p, int it) {
     return Span{it % p.rows, b_lo, min(p.chunk, p.nb - b_lo)};     // nblk <= 32
 }
 
-// Table of an item's blocks, one uint4 per block: source offset (64 bit), level | nvalid << 8,
-// block index in the row.  Built by a full warp in one coalesced pass over the metadata.
-template <int D, int G>
-__device__ __forceinline__ void build_table(const Params& p, uint4* tab, const Span& sp, int lane) {
-    if (lane < sp.nblk) {
-        const size_t m0 = (size_t)(p.per_row_meta ? sp.row : 0) * p.nb;
-        const int blk = p.perm[m0 + sp.b_lo + lane];
-        int lv = p.level[m0 + blk];
-        const int nv = min(p.valid[m0 + blk], kP);
-        if (!level_ok(lv) || nv <= 0) lv = 0;
-        const unsigned long long src = (unsigned long long)sp.row * (unsigned long long)p.stride_bh + (unsigned long long)p.offs[m0 + blk];
-        tab[lane] = make_uint4((uint32_t)src, (uint32_t)(src >> 32), (uint32_t)lv | ((uint32_t)max(nv, 0) << 8), (uint32_t)blk);
-    }
-}
-
 // ---- rung-sorted block lists -----------------------------------------------------------------------
-// One CTA per metadata row: a stable counting sort of the row's block indices by rung (16, 8, 4, 2,
-// centroid, then blocks with nothing to do).  Every thread owns a contiguous run of blocks, counts
+// One CTA per metadata row: a stable counting sort of the row's blocks by rung (16, 8, 4, 2,
+// centroid, then blocks with nothing to do).  An entry is everything the producer needs to know
+// about a block: byte offset in the row (64 bit), level | nvalid << 8 (level 0: skip), block index.  Every thread owns a contiguous run of blocks, counts
 // its classes, an in-order scan over (class, thread) gives it a write cursor per class, and it
 // walks its run once more.  Deterministic: no atomics.
 constexpr int kPlanMaxThreads = 1024;
 __device__ __forceinline__ int rung_class(int lv, int nv) {
     return nv <= 0 ? 5 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
 }
-__global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* level, const int32_t* valid, int32_t* perm, int nb) {
+__global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* level, const int32_t* valid, const int64_t* offs,
+                                                                uint4* plan, int nb) {
     __shared__ int wsum[kPlanMaxThreads / 32][6];   // per-warp class totals, then their exclusive scan
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const int32_t* lv = level + (size_t)blockIdx.x * nb;
     const int32_t* nv = valid + (size_t)blockIdx.x * nb;
-    int32_t* out = perm + (size_t)blockIdx.x * nb;
+    const int64_t* of = offs + (size_t)blockIdx.x * nb;
+    uint4* out = plan + (size_t)blockIdx.x * nb;
     const int per = (nb + (int)blockDim.x - 1) / (int)blockDim.x;
     const int lo = min(nb, tid * per), hi = min(nb, lo + per);
     int cnt[6] = {0, 0, 0, 0, 0, 0};
@@ -349,10 +335,13 @@ __global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* le
 #pragma unroll
     for (int k = 0; k < 6; ++k) cur[k] += wsum[warp][k];
     for (int b = lo; b < hi; ++b) {
-        const int c = rung_class(lv[b], nv[b]);
+        const int l = lv[b], n = min(nv[b], kP);
+        const int c = rung_class(l, n);
+        const unsigned long long o = (unsigned long long)of[b];
+        const uint4 e = make_uint4((uint32_t)o, (uint32_t)(o >> 32), c == 5 ? 0u : ((uint32_t)l | ((uint32_t)n << 8)), (uint32_t)b);
 #pragma unroll
         for (int k = 0; k < 6; ++k)
-            if (c == k) out[cur[k]++] = b;
+            if (c == k) out[cur[k]++] = e;
     }
 }
 
@@ -398,6 +387,21 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     bool ok = true;
     if (lane == 0) ok = announce(0, item, span_of(p, item), span_of(p, item).nblk);
     ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    // Block table of an item: entry `lane` of its run of the row's plan, with the row's base offset
+    // added.  The next item's entries are requested at the start of the current item and parked in
+    // the table when its last block has been issued, so the global-memory latency is never waited for.
+    auto fetch_entry = [&](const Span& sp) -> uint4 {
+        uint4 e = make_uint4(0, 0, 0, 0);
+        if (lane < sp.nblk) {
+            e = p.plan[(size_t)(p.per_row_meta ? sp.row : 0) * p.nb + sp.b_lo + lane];
+            const unsigned long long src = (unsigned long long)sp.row * (unsigned long long)p.stride_bh +
+                                           (((unsigned long long)e.y << 32) | e.x);
+            e.x = (uint32_t)src; e.y = (uint32_t)(src >> 32);
+        }
+        return e;
+    };
+    sm.meta_tab[lane] = fetch_entry(span_of(p, item));
+    __syncwarp();
     for (int iseq = 0; ok; ++iseq) {
         const bool done = item >= p.items;
         int next2 = 0;
@@ -412,10 +416,9 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
             ok = announce(iseq + 1, next_item, ns, seq_alloc + nblk + ns.nblk);
         }
         if (done) break;
-        // this item's table comes from the query warp
-        if (ok && !mbar_wait(&sm.tab_ready[iseq & 1], (uint32_t)(iseq >> 1) & 1u)) ok = false;
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        const uint4* tab = sm.meta_tab + (iseq & 1) * 32;
+        const uint4 next_entry = fetch_entry(ns);
+        const uint4* tab = sm.meta_tab;
         const size_t sb0 = (size_t)row * p.nb;
         const uint8_t* klo0 = reinterpret_cast<const uint8_t*>(p.klo) + sb0 * C::KSCALE;
         const uint8_t* kst0 = reinterpret_cast<const uint8_t*>(p.kstep) + sb0 * C::KSCALE;
@@ -499,6 +502,9 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
 #endif
         }
         if (!ok) break;
+        __syncwarp();
+        sm.meta_tab[lane] = next_entry;
+        __syncwarp();
         item = next_item;
         next_item = __shfl_sync(0xffffffffu, next2, 0);
     }
@@ -543,11 +549,6 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
         if (!mbar_wait(&sm.item_full[s], (uint32_t)(j / kItemSlots) & 1u)) { code = 7; break; }
         const ItemDesc it = sm.item[s];
         if (it.exit) return;
-        // the item's block table for the producer (its buffer was last read for item j-2, which the
-        // producer had finished before it announced this item)
-        build_table<D, G>(p, sm.meta_tab + ib * 32, span_of(p, it.item), lane);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.tab_ready[ib]);
         // the query buffer was last used by item j-2: wait until every consumer warp has left it
         if (j >= 2 && !mbar_wait(&sm.item_empty[(j - 2) % kItemSlots], (uint32_t)((j - 2) / kItemSlots) & 1u)) { code = 8; break; }
         float* sq = sm.sq + ib * 8 * D;
@@ -572,25 +573,39 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
             }
         }
         __syncwarp();
-        // entries (chunk i, lane l, half jj) of each plane
-        for (int idx = lane; idx < C::CH * 32 * 8; idx += 32) {
-            const int jj = idx & 7, l = (idx >> 3) & 31, i = idx >> 8;
-            const int r = l >> 2, t = l & 3;
-            const int ks = 2 * i + (jj >> 2), e = jj & 3;
+        // which rungs does the item hold?  (its run of the sorted plan; usually one or two)
+        const Span sp = span_of(p, it.item);
+        int lvl = 0;
+        if (lane < sp.nblk) lvl = (int)(p.plan[(size_t)(p.per_row_meta ? sp.row : 0) * p.nb + sp.b_lo + lane].z & 0xffu);
+        const bool need8 = __any_sync(0xffffffffu, lvl == 8), need4 = __any_sync(0xffffffffu, lvl == 4);
+        const bool need2 = __any_sync(0xffffffffu, lvl == 2), need16 = __any_sync(0xffffffffu, lvl == 16);
+        // This lane writes its own fragment lane of every chunk: 8 halves (two k-steps x four slots)
+        // per plane and chunk, as one 16-byte store.  Only the arrangements of rungs that occur.
+        {
+            const int r = lane >> 2, t = lane & 3;
             const float sc = sf[8 + r];
             const float* qr = sq + r * D + C::DT * t;
 #pragma unroll
-            for (int a = 0; a < 3; ++a) {
-                const int bits = a == 0 ? 8 : a == 1 ? 4 : 2;
-                const float x = qr[arr_chan(bits, ks, e)] * sc * arr_scale(bits, e);
-                const __half h = __float2half_rn(x);
-                qp[(2 * a) * C::QPLANE + idx] = h;
-                qp[(2 * a + 1) * C::QPLANE + idx] = __float2half_rn(x - __half2float(h));
+            for (int a = 0; a < 4; ++a) {
+                const int bits = a == 0 ? 8 : a == 1 ? 4 : a == 2 ? 2 : 16;
+                const bool need = a == 0 ? need8 : a == 1 ? need4 : a == 2 ? need2 : need16;
+                if (!need) continue;
+#pragma unroll 1
+                for (int i = 0; i < C::CH; ++i) {
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int jp = 0; jp < 4; ++jp) {            // halves 2jp, 2jp+1: k-step 2i + (jp >> 1), slots 2(jp & 1) + {0, 1}
+                        const int ks = 2 * i + (jp >> 1), e0 = 2 * (jp & 1);
+                        const float x0 = qr[arr_chan(bits, ks, e0)] * sc * arr_scale(bits, e0);
+                        const float x1 = qr[arr_chan(bits, ks, e0 + 1)] * sc * arr_scale(bits, e0 + 1);
+                        if (a < 3) split_f16x2(x0, x1, hi[jp], lo[jp]);
+                        else split_bf16x2(x0, x1, hi[jp], lo[jp]);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(qp + (size_t)(2 * a) * C::QPLANE + ((size_t)i * 32 + lane) * 8);
+                    dst[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    dst[C::QPLANE / 8] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
             }
-            const float x = qr[arr_chan(16, ks, e)] * sc;
-            const __nv_bfloat16 hb = __float2bfloat16_rn(x);
-            reinterpret_cast<__nv_bfloat16*>(qp)[6 * C::QPLANE + idx] = hb;
-            reinterpret_cast<__nv_bfloat16*>(qp)[7 * C::QPLANE + idx] = __float2bfloat16_rn(x - __bfloat162float(hb));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.qready[ib]);
@@ -628,29 +643,9 @@ __device__ __forceinline__ uint4 qchunk(const Ctx<D, G>& c, int plane, int i) {
     return lds_v4(c.qprep + (uint32_t)(plane * Cfg<D, G>::QPLANE * 2 + i * 512));
 }
 
-// ---- q . klo for every token group of a quantised block: one n-tile whose column n is group n ----
-template <int D, int G>
-__device__ __forceinline__ void key_bias(const Ctx<D, G>& c, uint32_t klo, float (&bias)[4]) {
-    using C = Cfg<D, G>;
-    const bool live = c.r < C::TG;
-    const uint32_t lo = klo + (uint32_t)(((live ? c.r : 0) * D + C::DT * c.t) * 2);
-    bias[0] = bias[1] = bias[2] = bias[3] = 0.f;
-    float bias2[4] = {0.f, 0.f, 0.f, 0.f};            // second chain: back-to-back MMAs into one accumulator serialise
-#pragma unroll
-    for (int i = 0; i < C::CH; ++i) {
-        const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
-        uint4 b = lds_v4(lo + 16 * i);
-        if (!live) b = make_uint4(0, 0, 0, 0);
-        mma_f16(bias, qh.x, ql.x, qh.y, ql.y, b.x, b.y);
-        mma_f16(bias2, qh.z, ql.z, qh.w, ql.w, b.z, b.w);
-    }
-    bias[0] += bias2[0]; bias[1] += bias2[1]; bias[2] += bias2[2]; bias[3] += bias2[3];
-}
-
 // ---- K side of one unit of a quantised block: scores in the log2 domain ---------------------------
 template <int D, int G, int BITS>
-__device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, int tg, const float (&bias)[4],
-                                            float (&z)[Unit<D, G>::ZN]) {
+__device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, int tg, float (&z)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
     constexpr int RB = D * BITS / 8;                     // bytes per token row
@@ -662,23 +657,39 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     float acc[UU::NU][4];
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    // q . klo of this token group rides along as one more n-tile whose eight columns all carry the
+    // group's klo (so every thread ends up with its own head's value, no shuffle); two accumulators,
+    // one per k-step of a chunk, keep the MMAs independent.
+    float bias0[4] = {0.f, 0.f, 0.f, 0.f}, bias1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
     for (int i = 0; i < C::CH; ++i) {                   // two k-steps at a time
         const uint4 qh = qchunk(c, plane, i), ql = qchunk(c, plane + 1, i);
-        uint32_t sp[4];                                  // step pairs of k-steps 2i and 2i+1 in this arrangement
+        uint32_t sp[4], lp[4];                           // kstep / klo pairs of k-steps 2i and 2i+1 in this arrangement
         if (BITS == 8) {
-            const uint4 v = lds_v4(nat + 16 * i);
+            const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
             sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
+            lp[0] = l.x; lp[1] = l.y; lp[2] = l.z; lp[3] = l.w;
         } else if (BITS == 4) {                          // s = 2x+y with x = i: words 4i+y, 4i+y+2
-            const uint4 v = lds_v4(nat + 16 * i);
+            const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
             sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
             sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
+            // the query plane carries x16 on slots 0,1 (arr_scale): take it back out of klo
+            const __half2 k16 = __float2half2_rn(0.0625f);
+            lp[0] = h2_as_u32(__hmul2(u32_as_h2(prmt(l.x, l.z, 0x5410)), k16)); lp[1] = prmt(l.x, l.z, 0x7632);
+            lp[2] = h2_as_u32(__hmul2(u32_as_h2(prmt(l.y, l.w, 0x5410)), k16)); lp[3] = prmt(l.y, l.w, 0x7632);
         } else {                                         // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
             const uint32_t w0 = nat + (uint32_t)(32 * (i >> 1) + 8 * (i & 1));
             const uint2 va = lds_v2(w0), vb = lds_v2(w0 + 16);
+            const uint2 la = lds_v2(w0 - C::KSCALE), lb = lds_v2(w0 - C::KSCALE + 16);
             sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
             sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
+            // the query plane carries x4 on slots 2,3
+            const __half2 k4 = __float2half2_rn(0.25f);
+            lp[0] = prmt(la.x, lb.x, 0x5410); lp[1] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.x, lb.x, 0x7632)), k4));
+            lp[2] = prmt(la.y, lb.y, 0x5410); lp[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.y, lb.y, 0x7632)), k4));
         }
+        mma_f16(bias0, qh.x, ql.x, qh.y, ql.y, lp[0], lp[1]);
+        mma_f16(bias1, qh.z, ql.z, qh.w, ql.w, lp[2], lp[3]);
         uint32_t a[8];
         mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
         mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
@@ -712,9 +723,7 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[4], a[5], a[6], a[7], bb[n][2], bb[n][3]);
     }
-    // bias of this token group for head r lives in lane 4r + tg/2, column tg & 1
-    const float bsel = (tg & 1) ? bias[1] + bias[3] : bias[0] + bias[2];
-    const float bg = __shfl_sync(0xffffffffu, bsel, (c.lane & ~3) | (tg >> 1));
+    const float bg = (bias0[0] + bias0[2]) + (bias1[0] + bias1[2]);      // hi rows + lo rows, both k-steps
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) {
         z[2 * n + 0] = fmaf(acc[n][0] + acc[n][2], k_unscale(BITS), bg) * c.f;
@@ -941,23 +950,21 @@ __device__ __forceinline__ void clear_invalid_tail(uint8_t* blk, int level, int 
     __syncwarp();
 }
 
-// One quantised block, units [u0, u1): bias once, then the units.
+// One quantised block, units [u0, u1).
 template <int D, int G, int BITS>
 __device__ __forceinline__ void quant_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid, int u0, int u1) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
     if (u1 <= u0 || nvalid <= u0 * UU::U) return;
-    float bias[4];
-    key_bias(c, blk + 2 * (kP * D * BITS / 8), bias);
 #pragma unroll 1
     for (int unit = u0; unit < u1; ++unit) {
         const int nrel = nvalid - unit * UU::U;
         if (nrel <= 0) break;
         float z[UU::ZN];
 #ifdef GKV_DBG_NOK
-        for (int i = 0; i < UU::ZN; ++i) z[i] = bias[0] + (float)i;
+        for (int i = 0; i < UU::ZN; ++i) z[i] = (float)(i + c.r);
 #else
-        scores_unit<D, G, BITS>(c, blk, unit, bias, z);
+        scores_unit<D, G, BITS>(c, blk, unit, z);
 #endif
         softmax_unit(c, st, z, nrel);
 #ifndef GKV_DBG_NOV
@@ -1185,8 +1192,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params
         }
         mbar_init(&sm.qready[0], 1);
         mbar_init(&sm.qready[1], 1);
-        mbar_init(&sm.tab_ready[0], 1);
-        mbar_init(&sm.tab_ready[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
