@@ -53,19 +53,35 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     const int s_lo = p.segs > 1 ? (int)blockIdx.y * p.per_seg : 0;
     const int s_hi = p.segs > 1 ? min(p.parts, s_lo + p.per_seg) : p.parts;
     const size_t out_row = p.segs > 1 ? (size_t)blockIdx.y * gridDim.x + orow : (size_t)orow;
-    for (int s = s_lo + warp; s < s_hi; s += 8) {
-        const float* rec = base + s * stride;
-        const float ms = rec[0];
-        if (!(ms > -INFINITY)) continue;             // empty slice (warp-uniform)
-        const float mn = fmaxf(m, ms);
-        const float a = expf(m - mn), b = expf(ms - mn);   // a = 0 while m = -inf
-        l = l * a + rec[1] * b;
+    // kBatch records at a time: all their loads are issued before the first is merged (the merge
+    // itself is a serial recurrence, and one load round trip per record made this kernel
+    // latency-bound); the order of the merge is unchanged.
+    constexpr int kBatch = 4;
+    for (int s0 = s_lo + warp; s0 < s_hi; s0 += 8 * kBatch) {
+        float ms[kBatch], ls[kBatch], v[kBatch][kPer];
 #pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-            const int d = lane + 32 * i;
-            if (d < D) o[i] = o[i] * a + rec[2 + d] * b;
+        for (int b = 0; b < kBatch; ++b) {
+            const int s = s0 + 8 * b;
+            const bool live = s < s_hi;
+            const float* rec = base + (live ? s : s0) * stride;
+            ms[b] = live ? rec[0] : -INFINITY;
+            ls[b] = rec[1];
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int d = lane + 32 * i;
+                v[b][i] = d < D ? rec[2 + d] : 0.f;
+            }
         }
-        m = mn;
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            if (!(ms[b] > -INFINITY)) continue;          // empty slice (warp-uniform)
+            const float mn = fmaxf(m, ms[b]);
+            const float a = expf(m - mn), bb = expf(ms[b] - mn);   // a = 0 while m = -inf
+            l = l * a + ls[b] * bb;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) o[i] = o[i] * a + v[b][i] * bb;
+            m = mn;
+        }
     }
     if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
@@ -206,12 +222,11 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     float* records = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kHeaderBytes);
 
     if (pl.mma) {
-        GKV_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, stream));
         // the block lists sit at the end of the workspace, behind the records of either kernel
         uint4* plan = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + need - perm_bytes(rows, nb));
-        int plan_threads = ((nb + 3) / 4 + 31) & ~31;           // ~4 blocks per thread
+        int plan_threads = (nb + 31) & ~31;                     // one block per thread up to the CTA limit
         plan_threads = plan_threads < 32 ? 32 : plan_threads > mma::kPlanMaxThreads ? mma::kPlanMaxThreads : plan_threads;
-        mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, offs, plan, nb);
+        mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, offs, plan, nb, header, (int)(kHeaderBytes / 4));
         GKV_LAUNCH_CHECK();
         mma::Params mp;
         mp.plan = plan; mp.rows = rows;

@@ -292,13 +292,16 @@ __device__ __forceinline__ Span span_of(const Params& p, int it) {
 // centroid, then blocks with nothing to do).  An entry is everything the producer needs to know
 // about a block: byte offset in the row (64 bit), level | nvalid << 8 (level 0: skip), block index.  Every thread owns a contiguous run of blocks, counts
 // its classes, an in-order scan over (class, thread) gives it a write cursor per class, and it
-// walks its run once more.  Deterministic: no atomics.
+// walks its run once more.  Deterministic: no atomics.  Also clears the workspace header.
 constexpr int kPlanMaxThreads = 1024;
 __device__ __forceinline__ int rung_class(int lv, int nv) {
     return nv <= 0 ? 5 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
 }
 __global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* level, const int32_t* valid, const int64_t* offs,
-                                                                uint4* plan, int nb) {
+                                                                uint4* plan, int nb, int* header, int header_ints) {
+    // the decode kernel's work counter and status word start at zero
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < header_ints; i += blockDim.x) header[i] = 0;
     __shared__ int wsum[kPlanMaxThreads / 32][6];   // per-warp class totals, then their exclusive scan
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const int32_t* lv = level + (size_t)blockIdx.x * nb;
@@ -1061,7 +1064,7 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     int seq = pair;
     int code = 0;                                   // non-zero: a wait gave up
 #ifdef GKV_DBG_TIMING
-    long long c_all = clock64(), c_wait = 0, c_comp = 0, c_item = 0, c_n = 0;
+    long long c_all = clock64(), c_wait = 0, c_comp = 0, c_item = 0, c_n = 0, c_lat = 0, c_latn = 0;
     const unsigned long long t_begin = global_ns();
 #endif
     for (int iseq = 0; code == 0; ++iseq) {
@@ -1085,6 +1088,8 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
                 atomicAdd(dbg + 2, (unsigned long long)c_comp);
                 atomicAdd(dbg + 3, (unsigned long long)c_item);
                 atomicAdd(dbg + 4, (unsigned long long)c_n);
+                atomicAdd(dbg + 5, (unsigned long long)c_lat);
+                atomicAdd(dbg + 6, (unsigned long long)c_latn);
             }
 #endif
             return;
@@ -1110,7 +1115,11 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
             if (!mbar_wait(&sm.full[slot], (uint32_t)(seq / kNSlot) & 1u)) { code = 4; break; }
             const Desc d = sm.desc[slot];
 #ifdef GKV_DBG_TIMING
-            { const long long now = clock64(); c_wait += now - _cw0; _cw0 = now; ++c_n; }
+            {
+                const long long now = clock64();
+                if (now - _cw0 > 400) { c_lat += now - _cw0; ++c_latn; }      // length of the waits that were real waits
+                c_wait += now - _cw0; _cw0 = now; ++c_n;
+            }
 #endif
 #ifdef GKV_DBG_NOCOMPUTE
             if (false) {
