@@ -52,6 +52,13 @@ METRIC = "packed_kv_decode_attn_context_tokens_per_s"
 UNIT = "context-tokens/s"
 
 
+# DRAM bytes moved per algorithmic byte by the decode kernel on the cfg1 rung mix, from the ncu
+# capture summarised in profiles/decode_mma_cfg1-small_ncu.md (dram read + write of one launch of
+# the profiling-sized slice over its algorithmic bytes).  Traffic grows with the number of blocks,
+# so a full-size launch is that ratio times its own algorithmic bytes.
+DRAM_TRAFFIC_RATIO = {"cfg1": 1.058, "cfg1-small": 1.058}
+
+
 def measured_peak_gbs():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -264,9 +271,11 @@ def run_gpu(args):
         "e2e": {"value": tokens_per_step / (ms_e2e / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": L * B * Hq * D * 4, "d2h_bytes_per_step": L * B * Hq * D * 4,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": (3 if split else 2) * launches,
+        "gpu_launches": launches * (ext.lib.gkv_decode_kernel_launches(B, Hq, w["Hkv"], D, caches[0].nb, GROUP) + (1 if split else 0)),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "peak_kind": f"of {peak_kind}",
+                     "traffic": (bytes_per_launch * DRAM_TRAFFIC_RATIO[args.workload]
+                                 if args.workload in DRAM_TRAFFIC_RATIO and not split else None),
                      "kernel": "decode split kernel (+ its LSE combine, timed together)",
                      "algorithmic_bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_launch_s * 1e6},
         "clocks": clocks,

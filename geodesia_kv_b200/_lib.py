@@ -21,6 +21,7 @@ SIGNATURES = {
     "gkv_error_string": (C.c_char_p, [_i]),
     "gkv_last_cuda_error": (_i, []),
     "gkv_decode_workspace_bytes": (_sz, [_i] * 5),
+    "gkv_decode_kernel_launches": (_i, [_i] * 6),
     "gkv_mixed_attn_decode": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_partial": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_static": (_i, [_vp] * 10 + [_i] * 7 + [_i64, _i, _vp]),

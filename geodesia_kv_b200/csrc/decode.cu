@@ -311,6 +311,13 @@ size_t gkv_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
     return gkv::workspace_bytes(B, Hq, Hkv, D, nb);
 }
 
+int gkv_decode_kernel_launches(int B, int Hq, int Hkv, int D, int nb, int group) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0 || nb < 0 || group <= 0) return 0;
+    const gkv::Plan pl = gkv::make_plan(B * Hkv, nb, D, group, Hq / Hkv, nb > 0);
+    // tensor-core path: block lists, split kernel, one or two merge levels; generic path: split kernel, merge
+    return pl.mma ? 2 + (pl.segs > 1 ? 2 : 1) : 2;
+}
+
 int gkv_mixed_attn_decode(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
                           const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
                           const int32_t* valid, float* out, void* workspace, size_t workspace_bytes,

@@ -633,6 +633,13 @@ struct Unit {
     static constexpr int ZN = G / 4;     // scores held per thread
 };
 
+// Inside every 8-token n-tile of a quantised block, score column c stands for token
+// token_of_column(c) = (0, 1, 3, 2, 4, 5, 7, 6)[c].  On the K side that is just which row a lane
+// reads; on the V side it makes the four lanes of a quad read token rows of alternating parity
+// (t, t+1 swapped for odd t), which halves the bank conflicts of the 4-bit value rows, while a
+// lane's two tokens of a k-pair stay neighbours so their scales still come from one load.
+__device__ __forceinline__ int token_of_column(int c) { return c ^ ((c >> 1) & 1); }
+
 template <int D, int G>
 struct Ctx {                             // per-thread constants of the consumer role
     uint32_t qprep;                      // shared address of this lane's first prepared-query chunk (plane 0)
@@ -655,7 +662,15 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     constexpr int TB = RB / 4;                           // bytes per thread per row
     constexpr int plane = BITS == 8 ? 0 : BITS == 4 ? 2 : 4;
     const uint32_t nat = blk + (uint32_t)(2 * (kP * RB) + C::KSCALE + (tg * D + C::DT * c.t) * 2);
-    const uint32_t row0 = blk + (uint32_t)((tg * UU::U + c.r) * RB + c.t * TB);
+    // The thread's codes of a token row are fetched with the widest load that fits (all chunks at
+    // once for 4- and 2-bit codes): a quarter warp then reads whole rows side by side, free of the
+    // bank conflicts that one 4-byte load per chunk had (rows are 32-128 bytes apart).
+    constexpr int CB = TB / C::CH;                       // code bytes per thread, row and chunk
+    constexpr int LB = TB < 16 ? TB : 16;                // bytes per fetch
+    constexpr int CG = LB / CB;                          // chunks per fetch
+    constexpr int LW = LB / 4;
+    static_assert(LB >= 4 && C::CH % CG == 0, "unsupported shape");
+    const uint32_t row0 = blk + (uint32_t)((tg * UU::U + token_of_column(c.r)) * RB + c.t * TB);
 
     float acc[UU::NU][4];
 #pragma unroll
@@ -665,66 +680,76 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     // one per k-step of a chunk, keep the MMAs independent.
     float bias0[4] = {0.f, 0.f, 0.f, 0.f}, bias1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-    for (int i = 0; i < C::CH; ++i) {                   // two k-steps at a time
-        const uint4 qh = qchunk(c, plane, i), ql = qchunk(c, plane + 1, i);
-        uint32_t sp[4], lp[4];                           // kstep / klo pairs of k-steps 2i and 2i+1 in this arrangement
-        if (BITS == 8) {
-            const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
-            sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
-            lp[0] = l.x; lp[1] = l.y; lp[2] = l.z; lp[3] = l.w;
-        } else if (BITS == 4) {                          // s = 2x+y with x = i: words 4i+y, 4i+y+2
-            const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
-            sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
-            sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
-            // the query plane carries x16 on slots 0,1 (arr_scale): take it back out of klo
-            const __half2 k16 = __float2half2_rn(0.0625f);
-            lp[0] = h2_as_u32(__hmul2(u32_as_h2(prmt(l.x, l.z, 0x5410)), k16)); lp[1] = prmt(l.x, l.z, 0x7632);
-            lp[2] = h2_as_u32(__hmul2(u32_as_h2(prmt(l.y, l.w, 0x5410)), k16)); lp[3] = prmt(l.y, l.w, 0x7632);
-        } else {                                         // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
-            const uint32_t w0 = nat + (uint32_t)(32 * (i >> 1) + 8 * (i & 1));
-            const uint2 va = lds_v2(w0), vb = lds_v2(w0 + 16);
-            const uint2 la = lds_v2(w0 - C::KSCALE), lb = lds_v2(w0 - C::KSCALE + 16);
-            sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
-            sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
-            // the query plane carries x4 on slots 2,3
-            const __half2 k4 = __float2half2_rn(0.25f);
-            lp[0] = prmt(la.x, lb.x, 0x5410); lp[1] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.x, lb.x, 0x7632)), k4));
-            lp[2] = prmt(la.y, lb.y, 0x5410); lp[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.y, lb.y, 0x7632)), k4));
-        }
-        mma_f16(bias0, qh.x, ql.x, qh.y, ql.y, lp[0], lp[1]);
-        mma_f16(bias1, qh.z, ql.z, qh.w, ql.w, lp[2], lp[3]);
-        uint32_t a[8];
-        mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
-        mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
-        mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
-        mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
-        const uint32_t rowi = row0 + (uint32_t)(BITS == 8 ? 8 * i : BITS == 4 ? 4 * i : 4 * (i >> 1));
-        const int sh2 = 8 * (i & 1);
-        uint32_t bb[UU::NU][4];                          // B registers of k-steps 2i (0,1) and 2i+1 (2,3)
+    for (int g = 0; g < C::CH / CG; ++g) {
+        uint32_t W[UU::NU][LW];
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) {
-            if (BITS == 8) {
-                const uint2 w = lds_v2(rowi + n * 8 * RB);
-                bb[n][0] = prmt(w.x, 0u, 0x4140); bb[n][1] = prmt(w.x, 0u, 0x4342);
-                bb[n][2] = prmt(w.y, 0u, 0x4140); bb[n][3] = prmt(w.y, 0u, 0x4342);
-            } else if (BITS == 4) {
-                const uint32_t w = lds_u32(rowi + n * 8 * RB);
-                const uint32_t u = w << 3, v = w >> 5;
-                bb[n][0] = u & 0x00780078u; bb[n][1] = u & 0x07800780u;
-                bb[n][2] = v & 0x00780078u; bb[n][3] = v & 0x07800780u;
-            } else {
-                // fields 4h..4h+3 (and +8) of the word, h = i & 1, brought to bits 8-9 / 6-7
-                const uint32_t w = lds_u32(rowi + n * 8 * RB) >> sh2;
-                const uint32_t u = w << 4;
-                bb[n][0] = (w << 8) & 0x03000300u; bb[n][1] = u & 0x00C000C0u;
-                bb[n][2] = u & 0x03000300u;        bb[n][3] = w & 0x00C000C0u;
-            }
+            const uint32_t src = row0 + (uint32_t)(g * LB + n * 8 * RB);
+            if (LW == 4) { const uint4 v = lds_v4(src); W[n][0] = v.x; W[n][1 % LW] = v.y; W[n][2 % LW] = v.z; W[n][3 % LW] = v.w; }
+            else if (LW == 2) { const uint2 v = lds_v2(src); W[n][0] = v.x; W[n][1 % LW] = v.y; }
+            else W[n][0] = lds_u32(src);
         }
-        // k-step major: the two MMAs of an n-tile are NU issues apart, which hides the MMA latency
 #pragma unroll
-        for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[0], a[1], a[2], a[3], bb[n][0], bb[n][1]);
+        for (int ii = 0; ii < CG; ++ii) {                // two k-steps at a time
+            const int i = g * CG + ii;
+            const uint4 qh = qchunk(c, plane, i), ql = qchunk(c, plane + 1, i);
+            uint32_t sp[4], lp[4];                       // kstep / klo pairs of k-steps 2i and 2i+1 in this arrangement
+            if (BITS == 8) {
+                const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
+                sp[0] = v.x; sp[1] = v.y; sp[2] = v.z; sp[3] = v.w;
+                lp[0] = l.x; lp[1] = l.y; lp[2] = l.z; lp[3] = l.w;
+            } else if (BITS == 4) {                      // s = 2x+y with x = i: words 4i+y, 4i+y+2
+                const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
+                sp[0] = prmt(v.x, v.z, 0x5410); sp[1] = prmt(v.x, v.z, 0x7632);
+                sp[2] = prmt(v.y, v.w, 0x5410); sp[3] = prmt(v.y, v.w, 0x7632);
+                // the query plane carries x16 on slots 0,1 (arr_scale): take it back out of klo
+                const __half2 k16 = __float2half2_rn(0.0625f);
+                lp[0] = h2_as_u32(__hmul2(u32_as_h2(prmt(l.x, l.z, 0x5410)), k16)); lp[1] = prmt(l.x, l.z, 0x7632);
+                lp[2] = h2_as_u32(__hmul2(u32_as_h2(prmt(l.y, l.w, 0x5410)), k16)); lp[3] = prmt(l.y, l.w, 0x7632);
+            } else {                                     // s = 4x+y: x = i>>1, y = 2(i&1)+{0,1}: words 8x+y, 8x+y+4
+                const uint32_t w0 = nat + (uint32_t)(32 * (i >> 1) + 8 * (i & 1));
+                const uint2 va = lds_v2(w0), vb = lds_v2(w0 + 16);
+                const uint2 la = lds_v2(w0 - C::KSCALE), lb = lds_v2(w0 - C::KSCALE + 16);
+                sp[0] = prmt(va.x, vb.x, 0x5410); sp[1] = prmt(va.x, vb.x, 0x7632);
+                sp[2] = prmt(va.y, vb.y, 0x5410); sp[3] = prmt(va.y, vb.y, 0x7632);
+                // the query plane carries x4 on slots 2,3
+                const __half2 k4 = __float2half2_rn(0.25f);
+                lp[0] = prmt(la.x, lb.x, 0x5410); lp[1] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.x, lb.x, 0x7632)), k4));
+                lp[2] = prmt(la.y, lb.y, 0x5410); lp[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.y, lb.y, 0x7632)), k4));
+            }
+            mma_f16(bias0, qh.x, ql.x, qh.y, ql.y, lp[0], lp[1]);
+            mma_f16(bias1, qh.z, ql.z, qh.w, ql.w, lp[2], lp[3]);
+            uint32_t a[8];
+            mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
+            mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
+            mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
+            mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
+            uint32_t bb[UU::NU][4];                      // B registers of k-steps 2i (0,1) and 2i+1 (2,3)
 #pragma unroll
-        for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[4], a[5], a[6], a[7], bb[n][2], bb[n][3]);
+            for (int n = 0; n < UU::NU; ++n) {
+                if (BITS == 8) {
+                    const uint32_t wx = W[n][(2 * ii) % LW], wy = W[n][(2 * ii + 1) % LW];
+                    bb[n][0] = prmt(wx, 0u, 0x4140); bb[n][1] = prmt(wx, 0u, 0x4342);
+                    bb[n][2] = prmt(wy, 0u, 0x4140); bb[n][3] = prmt(wy, 0u, 0x4342);
+                } else if (BITS == 4) {
+                    const uint32_t w = W[n][ii % LW];
+                    const uint32_t u = w << 3, v = w >> 5;
+                    bb[n][0] = u & 0x00780078u; bb[n][1] = u & 0x07800780u;
+                    bb[n][2] = v & 0x00780078u; bb[n][3] = v & 0x07800780u;
+                } else {
+                    // fields 4h..4h+3 (and +8) of the word, h = i & 1, brought to bits 8-9 / 6-7
+                    const uint32_t w = W[n][(ii >> 1) % LW] >> (8 * (ii & 1));
+                    const uint32_t u = w << 4;
+                    bb[n][0] = (w << 8) & 0x03000300u; bb[n][1] = u & 0x00C000C0u;
+                    bb[n][2] = u & 0x03000300u;        bb[n][3] = w & 0x00C000C0u;
+                }
+            }
+            // k-step major: the two MMAs of an n-tile are NU issues apart, which hides the MMA latency
+#pragma unroll
+            for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[0], a[1], a[2], a[3], bb[n][0], bb[n][1]);
+#pragma unroll
+            for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[4], a[5], a[6], a[7], bb[n][2], bb[n][3]);
+        }
     }
     const float bg = (bias0[0] + bias0[2]) + (bias1[0] + bias1[2]);      // hi rows + lo rows, both k-steps
 #pragma unroll
@@ -787,13 +812,13 @@ __device__ __forceinline__ float move_reference(WarpState<D, G>& st, float mx) {
 
 // z: scores of head r for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid tokens
 // left in this unit (>= 1).  Returns the weights in z.
-template <int D, int G>
+template <int D, int G, bool PERM>
 __device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel) {
     using UU = Unit<D, G>;
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < UU::ZN; ++i) {
-        const int tok = (i >> 1) * 8 + 2 * c.t + (i & 1);
+        const int tok = (i >> 1) * 8 + (PERM ? token_of_column(2 * c.t + (i & 1)) : 2 * c.t + (i & 1));
         if (tok >= nrel) z[i] = -INFINITY;
         mx = fmaxf(mx, z[i]);
     }
@@ -809,19 +834,22 @@ __device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>
     st.l += ls;
 }
 
-// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane at shared address `row` (token `tok`, even).
+// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane at shared address `row` (token `tok`, even);
+// `odd` swaps the two tokens of every pair (see token_of_column).
 template <int GV>
-__device__ __forceinline__ void scale_pairs(uint32_t row, uint32_t (&out)[GV]) {
+__device__ __forceinline__ void scale_pairs(uint32_t row, bool odd, uint32_t (&out)[GV]) {
+    const uint32_t lo = odd ? 0x1054u : 0x5410u, hi = odd ? 0x3276u : 0x7632u;
     if (GV == 4) {
         const uint4 v = lds_v4(row);
-        out[0] = prmt(v.x, v.z, 0x5410); out[1] = prmt(v.x, v.z, 0x7632);
-        out[2 % GV] = prmt(v.y, v.w, 0x5410); out[3 % GV] = prmt(v.y, v.w, 0x7632);
+        out[0] = prmt(v.x, v.z, lo); out[1] = prmt(v.x, v.z, hi);
+        out[2 % GV] = prmt(v.y, v.w, lo); out[3 % GV] = prmt(v.y, v.w, hi);
     } else if (GV == 2) {
         const uint2 v = lds_v2(row);
-        out[0] = prmt(v.x, v.y, 0x5410); out[1 % GV] = prmt(v.x, v.y, 0x7632);
+        out[0] = prmt(v.x, v.y, lo); out[1 % GV] = prmt(v.x, v.y, hi);
     } else {
+        const uint32_t ra = row + (odd ? 2 * GV : 0), rb = row + (odd ? 0 : 2 * GV);
 #pragma unroll
-        for (int cg = 0; cg < GV; ++cg) out[cg] = lds_u16(row + 2 * cg) | (lds_u16(row + 2 * (GV + cg)) << 16);
+        for (int cg = 0; cg < GV; ++cg) out[cg] = lds_u16(ra + 2 * cg) | (lds_u16(rb + 2 * cg) << 16);
     }
 }
 
@@ -837,7 +865,9 @@ __device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>&
     constexpr uint32_t MASK = (((1u << BITS) - 1u) << POS) * 0x00010001u;
     constexpr float PSCALE = (float)(256 >> POS);    // weights carry 2^(8-POS) so that every rung adds p*v*2^-16
     const __half2 lo_scale = __float2half2_rn((float)(1 << POS));
-    const int tok0 = unit * UU::U + 2 * c.t;         // first token of this thread's pair in k-step 0
+    const int tok0 = unit * UU::U + 2 * c.t;         // lower token of this thread's pair in k-step 0
+    const bool odd = c.t & 1;                        // odd lanes of a quad take their pair in swapped order
+    const uint32_t sw = odd ? RB : 0;
     // codes of (token tok0, channels NT*r .. of group 0); scale rows of token tok0
     uint32_t vrow = blk + (uint32_t)(kP * RB + tok0 * RB + (C::NT * c.r * BITS) / 8);
     uint32_t srow = blk + (uint32_t)(2 * (kP * RB) + 2 * C::KSCALE + tok0 * C::GV * 2);
@@ -851,10 +881,10 @@ __device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>&
 #pragma unroll
         for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];       // next k-step's weights move to the front
         uint32_t sa[C::GV], sb[C::GV], la[C::GV], lb[C::GV];
-        scale_pairs<C::GV>(srow + C::VSCALE, sa);                     // vstep, tokens (ta, ta+1)
-        scale_pairs<C::GV>(srow + C::VSCALE + 8 * C::GV * 2, sb);     // vstep, tokens (tb, tb+1)
-        scale_pairs<C::GV>(srow, la);                                 // vlo
-        scale_pairs<C::GV>(srow + 8 * C::GV * 2, lb);
+        scale_pairs<C::GV>(srow + C::VSCALE, odd, sa);                // vstep, the lane's token pair of n-tile 2ku
+        scale_pairs<C::GV>(srow + C::VSCALE + 8 * C::GV * 2, odd, sb);  // vstep, its pair of n-tile 2ku+1
+        scale_pairs<C::GV>(srow, odd, la);                            // vlo
+        scale_pairs<C::GV>(srow + 8 * C::GV * 2, odd, lb);
         // p . vlo: column n of this n-tile is channel group n
         {
             uint32_t b0 = 0, b1 = 0;
@@ -876,7 +906,7 @@ __device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>&
             uint32_t x[4][(NB + 31) / 32];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const uint32_t src = vrow + (uint32_t)(((k & 2) ? 8 : 0) * RB + (k & 1) * RB + (G * cg * BITS) / 8);
+                const uint32_t src = vrow + ((k & 1) ? RB - sw : sw) + (uint32_t)(((k & 2) ? 8 : 0) * RB + (G * cg * BITS) / 8);
                 if (NB >= 32) {
 #pragma unroll
                     for (int w = 0; w < (NB + 31) / 32; ++w) x[k][w] = lds_u32(src + 4 * w);
@@ -969,7 +999,7 @@ __device__ __forceinline__ void quant_block(const Ctx<D, G>& c, WarpState<D, G>&
 #else
         scores_unit<D, G, BITS>(c, blk, unit, z);
 #endif
-        softmax_unit(c, st, z, nrel);
+        softmax_unit<D, G, true>(c, st, z, nrel);
 #ifndef GKV_DBG_NOV
         values_unit<D, G, BITS>(c, st, blk, unit, z);
 #else
@@ -987,7 +1017,7 @@ __device__ __forceinline__ void bf16_block(const Ctx<D, G>& c, WarpState<D, G>& 
         if (nrel <= 0) break;
         float z[UU::ZN];
         scores_unit_bf16(c, blk, unit, z);
-        softmax_unit(c, st, z, nrel);
+        softmax_unit<D, G, false>(c, st, z, nrel);
         values_unit_bf16(c, st, blk, unit, z);
     }
 }

@@ -63,6 +63,11 @@ int gkv_last_cuda_error(void);          /* cudaError_t of the last failing CUDA 
  */
 size_t gkv_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int nb);
 
+/* Number of kernels one decode call of this shape launches (host arithmetic only; for callers
+ * that account for launches, e.g. a benchmark).  Assumes 16-byte aligned scale planes, which is
+ * what selects the tensor-core kernel.  No counterpart in the reference.                       */
+int gkv_decode_kernel_launches(int B, int Hq, int Hkv, int D, int nb, int group);
+
 int gkv_mixed_attn_decode(const float *q, const uint8_t *data, const int64_t *offs,
                           const void *klo, const void *kstep, const void *vlo, const void *vstep,
                           const int32_t *level, const int32_t *valid, float *out,

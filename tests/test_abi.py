@@ -35,6 +35,9 @@ def test_host_only_calls_need_no_gpu():
     need = lib.gkv_decode_workspace_bytes(32, 32, 8, 128, 256)
     assert need > 0 and need % 256 == 0
     assert lib.gkv_decode_workspace_bytes(0, 1, 1, 128, 1) == 0
+    assert lib.gkv_decode_kernel_launches(32, 32, 8, 128, 256, 32) == 3       # block lists, split kernel, one merge
+    assert lib.gkv_decode_kernel_launches(1, 28, 4, 128, 16384, 32) == 4      # long rows: two merge levels
+    assert lib.gkv_decode_kernel_launches(1, 4, 4, 96, 8, 32) == 2            # generic kernel + merge
 
 
 def test_argument_validation_happens_before_any_cuda_call():
