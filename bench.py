@@ -59,6 +59,17 @@ UNIT = "context-tokens/s"
 DRAM_TRAFFIC_RATIO = {"cfg1": 1.058, "cfg1-small": 1.058}
 
 
+def workload_config(w, world, split, cache_gb=None):
+    cfg = {"workload": w["name"], "layers": w["layers"], "q_heads": w["Hq"], "kv_heads": w["Hkv"], "head_dim": w["D"],
+           "sequences_per_gpu": w["B"], "context_tokens": w["T"], "group": GROUP,
+           "rung_mix_16_8_4_2_c": list(w["probs"]),
+           "sharding": (f"sp{world}: one sequence cut into byte-balanced block ranges, one all-gather of Hq*(D+2) floats per layer"
+                        if split else f"dp{world}: independent sequences, no collective")}
+    if cache_gb is not None:
+        cfg["l2"] = f"inputs larger than L2: {cache_gb:.1f} GB of packed cache per GPU, each layer read once per step"
+    return cfg
+
+
 def measured_peak_gbs():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -239,10 +250,28 @@ def run_gpu(args):
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
+    # One step (every layer's launches, and the all-gather of a split sequence) is replayed from a
+    # CUDA graph, as a serving loop would run it: at a few tens of microseconds per layer the
+    # Python and launch overhead would otherwise be what is measured.  --eager times plain launches.
+    # The sequence-split step, whose all-gather would have to be captured too, always runs eagerly.
+    launch_mode = "eager"
+    run_step = step_resident
+    if not args.eager and not split:      # a step with the all-gather inside is not captured (see --eager)
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_resident()
+            graph.replay()
+            torch.cuda.synchronize()
+            run_step, launch_mode = graph.replay, "cuda graph of one step"
+        except Exception as e:      # capture unsupported here (e.g. by the collective): fall back
+            launch_mode = f"eager (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_total = timed(step_resident, args.steps)
+    ms_total = timed(run_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     for _ in range(2):
         step_e2e()
@@ -261,11 +290,7 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if split else "weak",
         "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
-        "config": {"workload": w["name"], "layers": L, "q_heads": Hq, "kv_heads": w["Hkv"], "head_dim": D,
-                   "sequences_per_gpu": B, "context_tokens": w["T"], "group": GROUP,
-                   "rung_mix_16_8_4_2_c": list(w["probs"]), "sharding": (f"sp{world}: one sequence cut into byte-balanced block ranges, one all-gather of Hq*(D+2) floats per layer"
-                                if split else f"dp{world}: independent sequences, no collective"),
-                   "l2": f"inputs larger than L2: {cache_bytes / 1e9:.1f} GB of packed cache per GPU, each layer read once per step"},
+        "config": dict(workload_config(w, world, split, cache_bytes / 1e9), launch=launch_mode),
         "per_gpu": value / world,
         "hbm_gbs_per_gpu": achieved,
         "e2e": {"value": tokens_per_step / (ms_e2e / args.steps / 1e3), "unit": UNIT,
@@ -305,12 +330,17 @@ def cpu_baseline_from_cache(cache, q, w, max_seconds=25.0):
         gkv_oracle.mixed_attn_decode(*args)
         return time.perf_counter() - t0
     probe = run(1)
-    nseq = max(1, min(B, int(max_seconds * 0.6 / max(probe, 1e-6))))
-    dt = min(run(nseq) for _ in range(1)) if nseq > 1 else probe
+    nseq = max(1, min(B, int(max_seconds * 0.4 / max(probe, 1e-6))))
+    # repeat the pass until ~10 s of CPU work have been timed (at least once, at most max_seconds)
+    times, spent = [], 0.0
+    while not times or (spent < 10.0 and spent + times[-1] < max_seconds):
+        times.append(run(nseq))
+        spent += times[-1]
+    dt = sum(times) / len(times)
     tokens = nseq * w["T"] / w["layers"]          # one layer is 1/layers of a step over nseq sequences
     return {"value": tokens / dt, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
-            "sample": f"layer 0 of the workload, {nseq} of {B} sequences, all KV heads; one pass of the C oracle "
-                      f"({dt:.2f} s), scaled to a {w['layers']}-layer step"}
+            "sample": f"layer 0 of the workload, {nseq} of {B} sequences, all KV heads; mean of {len(times)} passes of the "
+                      f"C oracle ({spent:.1f} s in all), scaled to a {w['layers']}-layer step"}
 
 
 def run_reference(args):
@@ -323,14 +353,18 @@ def run_reference(args):
     sys.path.insert(0, str(ROOT / "tests"))
     import gkv_oracle
     gkv_oracle.build()
+    gkv_oracle.set_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every core
     w = WORKLOADS[args.workload]
     nb_full = w["T"] // 64
-    # bounded sample: ONE sequence, ONE layer, at most 256 blocks per head (the per-sequence
-    # block count of the 16k configs); packed on the CPU by the oracle itself.
+    # bounded sample: a few sequences (enough cache rows to occupy every host thread), ONE layer, at
+    # most 256 blocks per head (the per-sequence block count of the 16k configs); packed on the CPU
+    # by the oracle itself.
     nb = min(nb_full, 256)
+    nseq = min(w["B"], max(1, -(-2 * gkv_oracle.num_threads() // w["Hkv"])))
+    split = bool(w.get("split")) and args.gpus > 1
     rng = np.random.default_rng(1000)
     rows = []
-    for h in range(w["Hkv"]):
+    for h in range(nseq * w["Hkv"]):
         k = rng.standard_normal((nb, 64, w["D"]), dtype=np.float32)
         v = rng.standard_normal((nb, 64, w["D"]), dtype=np.float32)
         k[:, :, rng.permutation(w["D"])[:4]] *= 8.0
@@ -338,11 +372,11 @@ def run_reference(args):
         lv[0] = lv[-1] = 16
         rows.append(gkv_oracle.pack_row(k, v, lv, GROUP))
     stride = max(r["data"].size for r in rows)
-    data = np.zeros((1, w["Hkv"], stride), np.uint8)
+    data = np.zeros((nseq, w["Hkv"], stride), np.uint8)
     for h, r in enumerate(rows):
-        data[0, h, :r["data"].size] = r["data"]
-    st = lambda key: np.stack([r[key] for r in rows])[None]
-    q = rng.standard_normal((1, w["Hq"], w["D"]), dtype=np.float32) * np.float32(w["D"] ** -0.5)
+        data[h // w["Hkv"], h % w["Hkv"], :r["data"].size] = r["data"]
+    st = lambda key: (lambda a: a.reshape((nseq, w["Hkv"]) + a.shape[1:]))(np.stack([r[key] for r in rows]))
+    q = rng.standard_normal((nseq, w["Hq"], w["D"]), dtype=np.float32) * np.float32(w["D"] ** -0.5)
     call = lambda: gkv_oracle.mixed_attn_decode(q, data, st("offs"), st("klo"), st("kstep"), st("vlo"), st("vstep"),
                                                 st("level"), st("valid"), 64, GROUP)
     for _ in range(max(args.warmup, 1)):
@@ -351,16 +385,15 @@ def run_reference(args):
     for _ in range(args.steps):
         call()
     dt = (time.perf_counter() - t0) / args.steps
-    # one sample = nb*64 tokens of one layer; a step attends over `layers` layers
-    value = (nb * 64) / (dt * w["layers"])
-    sample = (f"1 sequence x 1 layer x {nb} blocks ({nb * 64} tokens) per step, all {w['Hkv']} KV heads, "
+    # one sample = nseq*nb*64 tokens of one layer; a step attends over `layers` layers
+    value = (nseq * nb * 64) / (dt * w["layers"])
+    sample = (f"{nseq} sequence(s) x 1 layer x {nb} blocks ({nb * 64} tokens each) per step, all {w['Hkv']} KV heads, "
               f"scaled to a {w['layers']}-layer step")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * w["layers"],
             "higher_is_better": True, "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "fp64 accumulate (C oracle)",
             "data": "synthetic",
-            "config": {"workload": w["name"], "layers": w["layers"], "q_heads": w["Hq"], "kv_heads": w["Hkv"],
-                       "head_dim": w["D"], "context_tokens": w["T"], "group": GROUP},
+            "config": workload_config(w, args.gpus, split),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
                              "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -377,6 +410,7 @@ def main():
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="time plain launches instead of a CUDA graph of the step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -69,9 +69,14 @@ def sequence_split_decode(q: torch.Tensor, cache, lo: int, hi: int, group: dist.
     ext = get_ext()
     if ext is None:
         raise RuntimeError("sequence_split_decode needs the CUDA extension; there is no CPU path")
-    sl = slice(lo, hi)
-    partial = ext.mixed_attn_decode_partial(
-        q, cache.data, cache.offs[..., sl].contiguous(), cache.klo[:, :, sl].contiguous(),
-        cache.kstep[:, :, sl].contiguous(), cache.vlo[:, :, sl].contiguous(), cache.vstep[:, :, sl].contiguous(),
-        cache.level[..., sl].contiguous(), cache.valid[..., sl].contiguous(), 64, cache.group)
+    if lo == 0 and hi == cache.offs.shape[-1] and cache.offs.is_contiguous():
+        # the rank holds exactly its own blocks: pass the tensors through (no slicing, no copies)
+        views = (cache.data, cache.offs, cache.klo, cache.kstep, cache.vlo, cache.vstep, cache.level, cache.valid)
+    else:
+        sl = slice(lo, hi)
+        views = (cache.data, cache.offs[..., sl].contiguous(), cache.klo[:, :, sl].contiguous(),
+                 cache.kstep[:, :, sl].contiguous(), cache.vlo[:, :, sl].contiguous(),
+                 cache.vstep[:, :, sl].contiguous(), cache.level[..., sl].contiguous(),
+                 cache.valid[..., sl].contiguous())
+    partial = ext.mixed_attn_decode_partial(q, *views, 64, cache.group)
     return gather_and_combine(partial, ext.combine_partials, group)
