@@ -50,6 +50,9 @@ namespace mma {
 #ifndef GKV_CTAS
 #define GKV_CTAS 2        // CTAs per SM
 #endif
+#ifndef GKV_K_FETCH
+#define GKV_K_FETCH 8     // widest shared-memory load used for a lane's codes of a K row (4, 8 or 16 bytes)
+#endif
 #ifndef GKV_RING_KB
 #define GKV_RING_KB 71    // byte ring per CTA
 #endif
@@ -666,7 +669,8 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     // once for 4- and 2-bit codes): a quarter warp then reads whole rows side by side, free of the
     // bank conflicts that one 4-byte load per chunk had (rows are 32-128 bytes apart).
     constexpr int CB = TB / C::CH;                       // code bytes per thread, row and chunk
-    constexpr int LB = TB < 16 ? TB : 16;                // bytes per fetch
+    constexpr int LB0 = TB < GKV_K_FETCH ? TB : GKV_K_FETCH;
+    constexpr int LB = LB0 < CB ? CB : LB0;              // bytes per fetch (at least one chunk)
     constexpr int CG = LB / CB;                          // chunks per fetch
     constexpr int LW = LB / 4;
     static_assert(LB >= 4 && C::CH % CG == 0, "unsupported shape");
