@@ -129,9 +129,12 @@ __global__ void __launch_bounds__(kDistThreads) distortion_kernel(DistParams p) 
     const int D = p.D, tid = threadIdx.x;
     const int kg = min(p.group, kP), vg = min(p.group, D);
     const int G = kP / kg, gv = D / vg;
-    float* sk = smem;                    // [64][D]
-    float* sv = sk + kP * D;             // [64][D]
-    float* rk = sv + kP * D;             // [G][D]   K ranges
+    // tile rows are padded by one float: several passes below walk a row per thread, and rows an
+    // exact multiple of 32 floats apart would all sit in one bank
+    const int ld = D + 1;
+    float* sk = smem;                    // [64][ld]
+    float* sv = sk + kP * ld;            // [64][ld]
+    float* rk = sv + kP * ld;            // [G][D]   K ranges
     float* rv = rk + G * D;              // [64][gv] V ranges
     float* mean = rv + kP * gv;          // [2][D]
     float* rad = mean + 2 * D;           // [2][64]
@@ -147,33 +150,51 @@ __global__ void __launch_bounds__(kDistThreads) distortion_kernel(DistParams p) 
     }
     const uint16_t* kb = reinterpret_cast<const uint16_t*>(p.data + (size_t)row * p.stride_bh + p.offs[mi]);
     const uint16_t* vb = kb + kP * D;
-    for (int e = tid; e < kP * D; e += kDistThreads) {
-        sk[e] = bf16_bits_to_float(kb[e]);
-        sv[e] = bf16_bits_to_float(vb[e]);
+    if ((reinterpret_cast<uintptr_t>(kb) & 15) == 0) {
+        const uint4* k8 = reinterpret_cast<const uint4*>(kb);
+        const uint4* v8 = reinterpret_cast<const uint4*>(vb);
+        for (int e8 = tid; e8 < kP * D / 8; e8 += kDistThreads) {        // D % 8 == 0: a load stays inside a row
+            const int t = (8 * e8) / D, d = 8 * e8 - t * D;
+            const uint4 a = k8[e8], b = v8[e8];
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                sk[t * ld + d + 2 * i] = bf16_bits_to_float(aw[i] & 0xffffu);
+                sk[t * ld + d + 2 * i + 1] = bf16_bits_to_float(aw[i] >> 16);
+                sv[t * ld + d + 2 * i] = bf16_bits_to_float(bw[i] & 0xffffu);
+                sv[t * ld + d + 2 * i + 1] = bf16_bits_to_float(bw[i] >> 16);
+            }
+        }
+    } else {
+        for (int e = tid; e < kP * D; e += kDistThreads) {
+            const int t = e / D, d = e - t * D;
+            sk[t * ld + d] = bf16_bits_to_float(kb[e]);
+            sv[t * ld + d] = bf16_bits_to_float(vb[e]);
+        }
     }
     __syncthreads();
     for (int u = tid; u < G * D; u += kDistThreads) {
         const int tg = u / D, d = u - tg * D;
         float lo = INFINITY, hi = -INFINITY;
-        for (int i = 0; i < kg; ++i) { const float x = sk[(tg * kg + i) * D + d]; lo = fminf(lo, x); hi = fmaxf(hi, x); }
+        for (int i = 0; i < kg; ++i) { const float x = sk[(tg * kg + i) * ld + d]; lo = fminf(lo, x); hi = fmaxf(hi, x); }
         rk[u] = __fsub_rn(hi, lo);
     }
     for (int u = tid; u < kP * gv; u += kDistThreads) {
         const int t = u / gv, cg = u - t * gv;
         float lo = INFINITY, hi = -INFINITY;
-        for (int i = 0; i < vg; ++i) { const float x = sv[t * D + cg * vg + i]; lo = fminf(lo, x); hi = fmaxf(hi, x); }
+        for (int i = 0; i < vg; ++i) { const float x = sv[t * ld + cg * vg + i]; lo = fminf(lo, x); hi = fmaxf(hi, x); }
         rv[u] = __fsub_rn(hi, lo);
     }
     for (int u = tid; u < 2 * D; u += kDistThreads) {
         const float* src = u < D ? sk + u : sv + (u - D);
         float s = 0.f;
-        for (int t = 0; t < kP; ++t) s = __fadd_rn(s, src[t * D]);
+        for (int t = 0; t < kP; ++t) s = __fadd_rn(s, src[t * ld]);
         mean[u] = __fdiv_rn(s, (float)kP);
     }
     __syncthreads();
     for (int u = tid; u < 2 * kP; u += kDistThreads) {
         const int which = u / kP, t = u - which * kP;
-        const float* src = (which ? sv : sk) + t * D;
+        const float* src = (which ? sv : sk) + t * ld;
         const float* mu = mean + which * D;
         float s = 0.f;
         for (int d = 0; d < D; ++d) { const float x = __fsub_rn(src[d], mu[d]); s = __fadd_rn(s, __fmul_rn(x, x)); }
@@ -245,8 +266,8 @@ int gkv_block_distortion(const uint8_t* data, const int64_t* offs, const int32_t
     p.per_row_meta = meta_rows != 1; p.value_weight = value_weight; p.stride_bh = stride_bh;
     const int kg = min(group, kP), vg = min(group, D);
     const int G = kP / kg, gv = D / vg;
-    const size_t smem = sizeof(float) * ((size_t)2 * kP * D + (size_t)G * D + (size_t)kP * gv + 2 * D + 2 * kP + 3 * G + 3 * kP);
-    const size_t smem_max = sizeof(float) * ((size_t)2 * kP * kMaxD + (size_t)kP * kMaxD + (size_t)kP * kMaxD + 2 * kMaxD + 2 * kP + 3 * kP + 3 * kP);
+    const size_t smem = sizeof(float) * ((size_t)2 * kP * (D + 1) + (size_t)G * D + (size_t)kP * gv + 2 * D + 2 * kP + 3 * G + 3 * kP);
+    const size_t smem_max = sizeof(float) * ((size_t)2 * kP * (kMaxD + 1) + (size_t)kP * kMaxD + (size_t)kP * kMaxD + 2 * kMaxD + 2 * kP + 3 * kP + 3 * kP);
     GKV_CUDA_TRY(cudaFuncSetAttribute(distortion_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)(smem_max > 227 * 1024 ? 227 * 1024 : smem_max)));
     if (smem > 227 * 1024) return GKV_E_SHAPE;

@@ -1,7 +1,8 @@
 // Pack, demote and unpack kernels for the bit-ladder block format.
 //
 // One CTA owns one block of one cache row.  The block's K and V are first brought into
-// shared memory as fp32 tiles (from dense inputs when packing, from the packed bytes at the
+// shared memory as fp32 tiles (rows padded by one float: the V groups are read along a row by
+// threads that sit a whole group apart, which without the pad would all hit one bank) (from dense inputs when packing, from the packed bytes at the
 // current rung when demoting — so no dense copy of the cache ever exists in global memory),
 // then re-expressed at the target rung with exactly the arithmetic of the reference's
 // quantize_codes (tests/test_cuda_kernel.py:18-33): fp32 min/max per group, step =
@@ -18,12 +19,29 @@ struct TileJob {
     uint8_t* dst;          // block start in the destination row
     __half* klo; __half* kstep; __half* vlo; __half* vstep;   // this block's scale planes
     int level, D, group, G, gv;
+    int ld;                // row stride of the fp32 tiles in floats
 };
 
-// Tiles: sk, sv hold [64][D] fp32.  scode is a [64][D] byte scratch.
+__host__ __device__ __forceinline__ int tile_ld(int D) { return D + 1; }
+
+// code = clamp(rint((x - lo) / step), 0, qmax) with the quotient rounded as IEEE division rounds it.
+// A correctly rounded division is ~10 instructions; the product with a reciprocal is within a
+// few ulp of it (absolute error < 1e-4 for quotients up to 255), so it rounds to the same integer
+// unless it lands within 1e-3 of a tie, and only then is the exact division needed.
+__device__ __forceinline__ uint8_t exact_code(float x, float lf, float sf, float rs, float qmax) {
+    const float a = __fsub_rn(x, lf);
+    float q = __fmul_rn(a, rs);
+    const float fr = q - floorf(q);
+    if (!(fabsf(fr - 0.5f) > 1e-3f) || !(fabsf(q) < 1e6f)) q = __fdiv_rn(a, sf);    // near a tie, huge, or NaN
+    float c = rintf(q);
+    c = (c != c) ? 0.f : fminf(fmaxf(c, 0.f), qmax);
+    return (uint8_t)c;
+}
+
+// Tiles: sk, sv hold [64][ld] fp32.  scode is a dense [64][D] byte scratch.
 __device__ void quantize_tile_and_store(const TileJob& j, const float* __restrict__ sk,
                                         const float* __restrict__ sv, uint8_t* __restrict__ scode) {
-    const int tid = threadIdx.x, D = j.D, lv = j.level;
+    const int tid = threadIdx.x, D = j.D, lv = j.level, ld = j.ld;
     const int hb = half_bytes(lv, D);
     const bool scales_needed = (lv == 8 || lv == 4 || lv == 2);
     if (!scales_needed) {
@@ -34,9 +52,13 @@ __device__ void quantize_tile_and_store(const TileJob& j, const float* __restric
     if (lv == 16) {
         __nv_bfloat16* ko = reinterpret_cast<__nv_bfloat16*>(j.dst);
         __nv_bfloat16* vo = reinterpret_cast<__nv_bfloat16*>(j.dst + hb);
-        for (int i = tid; i < kP * D; i += kPackThreads) {
-            ko[i] = __float2bfloat16_rn(sk[i]);
-            vo[i] = __float2bfloat16_rn(sv[i]);
+        // two channels per thread and store
+        __nv_bfloat162* ko2 = reinterpret_cast<__nv_bfloat162*>(ko);
+        __nv_bfloat162* vo2 = reinterpret_cast<__nv_bfloat162*>(vo);
+        for (int i = tid; i < kP * D / 2; i += kPackThreads) {
+            const int t = (2 * i) / D, d = 2 * i - t * D;
+            ko2[i] = __floats2bfloat162_rn(sk[t * ld + d], sk[t * ld + d + 1]);
+            vo2[i] = __floats2bfloat162_rn(sv[t * ld + d], sv[t * ld + d + 1]);
         }
         return;
     }
@@ -47,7 +69,7 @@ __device__ void quantize_tile_and_store(const TileJob& j, const float* __restric
         for (int d = tid; d < 2 * D; d += kPackThreads) {
             const float* src = d < D ? sk + d : sv + (d - D);
             float s = 0.f;
-            for (int t = 0; t < kP; ++t) s = __fadd_rn(s, src[t * D]);
+            for (int t = 0; t < kP; ++t) s = __fadd_rn(s, src[t * ld]);
             const __half h = __float2half_rn(__fdiv_rn(s, (float)kP));
             if (d < D) ko[d] = h; else vo[d - D] = h;
         }
@@ -64,18 +86,16 @@ __device__ void quantize_tile_and_store(const TileJob& j, const float* __restric
                 const int tg = u / D, d = u - tg * D;
                 float lo = INFINITY, hi = -INFINITY;
                 for (int i = 0; i < g; ++i) {
-                    const float x = src[(tg * g + i) * D + d];
+                    const float x = src[(tg * g + i) * ld + d];
                     lo = fminf(lo, x); hi = fmaxf(hi, x);
                 }
                 const float step = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), qmax);
                 const __half l16 = __float2half_rn(lo), s16 = __float2half_rn(step);
                 j.klo[u] = l16; j.kstep[u] = s16;
-                const float lf = __half2float(l16), sf = __half2float(s16);
+                const float lf = __half2float(l16), sf = __half2float(s16), rs = __frcp_rn(sf);
                 for (int i = 0; i < g; ++i) {
-                    const int e = (tg * g + i) * D + d;
-                    float c = rintf(__fdiv_rn(__fsub_rn(src[e], lf), sf));
-                    c = (c != c) ? 0.f : fminf(fmaxf(c, 0.f), qmax);
-                    scode[e] = (uint8_t)c;
+                    const int t = tg * g + i;
+                    scode[t * D + d] = exact_code(src[t * ld + d], lf, sf, rs, qmax);
                 }
             }
         } else {
@@ -85,27 +105,39 @@ __device__ void quantize_tile_and_store(const TileJob& j, const float* __restric
                 const int t = u / j.gv, cg = u - t * j.gv;
                 float lo = INFINITY, hi = -INFINITY;
                 for (int i = 0; i < g; ++i) {
-                    const float x = src[t * D + cg * g + i];
+                    const float x = src[t * ld + cg * g + i];
                     lo = fminf(lo, x); hi = fmaxf(hi, x);
                 }
                 const float step = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), qmax);
                 const __half l16 = __float2half_rn(lo), s16 = __float2half_rn(step);
                 j.vlo[u] = l16; j.vstep[u] = s16;
-                const float lf = __half2float(l16), sf = __half2float(s16);
+                const float lf = __half2float(l16), sf = __half2float(s16), rs = __frcp_rn(sf);
                 for (int i = 0; i < g; ++i) {
-                    const int e = t * D + cg * g + i;
-                    float c = rintf(__fdiv_rn(__fsub_rn(src[e], lf), sf));
-                    c = (c != c) ? 0.f : fminf(fmaxf(c, 0.f), qmax);
-                    scode[e] = (uint8_t)c;
+                    const int d = cg * g + i;
+                    scode[t * D + d] = exact_code(src[t * ld + d], lf, sf, rs, qmax);
                 }
             }
         }
         __syncthreads();
         uint8_t* out = j.dst + which * hb;
-        for (int o = tid; o < hb; o += kPackThreads) {
-            uint32_t byte = 0;
-            for (int i = 0; i < per; ++i) byte |= (uint32_t)scode[o * per + i] << (i * lv);
-            out[o] = (uint8_t)byte;
+        if ((reinterpret_cast<uintptr_t>(out) & 3) == 0) {
+            // four output bytes per thread and store (hb is a multiple of 4 for every D % 8 == 0)
+            uint32_t* out4 = reinterpret_cast<uint32_t*>(out);
+            for (int w = tid; w < hb / 4; w += kPackThreads) {
+                uint32_t word = 0;
+                for (int b = 0; b < 4; ++b) {
+                    uint32_t byte = 0;
+                    for (int i = 0; i < per; ++i) byte |= (uint32_t)scode[(4 * w + b) * per + i] << (i * lv);
+                    word |= byte << (8 * b);
+                }
+                out4[w] = word;
+            }
+        } else {
+            for (int o = tid; o < hb; o += kPackThreads) {
+                uint32_t byte = 0;
+                for (int i = 0; i < per; ++i) byte |= (uint32_t)scode[o * per + i] << (i * lv);
+                out[o] = (uint8_t)byte;
+            }
         }
         __syncthreads();
     }
@@ -114,7 +146,7 @@ __device__ void quantize_tile_and_store(const TileJob& j, const float* __restric
 // Exact dequantisation of one block into the fp32 tiles (mixed_attn.cu:93-159).
 __device__ void dequant_block_to_tiles(const uint8_t* __restrict__ blk, int lv, int D, int group, int gv,
                                        const __half* klo, const __half* kstep, const __half* vlo,
-                                       const __half* vstep, float* sk, float* sv) {
+                                       const __half* vstep, float* sk, float* sv, int ld) {
     const uint8_t* vb = blk + half_bytes(lv, D);
     for (int e = threadIdx.x; e < kP * D; e += blockDim.x) {
         const int t = e / D, d = e - t * D;
@@ -130,8 +162,8 @@ __device__ void dequant_block_to_tiles(const uint8_t* __restrict__ blk, int lv, 
             kx = __fmaf_rn((float)unpack_code(blk, e, lv), __half2float(kstep[ks]), __half2float(klo[ks]));
             vx = __fmaf_rn((float)unpack_code(vb, e, lv), __half2float(vstep[vs]), __half2float(vlo[vs]));
         }
-        sk[e] = kx;
-        sv[e] = vx;
+        sk[t * ld + d] = kx;
+        sv[t * ld + d] = vx;
     }
 }
 
@@ -153,9 +185,10 @@ __device__ __forceinline__ float load_src(const void* p, int dtype, size_t i) {
 __global__ void __launch_bounds__(kPackThreads) pack_blocks_kernel(PackParams p) {
     extern __shared__ float smem[];
     const int D = p.D;
+    const int ld = tile_ld(D);
     float* sk = smem;
-    float* sv = sk + kP * D;
-    uint8_t* scode = reinterpret_cast<uint8_t*>(sv + kP * D);
+    float* sv = sk + kP * ld;
+    uint8_t* scode = reinterpret_cast<uint8_t*>(sv + kP * ld);
     const int blk = p.b_lo + blockIdx.x, row = blockIdx.y;
     const int mrow = p.per_row_meta ? row : 0;
     const int lv = p.level[(size_t)mrow * p.nb + blk];
@@ -163,11 +196,36 @@ __global__ void __launch_bounds__(kPackThreads) pack_blocks_kernel(PackParams p)
     int nvalid = p.valid ? p.valid[(size_t)mrow * p.nb + blk] : kP;
     nvalid = max(1, min(nvalid, kP));
     const size_t src0 = ((size_t)row * p.nb + blk) * kP * D;
-    for (int e = threadIdx.x; e < kP * D; e += kPackThreads) {
-        const int t = e / D, d = e - t * D;
-        const int ts = min(t, nvalid - 1);               // pad by repeating the last real row
-        sk[e] = load_src(p.k, p.src_dtype, src0 + (size_t)ts * D + d);
-        sv[e] = load_src(p.v, p.src_dtype, src0 + (size_t)ts * D + d);
+    const bool vec16 = p.src_dtype != 0 && ((reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0;
+    if (vec16) {
+        // eight 16-bit elements per load (D % 8 == 0, so a load never straddles a row)
+        const uint4* k8 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.k) + src0);
+        const uint4* v8 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.v) + src0);
+        for (int e8 = threadIdx.x; e8 < kP * D / 8; e8 += kPackThreads) {
+            const int t = (8 * e8) / D, d = 8 * e8 - t * D;
+            const int ts = min(t, nvalid - 1);           // pad by repeating the last real row
+            const uint4 a = k8[(ts * D + d) / 8], b = v8[(ts * D + d) / 8];
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint16_t a0 = (uint16_t)(aw[i] & 0xffffu), a1 = (uint16_t)(aw[i] >> 16);
+                const uint16_t b0 = (uint16_t)(bw[i] & 0xffffu), b1 = (uint16_t)(bw[i] >> 16);
+                if (p.src_dtype == 1) {
+                    sk[t * ld + d + 2 * i] = bf16_bits_to_float(a0); sk[t * ld + d + 2 * i + 1] = bf16_bits_to_float(a1);
+                    sv[t * ld + d + 2 * i] = bf16_bits_to_float(b0); sv[t * ld + d + 2 * i + 1] = bf16_bits_to_float(b1);
+                } else {
+                    sk[t * ld + d + 2 * i] = half_bits_to_float(a0); sk[t * ld + d + 2 * i + 1] = half_bits_to_float(a1);
+                    sv[t * ld + d + 2 * i] = half_bits_to_float(b0); sv[t * ld + d + 2 * i + 1] = half_bits_to_float(b1);
+                }
+            }
+        }
+    } else {
+        for (int e = threadIdx.x; e < kP * D; e += kPackThreads) {
+            const int t = e / D, d = e - t * D;
+            const int ts = min(t, nvalid - 1);           // pad by repeating the last real row
+            sk[t * ld + d] = load_src(p.k, p.src_dtype, src0 + (size_t)ts * D + d);
+            sv[t * ld + d] = load_src(p.v, p.src_dtype, src0 + (size_t)ts * D + d);
+        }
     }
     __syncthreads();
     TileJob j;
@@ -175,7 +233,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_blocks_kernel(PackParams p)
     const size_t sb = (size_t)row * p.nb + blk;
     j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
     j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
-    j.level = lv; j.D = D; j.group = p.group; j.G = p.G; j.gv = p.gv;
+    j.level = lv; j.D = D; j.group = p.group; j.G = p.G; j.gv = p.gv; j.ld = ld;
     quantize_tile_and_store(j, sk, sv, scode);
 }
 
@@ -190,9 +248,10 @@ struct DemoteParams {
 __global__ void __launch_bounds__(kPackThreads) demote_blocks_kernel(DemoteParams p) {
     extern __shared__ float smem[];
     const int D = p.D;
+    const int ld = tile_ld(D);
     float* sk = smem;
-    float* sv = sk + kP * D;
-    uint8_t* scode = reinterpret_cast<uint8_t*>(sv + kP * D);
+    float* sv = sk + kP * ld;
+    uint8_t* scode = reinterpret_cast<uint8_t*>(sv + kP * ld);
     const int blk = blockIdx.x, row = blockIdx.y;
     const int mrow = p.per_row_meta ? row : 0;
     const size_t mi = (size_t)mrow * p.nb + blk;
@@ -203,10 +262,10 @@ __global__ void __launch_bounds__(kPackThreads) demote_blocks_kernel(DemoteParam
     j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
     j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
     dequant_block_to_tiles(p.data_old + (size_t)row * p.stride_old + p.offs_old[mi], lo, D, p.group, p.gv,
-                           j.klo, j.kstep, j.vlo, j.vstep, sk, sv);
+                           j.klo, j.kstep, j.vlo, j.vstep, sk, sv, ld);
     __syncthreads();
     j.dst = p.data_new + (size_t)row * p.stride_new + p.offs_new[mi];
-    j.level = ln; j.D = D; j.group = p.group; j.G = p.G; j.gv = p.gv;
+    j.level = ln; j.D = D; j.group = p.group; j.G = p.G; j.gv = p.gv; j.ld = ld;
     quantize_tile_and_store(j, sk, sv, scode);
 }
 
@@ -227,10 +286,10 @@ __global__ void __launch_bounds__(kPackThreads) unpack_blocks_kernel(UnpackParam
     const size_t sb = (size_t)row * p.nb + blk;
     dequant_block_to_tiles(p.data + (size_t)row * p.stride_bh + p.offs[mi], lv, D, p.group, p.gv,
                            p.klo + sb * p.G * D, p.kstep + sb * p.G * D, p.vlo + sb * kP * p.gv,
-                           p.vstep + sb * kP * p.gv, p.k_out + sb * kP * D, p.v_out + sb * kP * D);
+                           p.vstep + sb * kP * p.gv, p.k_out + sb * kP * D, p.v_out + sb * kP * D, D);
 }
 
-static size_t tile_smem(int D) { return (size_t)kP * D * (2 * sizeof(float) + 1); }
+static size_t tile_smem(int D) { return (size_t)kP * (2 * tile_ld(D) * sizeof(float) + D); }
 
 static int set_smem(const void* fn, size_t bytes) {
     GKV_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
