@@ -367,7 +367,7 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     long long p_all = clock64(), p_wait = 0, p_issue = 0, p_meta = 0, p_scale = 0, p_n = 0;
 #endif
 
-    auto release_oldest = [&]() -> bool {     // lane 0 only
+    auto release_oldest = [&]() -> bool {     // all lanes, same result everywhere
         const int s = seq_free % kNSlot;
         if (!mbar_wait(&sm.empty[s], (uint32_t)(seq_free / kNSlot) & 1u)) return false;
         used -= (uint32_t)sm.desc[s].pad;
@@ -434,61 +434,56 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         p_meta += clock64() - _pm0;
 #endif
         for (int j = 0; j < nblk && ok; ++j, ++seq_alloc) {
+            // Ring bookkeeping is done by all lanes alike (same values everywhere, so nothing has to be
+            // broadcast); only the three operations with side effects are lane 0's.
             const uint4 cur = tab[j];
             const int lvj = (int)(cur.z & 0xffu), orig = (int)cur.w;
             const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
             const uint32_t dbytes = lvj ? 2u * (uint32_t)half_bytes(lvj, D) : 0u;
             const int slot = seq_alloc % kNSlot;
-            uint32_t res = 0;                                   // lane 0: ring offset | 1 << 31
+            const uint32_t need = (dbytes + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u) + 127u) & ~127u;
+#ifdef GKV_DBG_TIMING
+            const long long _pw0 = clock64();
+#endif
+            while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
+            const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
+            while (ok && used + waste + need > kRingBytes) ok = release_oldest();
+#ifdef GKV_DBG_TIMING
+            const long long _pi0 = clock64();
+            p_wait += _pi0 - _pw0; ++p_n;
+#endif
+            if (!ok) break;
+            const uint32_t dst = waste ? 0u : head;
+            used += waste + need;
+            head = dst + need;
+            if (head >= kRingBytes) head = 0;
             if (lane == 0) {
-                const uint32_t need = (dbytes + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u) + 127u) & ~127u;
-#ifdef GKV_DBG_TIMING
-                const long long _pw0 = clock64();
-#endif
-                while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
-                const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
-                while (ok && used + waste + need > kRingBytes) ok = release_oldest();
-#ifdef GKV_DBG_TIMING
-                const long long _pi0 = clock64();
-                p_wait += _pi0 - _pw0; ++p_n;
-#endif
-                if (ok) {
-                    const uint32_t dst = waste ? 0u : head;
-                    used += waste + need;
-                    head = dst + need;
-                    if (head >= kRingBytes) head = 0;
-                    Desc d;
-                    d.off = dst; d.level = lvj; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)(waste + need);
-                    sm.desc[slot] = d;
-                    const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
-                    uint8_t* d0 = sm.ring + dst;
+                Desc d;
+                d.off = dst; d.level = lvj; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)(waste + need);
+                sm.desc[slot] = d;
+                const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
+                uint8_t* d0 = sm.ring + dst;
 #ifdef GKV_DBG_NOLOAD
-                    if (true) { mbar_arrive(&sm.full[slot]); } else
+                if (true) { mbar_arrive(&sm.full[slot]); } else
 #endif
-                    if (lvj && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                        mbar_arrive_tx(&sm.full[slot], dbytes);
-                        bulk_g2s(d0, src, dbytes, &sm.full[slot]);
-                    } else {
-                        // block start not 16-byte aligned (a cache row at an odd address): no bulk copy,
-                        // this lane copies the bytes by hand
-                        for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
-                        __threadfence_block();
-                        mbar_arrive(&sm.full[slot]);
-                    }
-                    res = dst | 0x80000000u;
+                if (lvj && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                    mbar_arrive_tx(&sm.full[slot], dbytes);
+                    bulk_g2s(d0, src, dbytes, &sm.full[slot]);
+                } else {
+                    // block start not 16-byte aligned (a cache row at an odd address): no bulk copy,
+                    // this lane copies the bytes by hand
+                    for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
+                    __threadfence_block();
+                    mbar_arrive(&sm.full[slot]);
                 }
-#ifdef GKV_DBG_TIMING
-                p_issue += clock64() - _pi0;
-#endif
             }
 #ifdef GKV_DBG_TIMING
             const long long _ps0 = clock64();
+            p_issue += _ps0 - _pi0;
 #endif
-            res = __shfl_sync(0xffffffffu, res, 0);
-            if (!(res >> 31)) { ok = false; break; }
 #ifndef GKV_DBG_NOLOAD
             if (quant) {
-                const uint32_t sdst = smem_u32(sm.ring) + (res & 0x7fffffffu) + dbytes;
+                const uint32_t sdst = smem_u32(sm.ring) + dst + dbytes;
                 const size_t ko = (size_t)orig * C::KSCALE, vo = (size_t)orig * C::VSCALE;
                 constexpr int K = C::KSCALE, V = C::VSCALE;
 #pragma unroll
