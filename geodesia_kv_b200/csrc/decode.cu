@@ -116,6 +116,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
 // ---- split plan -------------------------------------------------------------------------------
 struct Plan {
     int nsplit, bps;      // work items per cache row, blocks per item
+    int bps2, nbig;       // tensor-core kernel: the first nbig items of a row take bps blocks, the rest bps2
     int parts;            // records per cache row and query head (the tensor-core kernel writes one per consumer warp)
     int segs;             // > 1: the merge runs in two levels, `segs` partial merges per output row first
     bool mma;             // tensor-core kernel (persistent, work items of `bps` blocks)
@@ -123,7 +124,7 @@ struct Plan {
 };
 
 constexpr size_t kHeaderBytes = 256;   // work counter + status word in front of the records
-constexpr int kCombineDirect = 64;     // up to this many records per output row one CTA merges them all
+constexpr int kCombineDirect = 256;    // up to this many records per output row one CTA merges them all
 constexpr int kCombineSegs = 32;       // above it: this many CTAs per row merge a slice each, then one merges those
 
 static bool mma_shape_ok(int D, int group, int rep) {
@@ -149,10 +150,23 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
             const int v = atoi(e);
             if (v >= 1 && v <= 32) chunk = v;
         }
-        pl.bps = chunk;
-        pl.nsplit = nb > 0 ? (nb + chunk - 1) / chunk : 1;
+        // The last part of every row's (rung-sorted) list goes out in half-size items: items are
+        // handed out chunk-major, so these are the last items of the grid, and the spread of the
+        // CTAs' finishing times is about one item.
+        int tail_pct = 0;
+        if (const char* e = getenv("GKV_DECODE_TAIL")) {       // tuning knob: percent of a row in half-size items
+            const int v = atoi(e);
+            if (v >= 0 && v <= 100) tail_pct = v;
+        }
+        int chunk2 = chunk / 2 < nw ? nw : chunk / 2;
+        if (chunk2 > chunk) chunk2 = chunk;
+        int nbig = nb > 0 ? (int)(((long)nb * (100 - tail_pct) / 100) / chunk) : 0;
+        if (nb / chunk < 4) nbig = (nb + chunk - 1) / chunk;   // short rows: uniform items
+        const int rest = nb - nbig * chunk > 0 ? nb - nbig * chunk : 0;
+        pl.bps = chunk; pl.bps2 = chunk2; pl.nbig = nbig;
+        pl.nsplit = nb > 0 ? nbig + (rest + chunk2 - 1) / chunk2 : 1;
         pl.parts = pl.nsplit * mma::kConsumerWarps;
-        pl.segs = pl.parts > kCombineDirect ? kCombineSegs : 1;
+        pl.segs = pl.parts > kCombineDirect ? (pl.parts / 64 < kCombineSegs ? pl.parts / 64 : kCombineSegs) : 1;
         const long items = (long)rows * pl.nsplit;
         if (items < pl.grid) pl.grid = (int)(items > 0 ? items : 1);
         return pl;
@@ -166,6 +180,7 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
     pl.parts = pl.nsplit;
     pl.segs = 1;
     pl.grid = 0;
+    pl.bps2 = pl.bps; pl.nbig = pl.nsplit;
     return pl;
 }
 
@@ -234,7 +249,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
         mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);
         mp.level = level; mp.valid = valid; mp.part = records; mp.counter = header; mp.status = header + 1;
-        mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps;
+        mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps; mp.chunk2 = pl.bps2; mp.nbig = pl.nbig;
         mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
         mp.stride_bh = stride_bh;
         int rc;

@@ -95,7 +95,8 @@ struct Params {
     int* counter;       // work-item counter (zeroed before launch)
     int* status;        // error word (zeroed before launch)
     int B, Hq, Hkv, nb, rep;
-    int chunk;          // blocks per item
+    int chunk;          // blocks per item for the first nbig chunks of a row's sorted list ...
+    int chunk2, nbig;   // ... and for the chunks after them (smaller items at the end trim the tail of the grid)
     int items_per_row, items;
     int per_row_meta;
     int rows;
@@ -286,8 +287,9 @@ struct Smem {
 struct Span { int row, b_lo, nblk; };
 __device__ __forceinline__ Span span_of(const Params& p, int it) {
     if (it >= p.items) return Span{0, 0, 0};
-    const int b_lo = (it / p.rows) * p.chunk;
-    return Span{it % p.rows, b_lo, min(p.chunk, p.nb - b_lo)};     // nblk <= 32
+    const int c = it / p.rows;
+    const int b_lo = c < p.nbig ? c * p.chunk : p.nbig * p.chunk + (c - p.nbig) * p.chunk2;
+    return Span{it % p.rows, b_lo, min(c < p.nbig ? p.chunk : p.chunk2, p.nb - b_lo)};     // nblk <= 32
 }
 
 // ---- rung-sorted block lists -----------------------------------------------------------------------
