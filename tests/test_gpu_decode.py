@@ -175,6 +175,30 @@ def test_blocks_with_zero_valid_tokens_are_skipped(ext, oracle):
     assert np.abs(got - want).max() < 5e-5
 
 
+def test_long_rows_with_scattered_skips_and_every_item_size(ext, oracle, monkeypatch):
+    """Rows longer than one plan-kernel pass per thread (nb > 1024), different rung vectors per row,
+    blocks with no valid tokens sprinkled in, and several work-item sizes (records per row on both
+    sides of the one-level / two-level merge switch)."""
+    B, Hq, Hkv, nb, D, group = 1, 8, 2, 1100, 64, 32
+    c = oracle_cache(oracle, 321, B, Hkv, nb, D, group, last_valid=13)
+    rng = np.random.default_rng(5)
+    c["valid"][0, 0, rng.permutation(nb - 1)[:60]] = 0
+    c["valid"][0, 1, rng.permutation(nb - 1)[:7]] = 0
+    q = rng.standard_normal((B, Hq, D), dtype=np.float32) * np.float32(D ** -0.5)
+    want = oracle.mixed_attn_decode(q, *oracle_args(c))
+    for chunk in (None, "4", "9", "32"):
+        if chunk is None:
+            monkeypatch.delenv("GKV_DECODE_CHUNK", raising=False)
+        else:
+            monkeypatch.setenv("GKV_DECODE_CHUNK", chunk)
+        got = run(ext, q, to_torch(c, "cuda"), c)
+        assert np.abs(got - want).max() < 5e-5, chunk
+    monkeypatch.setenv("GKV_DECODE_CHUNK", "8")
+    monkeypatch.setenv("GKV_DECODE_TAIL", "40")
+    got = run(ext, q, to_torch(c, "cuda"), c)
+    assert np.abs(got - want).max() < 5e-5
+
+
 def test_sequence_split_partials_recombine(ext, oracle):
     """Each 'rank' attends over a slice of the blocks; the LSE merge of the (m, l, o) records
     must equal one pass over the whole row (the multi-GPU path of the 1M-token config)."""
