@@ -284,7 +284,9 @@ def run_gpu(args):
         try:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # thread-local capture mode: other threads of the process (the collective library's
+            # watchdog, the clock sampler) may touch CUDA while this thread captures
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 step_resident()
             graph.replay()
             torch.cuda.synchronize()
@@ -305,7 +307,7 @@ def run_gpu(args):
         # the host still waits for the outputs of every step
         try:
             graph_e2e = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph_e2e):
+            with torch.cuda.graph(graph_e2e, capture_error_mode="thread_local"):
                 step_e2e_body()
 
             def run_e2e():
