@@ -43,6 +43,8 @@ WORKLOADS = {
                        name="profiling-sized slice of the qwen3-8b-shape workload: 2 layers, 8 seq x 16384 tok"),
     "cfg0": dict(layers=64, Hq=16, Hkv=2, D=128, B=1, T=16384, probs=(0.10, 0.20, 0.40, 0.20, 0.10),
                  name="qwen2.5-3b-shape single-sequence layer, 64 distinct layer buffers of 16384 tok"),
+    "cfg3-small": dict(layers=4, Hq=28, Hkv=4, D=128, B=1, T=131072, probs=(0.02, 0.08, 0.30, 0.40, 0.20), split=True,
+                       name="profiling-sized slice of the qwen2.5-7b-1m-shape workload: 4 layers, 1 seq x 131072 tok"),
     "cfg3": dict(layers=28, Hq=28, Hkv=4, D=128, B=1, T=1048576, probs=(0.02, 0.08, 0.30, 0.40, 0.20), split=True,
                  name="qwen2.5-7b-1m-shape decode attention, 28 layers, 1 seq x 1048576 tok"),
 }
@@ -280,7 +282,7 @@ def run_gpu(args):
     # The sequence-split step, whose all-gather would have to be captured too, always runs eagerly.
     launch_mode = "eager"
     run_step = step_resident
-    if not args.eager and not split:      # a step with the all-gather inside is not captured (see --eager)
+    if not args.eager and not split:      # a step with the all-gather inside is never captured (it hung here, twice)
         try:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
