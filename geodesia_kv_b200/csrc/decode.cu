@@ -143,7 +143,7 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
         pl.grid = mma::kCtasPerSM * kNumSM;
         const long total = (long)rows * nb;
         const int nw = mma::kConsumerWarps;
-        int chunk = (int)(total / ((long)pl.grid * 8));
+        int chunk = (int)(total / ((long)pl.grid * 6));      // ~6 items per CTA; larger items measured faster than finer balance
         if (chunk < nw) chunk = nw;
         if (chunk > 32) chunk = 32;                      // the producer's metadata table holds 32 blocks
         if (const char* e = getenv("GKV_DECODE_CHUNK")) {      // tuning knob: blocks per work item
