@@ -10,7 +10,8 @@
 //
 // Structure (one CTA = 4 consumer warps + a producer warp + a query warp, two CTAs per SM,
 // persistent):
-//   * work items are (cache row, chunk of consecutive blocks), handed out by an atomic
+//   * a small kernel first sorts every row's blocks by rung; work items are (cache row, run of
+//     up to 32 entries of that sorted list), numbered chunk-major and handed out by an atomic
 //     counter; every item ends in one (m, l, o) record per consumer warp and query head;
 //   * the producer warp streams each block's bytes and its four scale planes into a byte
 //     ring in shared memory with cp.async.bulk + mbarrier (non-multicast), several blocks
@@ -36,7 +37,7 @@
 //   p . (c*step + lo) = (p*step) . c + p . lo        (per token, per channel group)
 // The small operands q*step and p*step are split into fp16 hi + lo halves that ride in the
 // otherwise unused MMA rows 8..15 (the GQA group is at most 8 heads), giving ~22 significant
-// bits; the lo terms are two tiny extra MMAs.  Accumulation is fp32 throughout.
+// bits; the lo terms ride along as one more n-tile on each side.  Accumulation is fp32 throughout.
 #pragma once
 
 #include "gkv_common.cuh"
