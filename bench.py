@@ -342,7 +342,7 @@ def run_gpu(args):
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": launches * (ext.lib.gkv_decode_kernel_launches(B, Hq, w["Hkv"], D, caches[0].nb, GROUP) + (1 if split else 0)),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}",
+                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
                      "traffic": (bytes_per_launch * DRAM_TRAFFIC_RATIO[args.workload]
                                  if args.workload in DRAM_TRAFFIC_RATIO and not split else None),
                      "kernel": "decode split kernel (+ its LSE combine, timed together)",
