@@ -52,7 +52,7 @@ namespace mma {
 #define GKV_CTAS 2        // CTAs per SM
 #endif
 #ifndef GKV_K_FETCH
-#define GKV_K_FETCH 8     // widest shared-memory load used for a lane's codes of a K row (4, 8 or 16 bytes)
+#define GKV_K_FETCH 16    // widest shared-memory load used for a lane's codes of a K row (4, 8 or 16 bytes)
 #endif
 #ifndef GKV_RING_KB
 #define GKV_RING_KB 71    // byte ring per CTA
@@ -60,7 +60,24 @@ namespace mma {
 constexpr int kConsumerWarps = GKV_NW;
 constexpr int kCtasPerSM = GKV_CTAS;
 constexpr int kConsumers = kConsumerWarps * 32;
+#if GKV_NW == 4 && GKV_CTAS == 2 && !defined(GKV_NO_REG_SHIFT) && !defined(GKV_REG_SHIFT)
+#define GKV_REG_SHIFT 1
+#endif
+#ifdef GKV_REG_SHIFT
+// Register re-allocation between warpgroups (setmaxnreg): the CTA is two full warpgroups, the
+// consumers' and a helper one (producer warp, query warp, two warps that leave at once); the
+// helpers hand most of their registers to the consumers (200 instead of 168 each: enough to keep
+// the whole K loop of a unit unrolled with its loads in flight, measured +4 %).  Launched with 128
+// registers per thread, two CTAs per SM.
+constexpr int kThreads = kConsumers + 128;
+#ifndef GKV_HELPER_REGS
+#define GKV_HELPER_REGS 56
+#endif
+constexpr int kHelperRegs = GKV_HELPER_REGS, kConsumerRegs = 256 - GKV_HELPER_REGS;   // 128 * (helper + consumer) = 256 threads * 128 registers at launch
+static_assert(kConsumerWarps == 4, "the consumers must be exactly one warpgroup");
+#else
 constexpr int kThreads = kConsumers + 64;    // + producer warp + query warp
+#endif
 static_assert(kConsumerWarps % 2 == 0, "consumer warps work in pairs");
 constexpr int kNSlot = kConsumerWarps <= 4 ? 16 : 32;   // descriptor slots (blocks in flight per CTA)
 constexpr uint32_t kRingBytes = GKV_RING_KB * 1024;
@@ -681,7 +698,11 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     // group's klo (so every thread ends up with its own head's value, no shuffle); two accumulators,
     // one per k-step of a chunk, keep the MMAs independent.
     float bias0[4] = {0.f, 0.f, 0.f, 0.f}, bias1[4] = {0.f, 0.f, 0.f, 0.f};
+#ifndef GKV_K_ROLLED
+#pragma unroll
+#else
 #pragma unroll 1
+#endif
     for (int g = 0; g < C::CH / CG; ++g) {
         uint32_t W[UU::NU][LW];
 #pragma unroll
@@ -1236,6 +1257,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+#ifdef GKV_REG_SHIFT
+    if (threadIdx.x < kConsumers) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
+    if (threadIdx.x >= kConsumers + 64) return;
+#endif
     if (threadIdx.x < kConsumers) consumer_loop<D, G>(p, sm, &abort_flag);
     else if (threadIdx.x < kConsumers + 32) producer_loop<D, G>(p, sm, &abort_flag);
     else query_loop<D, G>(p, sm, &abort_flag);
