@@ -58,7 +58,7 @@ UNIT = "context-tokens/s"
 # capture summarised in profiles/decode_mma_cfg1-small_ncu.md (dram read + write of one launch of
 # the profiling-sized slice over its algorithmic bytes).  Traffic grows with the number of blocks,
 # so a full-size launch is that ratio times its own algorithmic bytes.
-DRAM_TRAFFIC_RATIO = {"cfg1": 1.058, "cfg1-small": 1.058}
+DRAM_TRAFFIC_RATIO = {"cfg1": 1.046, "cfg1-small": 1.046}
 
 
 def workload_config(w, world, split, cache_gb=None):
