@@ -22,9 +22,19 @@ SIGNATURES = {
     "gkv_last_cuda_error": (_i, []),
     "gkv_decode_workspace_bytes": (_sz, [_i] * 5),
     "gkv_decode_kernel_launches": (_i, [_i] * 6),
+    "gkv_decode_launch_count": (_i, [_i] * 7),
+    "gkv_set_decode_kernel": (_i, [_i]),
+    "gkv_set_decode_item_blocks": (_i, [_i]),
+    "gkv_decode_status": (_i, [_vp, C.POINTER(_i), _vp]),
+    "gkv_decode_plan_bytes": (_sz, [_i, _i]),
+    "gkv_decode_build_plan": (_i, [_vp] * 4 + [_i, _i, _vp]),
+    "gkv_mixed_attn_decode_planned": (_i, [_vp] * 10 + [_vp, _i, _vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_partial": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_static": (_i, [_vp] * 10 + [_i] * 7 + [_i64, _i, _vp]),
+    "gkv_exchange_inbox_bytes": (_sz, [_i, _i, _i]),
+    "gkv_mixed_attn_decode_exchange": (_i, [_vp] * 10 + [_vp, _vp, _sz] + [_i] * 7 + [_i64, _i] +
+                                       [C.POINTER(_vp), _i, _i, _vp, _vp, _vp]),
     "gkv_combine_partials": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "gkv_pack_blocks": (_i, [_vp, _vp, _i, _vp, _vp] + [_vp] * 4 + [_vp, _vp] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_demote_blocks": (_i, [_vp] * 6 + [_vp] * 4 + [_i] * 5 + [_i64, _i64, _i, _vp]),
@@ -38,22 +48,28 @@ class GkvError(RuntimeError):
     pass
 
 
+def bind(path) -> C.CDLL:
+    """Open a build of the library and attach the signatures of the header to it."""
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError here = header and library disagree
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
 def load():
-    """Load (building first if the sources are newer) and return the ctypes library."""
+    """Return the ctypes library, compiling it first when it is missing or was built from other
+    sources than the ones in the tree (compared by content, so a copied tree is not rebuilt)."""
     global _lib
     if _lib is not None:
         return _lib
     import os
     path = Path(os.environ.get("GKV_LIBRARY", LIB_PATH))    # a differently tuned build can be swapped in
-    if path == LIB_PATH and not LIB_PATH.exists():
+    if path == LIB_PATH:
         from . import build as _build
-        _build.build()
-    lib = C.CDLL(str(path))
-    for name, (res, args) in SIGNATURES.items():
-        fn = getattr(lib, name)          # AttributeError here = header and library disagree
-        fn.restype, fn.argtypes = res, args
-    _lib = lib
-    return lib
+        _build.build()                   # returns at once when the library matches the sources
+    _lib = bind(path)
+    return _lib
 
 
 def check(rc: int, what: str) -> None:

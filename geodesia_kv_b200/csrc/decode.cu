@@ -1,6 +1,4 @@
 // Decode attention over the packed cache: planning, the LSE combine and the C ABI.
-#include <stdlib.h>
-#include <string.h>
 
 #include "decode_generic.cuh"
 #include "decode_mma.cuh"
@@ -113,10 +111,170 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     }
 }
 
+// ---- final merge of a sequence that is split over several GPUs ------------------------------------
+// Every rank holds, per output row, the records of its own slice of the sequence.  This kernel is the
+// last merge level of the rank's decode AND the exchange between the ranks: the CTA of an output row
+// merges the local records into one (m, l, o), stores it into the inbox of every rank (its own
+// included) with plain peer stores, raises the row's sequence number in every inbox (release), waits
+// until all `world` records of that sequence number have arrived in its own inbox (acquire, bounded)
+// and merges them into the normalised output.  No collective library is involved, and nothing but
+// this library's kernels runs in the step.
+//
+// Inbox of one rank: records [2][world][rows][D+2] floats (indexed by the parity of the sequence
+// number: a rank can be at most one call ahead of a peer, so two buffers never collide) followed by
+// flags [world][rows] ints.  seq[rows] lives in local memory and counts this row's calls; all ranks
+// must make the same calls in the same order.
+constexpr int kMaxWorld = 8;
+struct ExchangeParams {
+    float* inbox[kMaxWorld];
+    int* flags[kMaxWorld];
+    int* seq;
+    int* xstatus;        // sticky error word of the exchange (non-zero: a wait ran out)
+    int rank, world, rows;
+};
+
+#ifndef GKV_EXCHANGE_WAIT_NS
+#define GKV_EXCHANGE_WAIT_NS 1000000000ull
+#endif
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(kCombineThreads) exchange_combine_kernel(CombineParams p, ExchangeParams x) {
+    __shared__ float sm_m[8], sm_l[8], sm_o[8][kMaxD];
+    __shared__ float xm[kMaxWorld], xl[kMaxWorld];
+    __shared__ int s_seq, s_fail;
+    const int orow = blockIdx.x, D = p.D;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* base;
+    int64_t stride;
+    if (p.rep > 0) {
+        const int row = orow / p.rep, r = orow % p.rep;
+        base = p.rec + ((size_t)row * p.nsplit * p.rep + r) * (D + 2);
+        stride = (int64_t)p.rep * (D + 2);
+    } else {
+        base = p.rec + (size_t)orow * (D + 2);
+        stride = p.stride_s;
+    }
+    const bool local_fail = p.status && *p.status;
+    constexpr int kPer = kMaxD / 32;
+    float m = -INFINITY, l = 0.f, o[kPer];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) o[i] = 0.f;
+    constexpr int kBatch = 4;
+    for (int s0 = warp; s0 < p.parts; s0 += 8 * kBatch) {
+        float ms[kBatch], ls[kBatch], v[kBatch][kPer];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int s = s0 + 8 * b;
+            const bool live = s < p.parts;
+            const float* rec = base + (live ? s : s0) * stride;
+            ms[b] = live ? rec[0] : -INFINITY;
+            ls[b] = rec[1];
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int d = lane + 32 * i;
+                v[b][i] = d < D ? rec[2 + d] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            if (!(ms[b] > -INFINITY)) continue;
+            const float mn = fmaxf(m, ms[b]);
+            const float a = expf(m - mn), bb = expf(ms[b] - mn);
+            l = l * a + ls[b] * bb;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) o[i] = o[i] * a + v[b][i] * bb;
+            m = mn;
+        }
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) sm_o[warp][d] = o[i];
+    }
+    if (threadIdx.x == 0) { s_seq = x.seq[orow] + 1; s_fail = 0; }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) M = fmaxf(M, sm_m[w]);
+    float L = 0.f, wgt[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        wgt[w] = (sm_m[w] > -INFINITY) ? expf(sm_m[w] - M) : 0.f;
+        L += sm_l[w] * wgt[w];
+    }
+    const int seq = s_seq, par = seq & 1;
+    // this rank's record of the row goes to every inbox
+    const size_t slot = ((size_t)(par * x.world + x.rank) * x.rows + orow) * (D + 2);
+    for (int d = threadIdx.x; d < D + 2; d += kCombineThreads) {
+        float a;
+        if (d == 0) a = M;
+        else if (d == 1) a = L;
+        else {
+            a = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) a += sm_o[w][d - 2] * wgt[w];
+        }
+        for (int r = 0; r < x.world; ++r) x.inbox[r][slot + d] = a;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int r = 0; r < x.world; ++r) st_release_sys(x.flags[r] + (size_t)x.rank * x.rows + orow, seq);
+        x.seq[orow] = seq;
+    }
+    // one thread per source rank waits for that rank's record of this call
+    if (threadIdx.x < x.world) {
+        const int* f = x.flags[x.rank] + (size_t)threadIdx.x * x.rows + orow;
+        unsigned long long t0 = 0;
+        bool got = false;
+        for (unsigned spin = 0;; ++spin) {
+            if (ld_acquire_sys(f) - seq >= 0) { got = true; break; }
+            if (spin > 16) __nanosleep(64);
+            if ((spin & 255u) == 255u) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > GKV_EXCHANGE_WAIT_NS) break;
+            }
+        }
+        if (!got) { s_fail = 1; atomicExch(x.xstatus, 1 + (int)threadIdx.x); }
+    }
+    __syncthreads();
+    const float* mine = x.inbox[x.rank] + (size_t)par * x.world * x.rows * (D + 2);
+    if (threadIdx.x < x.world) {
+        const float* rec = mine + ((size_t)threadIdx.x * x.rows + orow) * (D + 2);
+        xm[threadIdx.x] = __ldcg(rec);
+        xl[threadIdx.x] = __ldcg(rec + 1);
+    }
+    __syncthreads();
+    float GM = -INFINITY;
+    for (int r = 0; r < x.world; ++r) GM = fmaxf(GM, xm[r]);
+    float GL = 0.f, gw[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+        gw[r] = (r < x.world && xm[r] > -INFINITY) ? expf(xm[r] - GM) : 0.f;
+        if (r < x.world) GL += xl[r] * gw[r];
+    }
+    const float poison = (local_fail || s_fail) ? __int_as_float(0x7fc00000) : 0.f;
+    for (int d = threadIdx.x; d < D; d += kCombineThreads) {
+        float a = 0.f;
+        for (int r = 0; r < x.world; ++r) a += __ldcg(mine + ((size_t)r * x.rows + orow) * (D + 2) + 2 + d) * gw[r];
+        p.out[(size_t)orow * D + d] = a / fmaxf(GL, 1e-20f) + poison;
+    }
+}
+
 // ---- split plan -------------------------------------------------------------------------------
 struct Plan {
-    int nsplit, bps;      // work items per cache row, blocks per item
-    int bps2, nbig;       // tensor-core kernel: the first nbig items of a row take bps blocks, the rest bps2
+    int nsplit, bps;      // work items (tensor-core kernel: item slots) per cache row, blocks per item
     int parts;            // records per cache row and query head (the tensor-core kernel writes one per consumer warp)
     int segs;             // > 1: the merge runs in two levels, `segs` partial merges per output row first
     bool mma;             // tensor-core kernel (persistent, work items of `bps` blocks)
@@ -131,48 +289,61 @@ static bool mma_shape_ok(int D, int group, int rep) {
     return (D == 64 || D == 128) && (group == 16 || group == 32 || group == 64) && D % group == 0 && rep <= 8;
 }
 
-static bool force_generic() {
-    const char* e = getenv("GKV_DECODE_KERNEL");
-    return e && strcmp(e, "generic") == 0;
+// Process-wide kernel choice (gkv_set_decode_kernel): 0 = by shape, 1 = always the CUDA-core kernel.
+static int g_decode_kernel = 0;
+static bool force_generic() { return g_decode_kernel == 1; }
+// Process-wide override of the tensor-core kernel's work-item size (gkv_set_decode_item_blocks): 0 = by problem size.
+static int g_item_blocks = 0;
+
+// Per-device facts and one-time set-up, keyed by the CUDA device ordinal (a process may drive
+// several GPUs; function attributes and the SM count belong to the device, not the process).
+constexpr int kMaxDevices = 64;
+static int g_sm_count[kMaxDevices] = {0};
+
+static int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+
+// Multiprocessors of the current device (148 on B200); `fallback` when no device answers, so that
+// the pure-host size queries still work on a machine without a GPU.
+static int sm_count(int fallback = kNumSM) {
+    const int dev = current_device();
+    if (dev < 0) return fallback;
+    if (g_sm_count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            return fallback;
+        }
+        g_sm_count[dev] = n;
+    }
+    return g_sm_count[dev];
 }
 
 static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mma) {
     Plan pl;
+    const int sms = sm_count();
     pl.mma = allow_mma && mma_shape_ok(D, group, rep) && !force_generic();
     if (pl.mma) {
-        pl.grid = mma::kCtasPerSM * kNumSM;
+        pl.grid = mma::kCtasPerSM * sms;
         const long total = (long)rows * nb;
-        const int nw = mma::kConsumerWarps;
         int chunk = (int)(total / ((long)pl.grid * 6));      // ~6 items per CTA; larger items measured faster than finer balance
-        if (chunk < nw) chunk = nw;
-        if (chunk > 32) chunk = 32;                      // the producer's metadata table holds 32 blocks
-        if (const char* e = getenv("GKV_DECODE_CHUNK")) {      // tuning knob: blocks per work item
-            const int v = atoi(e);
-            if (v >= 1 && v <= 32) chunk = v;
-        }
-        // The last part of every row's (rung-sorted) list goes out in half-size items: items are
-        // handed out chunk-major, so these are the last items of the grid, and the spread of the
-        // CTAs' finishing times is about one item.
-        int tail_pct = 0;
-        if (const char* e = getenv("GKV_DECODE_TAIL")) {       // tuning knob: percent of a row in half-size items
-            const int v = atoi(e);
-            if (v >= 0 && v <= 100) tail_pct = v;
-        }
-        int chunk2 = chunk / 2 < nw ? nw : chunk / 2;
-        if (chunk2 > chunk) chunk2 = chunk;
-        int nbig = nb > 0 ? (int)(((long)nb * (100 - tail_pct) / 100) / chunk) : 0;
-        if (nb / chunk < 4) nbig = (nb + chunk - 1) / chunk;   // short rows: uniform items
-        const int rest = nb - nbig * chunk > 0 ? nb - nbig * chunk : 0;
-        pl.bps = chunk; pl.bps2 = chunk2; pl.nbig = nbig;
-        pl.nsplit = nb > 0 ? nbig + (rest + chunk2 - 1) / chunk2 : 1;
+        if (chunk < mma::kMinItemBlocks) chunk = mma::kMinItemBlocks;
+        if (chunk > mma::kMaxItemBlocks) chunk = mma::kMaxItemBlocks;    // the producers' block tables
+        if (g_item_blocks > 0) chunk = g_item_blocks;
+        // Every rung's run of a row's sorted list is cut into items of `chunk` blocks; whatever the
+        // mix of rungs, ceil(nb / chunk) + 4 slots hold them all (five runs, each with one short item
+        // at most).  Slots a row does not need stay empty.
+        pl.bps = chunk;
+        pl.nsplit = (nb + chunk - 1) / chunk + 4;
         pl.parts = pl.nsplit * mma::kConsumerWarps;
         pl.segs = pl.parts > kCombineDirect ? (pl.parts / 64 < kCombineSegs ? pl.parts / 64 : kCombineSegs) : 1;
-        const long items = (long)rows * pl.nsplit;
-        if (items < pl.grid) pl.grid = (int)(items > 0 ? items : 1);
         return pl;
     }
     // generic kernel: enough slices for ~4 CTAs per SM
-    int nsplit = (kNumSM * 4 + rows - 1) / rows;
+    int nsplit = (sms * 4 + rows - 1) / rows;
     if (nsplit > nb) nsplit = nb;
     if (nsplit < 1) nsplit = 1;
     pl.bps = nb > 0 ? (nb + nsplit - 1) / nsplit : 1;
@@ -180,7 +351,6 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
     pl.parts = pl.nsplit;
     pl.segs = 1;
     pl.grid = 0;
-    pl.bps2 = pl.bps; pl.nbig = pl.nsplit;
     return pl;
 }
 
@@ -188,8 +358,12 @@ static size_t records_bytes(int B, int Hq, const Plan& pl, int D) {
     return (size_t)B * Hq * ((size_t)pl.parts + (pl.segs > 1 ? pl.segs : 0)) * (D + 2) * sizeof(float);
 }
 
-// the tensor-core kernel's rung-sorted block lists: one 16-byte entry per block of every metadata row
-static size_t perm_bytes(int rows, int nb) { return (((size_t)rows * nb * sizeof(uint4)) + 255) & ~(size_t)255; }
+// the tensor-core kernel's rung-sorted block lists: one 16-byte entry per block of every metadata row,
+// followed by the rows' tables of where each rung starts in its list
+static size_t perm_entries_bytes(int rows, int nb) { return (((size_t)rows * nb * sizeof(uint4)) + 255) & ~(size_t)255; }
+static size_t perm_bytes(int rows, int nb) {
+    return perm_entries_bytes(rows, nb) + ((((size_t)rows * mma::kPlanTabInts * sizeof(int32_t)) + 255) & ~(size_t)255);
+}
 
 // Upper bound over both kernels, so the caller's buffer fits whichever is dispatched.
 static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
@@ -200,24 +374,49 @@ static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
     return ((kHeaderBytes + need + 255) & ~(size_t)255) + perm_bytes(rows, nb);
 }
 
+// A kernel that needs more than 48 KB of dynamic shared memory has to be opted in once per device.
+template <typename Kernel>
+static int opt_in_smem(Kernel kernel, unsigned char (&done)[kMaxDevices], size_t bytes) {
+    const int dev = current_device();
+    if (dev < 0) return GKV_E_CUDA;
+    if (!done[dev]) {
+        GKV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        done[dev] = 1;
+    }
+    return GKV_OK;
+}
+
+template <int D, int G, bool DUP>
+static int launch_mma2(const mma::Params& p, int grid, cudaStream_t stream) {
+    static unsigned char done[kMaxDevices] = {0};
+    if (const int rc = opt_in_smem(mma::decode_mma_kernel<D, G, DUP>, done, mma::Cfg<D, G>::SMEM)) return rc;
+    mma::decode_mma_kernel<D, G, DUP><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+// up to four query heads per cache row: the (hi, lo) halves of a head share one MMA
 template <int D, int G>
 static int launch_mma(const mma::Params& p, int grid, cudaStream_t stream) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        GKV_CUDA_TRY(cudaFuncSetAttribute(mma::decode_mma_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)mma::Cfg<D, G>::SMEM));
-        attr_set = true;
-    }
-    mma::decode_mma_kernel<D, G><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p);
+    return p.rep <= 4 ? launch_mma2<D, G, true>(p, grid, stream) : launch_mma2<D, G, false>(p, grid, stream);
+}
+
+static int launch_plan(const int32_t* level, const int32_t* valid, const int64_t* offs, uint4* plan, int meta_rows,
+                       int nb, int* header, cudaStream_t stream) {
+    int plan_threads = (nb + 31) & ~31;                     // one block per thread up to the CTA limit
+    plan_threads = plan_threads < 32 ? 32 : plan_threads > mma::kPlanMaxThreads ? mma::kPlanMaxThreads : plan_threads;
+    int32_t* tab = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(plan) + perm_entries_bytes(meta_rows, nb));
+    mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, offs, plan, tab, nb, header,
+                                                            header ? (int)(kHeaderBytes / 4) : 0);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }
 
 static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
                        const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
-                       const int32_t* valid, float* out, int normalise, void* workspace,
+                       const int32_t* valid, float* out, int normalise, const void* plan_in, void* workspace,
                        size_t ws_bytes, int B, int Hq, int Hkv, int D, int nb, int block, int group,
-                       int64_t stride_bh, int meta_rows, void* stream_) {
+                       int64_t stride_bh, int meta_rows, void* stream_, const ExchangeParams* xch = nullptr) {
     if (block != kP) return GKV_E_BLOCK;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || nb < 0 || group <= 0) return GKV_E_SHAPE;
     if (D <= 0 || D > kMaxD || D % 8 != 0) return GKV_E_SHAPE;
@@ -228,6 +427,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     if (nb > 0 && (!data || !offs || !klo || !kstep || !vlo || !vstep || !level || !valid)) return GKV_E_NULL;
     const size_t need = workspace_bytes(B, Hq, Hkv, D, nb);
     if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return GKV_E_WORKSPACE;
+    if (plan_in && (reinterpret_cast<uintptr_t>(plan_in) & 15)) return GKV_E_ARG;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
     const bool scales_aligned = ((reinterpret_cast<uintptr_t>(klo) | reinterpret_cast<uintptr_t>(kstep) |
@@ -237,30 +437,41 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     float* records = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kHeaderBytes);
 
     if (pl.mma) {
-        // the block lists sit at the end of the workspace, behind the records of either kernel
-        uint4* plan = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + need - perm_bytes(rows, nb));
-        int plan_threads = (nb + 31) & ~31;                     // one block per thread up to the CTA limit
-        plan_threads = plan_threads < 32 ? 32 : plan_threads > mma::kPlanMaxThreads ? mma::kPlanMaxThreads : plan_threads;
-        mma::plan_kernel<<<meta_rows, plan_threads, 0, stream>>>(level, valid, offs, plan, nb, header, (int)(kHeaderBytes / 4));
-        GKV_LAUNCH_CHECK();
+        const uint4* plan = static_cast<const uint4*>(plan_in);
+        if (plan) {
+            // the caller keeps the block lists (they change only with level/valid/offs): only the
+            // work counter and the status word have to start at zero
+            GKV_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, stream));
+        } else {
+            // the block lists sit at the end of the workspace, behind the records of either kernel
+            uint4* mine = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + need - perm_bytes(meta_rows, nb));
+            if (const int rc = launch_plan(level, valid, offs, mine, meta_rows, nb, header, stream)) return rc;
+            plan = mine;
+        }
         mma::Params mp;
         mp.plan = plan; mp.rows = rows;
+        mp.plan_tab = reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(plan) + perm_entries_bytes(meta_rows, nb));
         mp.q = q; mp.data = data; mp.offs = offs;
         mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
         mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);
         mp.level = level; mp.valid = valid; mp.part = records; mp.counter = header; mp.status = header + 1;
-        mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps; mp.chunk2 = pl.bps2; mp.nbig = pl.nbig;
+        mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps;
         mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
         mp.stride_bh = stride_bh;
         int rc;
         if (D == 128 && group == 32) rc = launch_mma<128, 32>(mp, pl.grid, stream);
+#ifdef GKV_FAST_BUILD      // development builds: only the main shape is instantiated
+        else rc = GKV_E_SHAPE;
+#else
         else if (D == 128 && group == 16) rc = launch_mma<128, 16>(mp, pl.grid, stream);
         else if (D == 128 && group == 64) rc = launch_mma<128, 64>(mp, pl.grid, stream);
         else if (D == 64 && group == 32) rc = launch_mma<64, 32>(mp, pl.grid, stream);
         else if (D == 64 && group == 16) rc = launch_mma<64, 16>(mp, pl.grid, stream);
         else rc = launch_mma<64, 64>(mp, pl.grid, stream);
+#endif
         if (rc) return rc;
     } else {
+        GKV_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, stream));      // status word reads "ok"
         DecodeParams p;
         p.q = q; p.data = data; p.offs = offs;
         p.klo = static_cast<const __half*>(klo); p.kstep = static_cast<const __half*>(kstep);
@@ -271,12 +482,8 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.rep = rep;
         p.nsplit = pl.nsplit; p.bps = pl.bps; p.per_row_meta = meta_rows != 1; p.stride_bh = stride_bh;
         const size_t smem = decode_generic_smem(rep, D);
-        static bool attr_set = false;
-        if (!attr_set) {
-            GKV_CUDA_TRY(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)decode_generic_smem(16, kMaxD)));
-            attr_set = true;
-        }
+        static unsigned char done[kMaxDevices] = {0};
+        if (const int rc = opt_in_smem(decode_generic_kernel, done, decode_generic_smem(16, kMaxD))) return rc;
         decode_generic_kernel<<<dim3(pl.nsplit, rows), kGenThreads, smem, stream>>>(p);
         GKV_LAUNCH_CHECK();
     }
@@ -294,7 +501,8 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0;
         c.stride_s = (int64_t)B * Hq * (D + 2); c.normalise = normalise; c.segs = 1; c.per_seg = 0;
     }
-    combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c);
+    if (xch) exchange_combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c, *xch);
+    else combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }
@@ -326,11 +534,53 @@ size_t gkv_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
     return gkv::workspace_bytes(B, Hq, Hkv, D, nb);
 }
 
-int gkv_decode_kernel_launches(int B, int Hq, int Hkv, int D, int nb, int group) {
+int gkv_decode_launch_count(int B, int Hq, int Hkv, int D, int nb, int group, int planned) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0 || nb < 0 || group <= 0) return 0;
     const gkv::Plan pl = gkv::make_plan(B * Hkv, nb, D, group, Hq / Hkv, nb > 0);
-    // tensor-core path: block lists, split kernel, one or two merge levels; generic path: split kernel, merge
-    return pl.mma ? 2 + (pl.segs > 1 ? 2 : 1) : 2;
+    // tensor-core path: block lists (unless the caller keeps them), split kernel, one or two merge
+    // levels; generic path: split kernel, merge
+    return pl.mma ? (planned ? 1 : 2) + (pl.segs > 1 ? 2 : 1) : 2;
+}
+
+int gkv_decode_kernel_launches(int B, int Hq, int Hkv, int D, int nb, int group) {
+    return gkv_decode_launch_count(B, Hq, Hkv, D, nb, group, 0);
+}
+
+int gkv_set_decode_kernel(int which) {
+    if (which != 0 && which != 1) return GKV_E_ARG;
+    gkv::g_decode_kernel = which;
+    return GKV_OK;
+}
+
+int gkv_set_decode_item_blocks(int blocks) {
+    if (blocks != 0 && (blocks < 1 || blocks > gkv::mma::kMaxItemBlocks)) return GKV_E_ARG;
+    gkv::g_item_blocks = blocks;
+    return GKV_OK;
+}
+
+size_t gkv_decode_plan_bytes(int meta_rows, int nb) {
+    if (meta_rows <= 0 || nb < 0) return 0;
+    return gkv::perm_bytes(meta_rows, nb > 0 ? nb : 1);
+}
+
+int gkv_decode_build_plan(const int64_t* offs, const int32_t* level, const int32_t* valid, void* plan,
+                          int meta_rows, int nb, void* stream) {
+    if (meta_rows <= 0 || nb < 0) return GKV_E_SHAPE;
+    if (nb == 0) return GKV_OK;
+    if (!offs || !level || !valid || !plan) return GKV_E_NULL;
+    if (reinterpret_cast<uintptr_t>(plan) & 15) return GKV_E_ARG;
+    return gkv::launch_plan(level, valid, offs, static_cast<uint4*>(plan), meta_rows, nb, nullptr,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int gkv_decode_status(const void* workspace, int* status_host, void* stream) {
+    if (!workspace || !status_host) return GKV_E_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int word = 0;
+    GKV_CUDA_TRY(cudaMemcpyAsync(&word, static_cast<const int*>(workspace) + 1, sizeof(int), cudaMemcpyDeviceToHost, st));
+    GKV_CUDA_TRY(cudaStreamSynchronize(st));
+    *status_host = word;
+    return GKV_OK;
 }
 
 int gkv_mixed_attn_decode(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
@@ -338,8 +588,19 @@ int gkv_mixed_attn_decode(const float* q, const uint8_t* data, const int64_t* of
                           const int32_t* valid, float* out, void* workspace, size_t workspace_bytes,
                           int B, int Hq, int Hkv, int D, int nb, int block, int group,
                           int64_t stride_bh, int meta_rows, void* stream) {
-    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, workspace,
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, nullptr, workspace,
                             workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream);
+}
+
+int gkv_mixed_attn_decode_planned(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
+                                  const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
+                                  const int32_t* valid, float* out, const void* plan, int partial,
+                                  void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D,
+                                  int nb, int block, int group, int64_t stride_bh, int meta_rows,
+                                  void* stream) {
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, partial ? 0 : 1, plan,
+                            workspace, workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows,
+                            stream);
 }
 
 int gkv_mixed_attn_decode_partial(const float* q, const uint8_t* data, const int64_t* offs,
@@ -348,8 +609,37 @@ int gkv_mixed_attn_decode_partial(const float* q, const uint8_t* data, const int
                                   void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D,
                                   int nb, int block, int group, int64_t stride_bh, int meta_rows,
                                   void* stream) {
-    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, partial, 0, workspace,
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, partial, 0, nullptr, workspace,
                             workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream);
+}
+
+size_t gkv_exchange_inbox_bytes(int world, int rows, int D) {
+    if (world <= 0 || world > gkv::kMaxWorld || rows <= 0 || D <= 0) return 0;
+    const size_t rec = (size_t)2 * world * rows * (D + 2) * sizeof(float);
+    const size_t flags = (size_t)world * rows * sizeof(int);
+    return ((rec + 255) & ~(size_t)255) + ((flags + 255) & ~(size_t)255);
+}
+
+int gkv_mixed_attn_decode_exchange(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
+                                   const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
+                                   const int32_t* valid, float* out, const void* plan, void* workspace,
+                                   size_t workspace_bytes, int B, int Hq, int Hkv, int D, int nb, int block,
+                                   int group, int64_t stride_bh, int meta_rows, void* const* inboxes, int rank,
+                                   int world, int* seq, int* xstatus, void* stream) {
+    if (!inboxes || !seq || !xstatus) return GKV_E_NULL;
+    if (world <= 0 || world > gkv::kMaxWorld || rank < 0 || rank >= world) return GKV_E_ARG;
+    if (B <= 0 || Hq <= 0 || D <= 0) return GKV_E_SHAPE;
+    gkv::ExchangeParams x;
+    const int rows = B * Hq;
+    const size_t rec = (((size_t)2 * world * rows * (D + 2) * sizeof(float)) + 255) & ~(size_t)255;
+    for (int r = 0; r < gkv::kMaxWorld; ++r) {
+        if (r < world && !inboxes[r]) return GKV_E_NULL;
+        x.inbox[r] = r < world ? static_cast<float*>(inboxes[r]) : nullptr;
+        x.flags[r] = r < world ? reinterpret_cast<int*>(static_cast<uint8_t*>(inboxes[r]) + rec) : nullptr;
+    }
+    x.seq = seq; x.xstatus = xstatus; x.rank = rank; x.world = world; x.rows = rows;
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, plan, workspace,
+                            workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream, &x);
 }
 
 int gkv_combine_partials(const float* partials, float* out, int parts, int rows, int D, void* stream) {
@@ -377,18 +667,17 @@ int gkv_mixed_attn_decode_static(const float* q, const uint8_t* data, const int6
     if (need > (size_t)GKV_STATIC_SCRATCH_BYTES) return GKV_E_STATIC_SCRATCH;
     // `g_static_scratch` is only a host-side handle here; the device address has to be asked for,
     // once per device, with that device current.
-    constexpr int kMaxDevices = 64;
-    static void* device_ptr[kMaxDevices] = {nullptr};
+    static void* device_ptr[gkv::kMaxDevices] = {nullptr};
     int dev = 0;
     GKV_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) return GKV_E_ARG;
+    if (dev < 0 || dev >= gkv::kMaxDevices) return GKV_E_ARG;
     if (!device_ptr[dev]) {
         void* ptr = nullptr;
         GKV_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
         if (!ptr) return GKV_E_CUDA;
         device_ptr[dev] = ptr;
     }
-    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, device_ptr[dev],
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, nullptr, device_ptr[dev],
                             (size_t)GKV_STATIC_SCRATCH_BYTES, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows,
                             stream);
 }

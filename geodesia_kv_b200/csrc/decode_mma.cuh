@@ -8,21 +8,25 @@
 // memory, which is why this is mma.sync and not tcgen05 (whose operands must be staged in
 // shared memory in canonical layout at 2 B per code).
 //
-// Structure (one CTA = 4 consumer warps + a producer warp + a query warp, two CTAs per SM,
-// persistent):
-//   * a small kernel first sorts every row's blocks by rung; work items are (cache row, run of
-//     up to 32 entries of that sorted list), numbered chunk-major and handed out by an atomic
-//     counter; every item ends in one (m, l, o) record per consumer warp and query head;
-//   * the producer warp streams each block's bytes and its four scale planes into a byte
-//     ring in shared memory with cp.async.bulk + mbarrier (non-multicast), several blocks
-//     ahead of the consumers, and announces every item one item early;
-//   * the query warp turns the next item's query rows into MMA A-fragment planes (double
-//     buffered), so the consumers never stop at an item boundary;
-//   * consumer warps work in pairs: a pair takes every second block of the stream and each of
-//     its warps one half of the block's tokens, with a private online softmax.  A block is
-//     therefore resident for half as long, which doubles the part of the ring that is free
-//     for copies in flight.  Nothing is merged inside the CTA: the combine kernel merges the
-//     per-warp records together with the split records.
+// Structure (one persistent CTA per SM: 12 consumer warps + 2 producer warps + a query warp + a
+// scheduler warp):
+//   * a small kernel first sorts every cache row's blocks by rung.  A work item is a run of
+//     consecutive entries of ONE rung of one row's sorted list (at most kMaxItemBlocks), so an
+//     item never mixes rungs: its code path, its query operands and the layout of its
+//     accumulators are fixed when it starts.  Items are numbered slot-major (slot * rows + row)
+//     and handed out by an atomic counter, so the grid walks the ladder roughly together.  The
+//     scheduler warp draws them a few items ahead and parks each item's block table in shared memory;
+//   * the blocks of an item alternate between two STREAMS.  Each stream has its own producer
+//     warp, its own byte ring in shared memory and three pairs of consumer warps.  The producer
+//     streams each block's bytes with one cp.async.bulk and its four scale planes with 16-byte
+//     cp.async copies from all lanes, all reporting to the slot's mbarrier;
+//   * the query warp turns the next item's query rows into MMA A-fragment planes for the
+//     item's rung (double buffered), so the consumers never stop at an item boundary;
+//   * a pair of consumer warps takes every third block of its stream and each of its warps
+//     one half of the block's tokens, with a private online softmax.  Nothing is merged
+//     inside the CTA: the combine kernel merges the per-warp records;
+//   * items of centroid blocks (512 bytes each) bypass the rings: the consumer warps read
+//     them straight from global memory with one coalesced 16-byte load per lane.
 //
 // Arithmetic.  Integer codes are fed to the MMA as fp16 values from the LINEAR range of the
 // format: bit patterns 0..2047 (subnormals and the first binade) are worth pattern * 2^-24, so a
@@ -30,14 +34,22 @@
 // needs no int->float conversion.  The tensor core aligns the products of a dot product by their
 // nominal exponents, so a code sitting in the low mantissa bits wastes that many bits of the
 // accumulation window (measured: 2-bit codes at bit 0 lose ~10 bits); codes are therefore
-// placed as high in the linear range as a single shift allows (bits 8-9 / 6-7 for 2-bit,
-// 7-10 / 3-6 for 4-bit, 0-7 for 8-bit) and the power of two is folded into the query planes.
-// De-quantisation is hoisted out of the contraction:
+// placed as high in the linear range as a single shift allows and the power of two is folded
+// into the other operand or into the epilogue.  De-quantisation is hoisted out of the contraction:
 //   q . (c*step + lo) = (q*step) . c + q . lo        (per token group, per channel)
 //   p . (c*step + lo) = (p*step) . c + p . lo        (per token, per channel group)
-// The small operands q*step and p*step are split into fp16 hi + lo halves that ride in the
-// otherwise unused MMA rows 8..15 (the GQA group is at most 8 heads), giving ~22 significant
-// bits; the lo terms ride along as one more n-tile on each side.  Accumulation is fp32 throughout.
+// The small operands q*step and p*step are split into fp16 hi + lo halves (~22 significant
+// bits); the lo terms ride along as one more MMA tile on each side.  Accumulation is fp32.
+//
+// Orientation.  QK^T is computed as S[head][token] (A = q*step, hi halves in rows 0-7 and lo halves
+// in rows 8-15; B = key codes), which leaves every thread with the weights of its head for the
+// token pairs 2t, 2t+1 — exactly a B fragment.  PV is therefore computed TRANSPOSED,
+// O^T[channel][head] (A = value codes, fetched with ldmatrix.trans so that a register already
+// holds one channel set of two neighbouring tokens; B = p*vstep): 32 accumulator registers per
+// thread instead of 64, which is what lets 12 consumer warps share an SM.  With at most four
+// query heads per cache row the eight B columns carry (hi, lo) of every head and one MMA does
+// both halves; with five to eight heads the hi and lo products are two MMAs into the same
+// accumulators.
 #pragma once
 
 #include "gkv_common.cuh"
@@ -45,57 +57,54 @@
 namespace gkv {
 namespace mma {
 
-#ifndef GKV_NW
-#define GKV_NW 4          // consumer warps per CTA
-#endif
-#ifndef GKV_CTAS
-#define GKV_CTAS 2        // CTAs per SM
-#endif
+constexpr int kConsumerWarps = 12;       // three warpgroups
+constexpr int kStreams = 2;              // byte rings / producer warps per CTA
+constexpr int kPairsPerStream = kConsumerWarps / 2 / kStreams;
+constexpr int kCtasPerSM = 1;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 128;          // + helper warpgroup: producers 0/1, query warp, scheduler warp
+// Register re-allocation between warpgroups (setmaxnreg): launched with 128 registers per thread
+// (512 threads), the helper warpgroup drops to kHelperRegs and the consumers rise to kConsumerRegs:
+// 384 * 152 + 128 * 56 = 65536.
+constexpr int kHelperRegs = 56, kConsumerRegs = 152;
 #ifndef GKV_K_FETCH
 #define GKV_K_FETCH 16    // widest shared-memory load used for a lane's codes of a K row (4, 8 or 16 bytes)
 #endif
 #ifndef GKV_RING_KB
-#define GKV_RING_KB 71    // byte ring per CTA
+#define GKV_RING_KB 100   // byte ring per stream
 #endif
-constexpr int kConsumerWarps = GKV_NW;
-constexpr int kCtasPerSM = GKV_CTAS;
-constexpr int kConsumers = kConsumerWarps * 32;
-#if GKV_NW == 4 && GKV_CTAS == 2 && !defined(GKV_NO_REG_SHIFT) && !defined(GKV_REG_SHIFT)
-#define GKV_REG_SHIFT 1
+#ifndef GKV_NSLOT
+#define GKV_NSLOT 16
 #endif
-#ifdef GKV_REG_SHIFT
-// Register re-allocation between warpgroups (setmaxnreg): the CTA is two full warpgroups, the
-// consumers' and a helper one (producer warp, query warp, two warps that leave at once); the
-// helpers hand most of their registers to the consumers (200 instead of 168 each: enough to keep
-// the whole K loop of a unit unrolled with its loads in flight, measured +4 %).  Launched with 128
-// registers per thread, two CTAs per SM.
-constexpr int kThreads = kConsumers + 128;
-#ifndef GKV_HELPER_REGS
-#define GKV_HELPER_REGS 56
-#endif
-constexpr int kHelperRegs = GKV_HELPER_REGS, kConsumerRegs = 256 - GKV_HELPER_REGS;   // 128 * (helper + consumer) = 256 threads * 128 registers at launch
-static_assert(kConsumerWarps == 4, "the consumers must be exactly one warpgroup");
-#else
-constexpr int kThreads = kConsumers + 64;    // + producer warp + query warp
-#endif
-static_assert(kConsumerWarps % 2 == 0, "consumer warps work in pairs");
-constexpr int kNSlot = kConsumerWarps <= 4 ? 16 : 32;   // descriptor slots (blocks in flight per CTA)
+constexpr int kNSlot = GKV_NSLOT;        // descriptor slots (blocks in flight) per stream
 constexpr uint32_t kRingBytes = GKV_RING_KB * 1024;
-constexpr int kItemSlots = 4;           // item descriptors in flight: finishing, current, announced, spare
-constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // every wait gives up after ~1 s, flags the error, returns
+constexpr int kMaxItemBlocks = 64;       // blocks per work item: 32 per producer (one table entry per lane)
+constexpr int kMinItemBlocks = kConsumerWarps / 2;   // one block per pair
+constexpr int kItemSlots = 4;            // item descriptors in flight: finishing, current, announced, spare
+#ifndef GKV_WAIT_LIMIT_NS
+#define GKV_WAIT_LIMIT_NS 1000000000ull
+#endif
+constexpr unsigned long long kWaitLimitNs = GKV_WAIT_LIMIT_NS;  // every wait gives up after ~1 s, flags the error, returns
+constexpr int kPlanTabInts = 8;          // per metadata row: start of each rung class in the sorted list (6), nb, padding
 
-struct Desc {           // one block in the ring
+struct Desc {           // one block in a ring
     uint32_t off;       // byte offset of the block in the ring
-    int32_t level;      // 0 = nothing to do (padding slot)
     int32_t nvalid;
-    int32_t pad;
+    int32_t pad;        // ring bytes the slot occupies (with alignment and wrap waste)
+    int32_t unused;
 };
 
 struct ItemDesc {       // one work item; published one item ahead of its blocks (ring of kItemSlots)
-    int32_t item;
+    int32_t item;       // slot * rows + row
     int32_t row;
-    int32_t end_seq;    // the item's blocks are the stream positions up to (not including) this one
+    int32_t level;      // rung of every block of the item (16, 8, 4, 2, 1)
+    int32_t b_lo;       // first entry of the item in the row's sorted list
+    int32_t nblk;
+    int32_t first;      // stream of the item's first block (blocks alternate from there)
+    int32_t end_seq0;   // per stream: the item's blocks are the stream positions below this
+    int32_t end_seq1;
     int32_t exit;
+    int32_t pad[3];
 };
 
 struct Params {
@@ -108,13 +117,13 @@ struct Params {
     const __half* vstep;
     const int32_t* level;
     const int32_t* valid;
-    const uint4* plan;  // (metadata rows, nb) block entries of every row sorted by rung, from plan_kernel
-    float* part;        // (rows, items per row, consumer warps, rep, D+2)
-    int* counter;       // work-item counter (zeroed before launch)
-    int* status;        // error word (zeroed before launch)
+    const uint4* plan;       // (metadata rows, nb) block entries of every row sorted by rung, from plan_kernel
+    const int32_t* plan_tab; // (metadata rows, kPlanTabInts) start of each rung class in that list
+    float* part;             // (rows, items per row, consumer warps, rep, D+2)
+    int* counter;            // work-item counter (zeroed before launch)
+    int* status;             // error word (zeroed before launch)
     int B, Hq, Hkv, nb, rep;
-    int chunk;          // blocks per item for the first nbig chunks of a row's sorted list ...
-    int chunk2, nbig;   // ... and for the chunks after them (smaller items at the end trim the tail of the grid)
+    int chunk;               // blocks per item (the last item of a rung's run may be shorter)
     int items_per_row, items;
     int per_row_meta;
     int rows;
@@ -163,9 +172,16 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t a) { uint32_t v; asm volati
 __device__ __forceinline__ uint32_t lds_u32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
 __device__ __forceinline__ uint2 lds_v2(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
 __device__ __forceinline__ uint4 lds_v4(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+// Four 8x8 matrices of 16-bit units, transposed: lane L passes the address of row (L & 7) of matrix
+// (L >> 3); thread (r = lane >> 2, t = lane & 3) receives, from each matrix, unit r of rows 2t (low
+// half) and 2t+1 (high half).
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -239,8 +255,12 @@ __host__ __device__ constexpr float arr_scale(int bits, int e) {
 }
 // 2^24 / (weight of one code in the linear range) for the K contraction of each rung
 __host__ __device__ constexpr float k_unscale(int bits) { return bits == 4 ? 131072.f : bits == 2 ? 65536.f : 16777216.f; }
-// V contraction: bit position the codes are brought to, and the weight scale that goes with it
-__host__ __device__ constexpr int v_pos(int bits) { return bits == 4 ? 4 : bits == 2 ? 8 : 0; }
+
+// Head whose scores a thread with row index r (= lane >> 2) holds.  With at most four heads per
+// cache row, rows 2h and 2h+1 both carry head h, so that the two threads can feed the hi and the
+// lo column of that head in the transposed PV product.
+template <bool DUP>
+__device__ __forceinline__ int head_of_row(int r) { return DUP ? (r >> 1) : r; }
 
 template <int D, int G>
 struct Cfg {
@@ -248,82 +268,69 @@ struct Cfg {
     static constexpr int KS = D / 16;         // QK k-steps
     static constexpr int CH = KS / 2;         // 16-byte chunks of prepared q per thread (2 k-steps each)
     static constexpr int TG = kP / G;         // token groups (K scales)
-    static constexpr int NTG = G / 8;         // token n-tiles per token group
     static constexpr int GV = D / G;          // channel groups (V scales)
-    static constexpr int NT = G / 8;          // channel n-tiles per channel group
-    static constexpr int NTILE = D / 8;       // output n-tiles
+    static constexpr int MT = D / 16;         // output m-tiles (16 channels each) of the transposed PV product
     static constexpr int KSCALE = TG * D * 2; // bytes of klo (or kstep) of one block
     static constexpr int VSCALE = kP * GV * 2;
-    // prepared-q planes, in halves: [plane][chunk][lane][8]
+    // prepared-q planes, in halves: [plane][chunk][lane][8]; plane 0 = hi, plane 1 = lo, of the item's rung
     static constexpr int QPLANE = CH * 32 * 8;
-    // planes: 0/1 arr8 hi/lo, 2/3 arr4 hi/lo, 4/5 arr2 hi/lo, 6/7 bf16 hi/lo
-    static constexpr int QPREP_BYTES = 8 * QPLANE * 2;
+    static constexpr int QPREP_BYTES = 2 * QPLANE * 2;
     static constexpr int SQ_BYTES = 8 * D * 4;
-    static constexpr size_t SMEM = kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
-                                   kNSlot * sizeof(Desc) + 2 * kNSlot * 8 + kItemSlots * sizeof(ItemDesc) +
-                                   (2 * kItemSlots + 2) * 8 + 32 * 16 + 64;
+    static constexpr size_t SMEM = kStreams * (size_t)kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
+                                   kStreams * kNSlot * (sizeof(Desc) + 16) + kItemSlots * sizeof(ItemDesc) +
+                                   (2 * kItemSlots + 2) * 8 + kItemSlots * kMaxItemBlocks * 16 + 128;
     static_assert(D % 32 == 0 && (G == 16 || G == 32 || G == 64) && D % G == 0, "unsupported shape");
 };
 
 template <int D, int G>
 struct Smem {
     using C = Cfg<D, G>;
-    uint8_t* ring;
+    uint8_t* ring;         // [kStreams][kRingBytes]
     __half* qprep;         // [2] prepared-query planes (item parity)
     float* sq;             // [2][8][D] raw query (fp32, softmax scale included)
     float* sf;             // [2][16]: per-head factor 2^-eq * log2(e), then 2^eq
-    Desc* desc;
-    uint64_t* full;
-    uint64_t* empty;
+    Desc* desc;            // [kStreams][kNSlot]
+    uint64_t* full;        // [kStreams][kNSlot]
+    uint64_t* empty;       // [kStreams][kNSlot]
     ItemDesc* item;        // [kItemSlots]
-    uint64_t* item_full;   // [kItemSlots] producer -> query warp and consumers
-    uint64_t* item_empty;  // [kItemSlots] one arrival per consumer warp that finished the item
+    uint64_t* item_full;   // [kItemSlots] scheduler warp -> producers, query warp and consumers
+    uint64_t* item_empty;  // [kItemSlots] one arrival per consumer warp and per producer that is done with the item
     uint64_t* qready;      // [2] query warp -> consumers
-    uint4* meta_tab;       // [32] block table of the producer's current item
+    uint4* item_tab;       // [kItemSlots][kMaxItemBlocks] block entries of the announced items (row base offset added)
     __device__ explicit Smem(uint8_t* base) {
         ring = base;
-        qprep = reinterpret_cast<__half*>(base + kRingBytes);
-        sq = reinterpret_cast<float*>(base + kRingBytes + 2 * C::QPREP_BYTES);
-        sf = sq + 2 * 8 * D;
-        desc = reinterpret_cast<Desc*>(sf + 32);
-        full = reinterpret_cast<uint64_t*>(desc + kNSlot);
-        empty = full + kNSlot;
-        item_full = empty + kNSlot;
-        item_empty = item_full + kItemSlots;
-        qready = item_empty + kItemSlots;
-        item = reinterpret_cast<ItemDesc*>(qready + 2);
-        meta_tab = reinterpret_cast<uint4*>(item + kItemSlots);
+        uint8_t* p = base + kStreams * (size_t)kRingBytes;
+        qprep = reinterpret_cast<__half*>(p);               p += 2 * C::QPREP_BYTES;
+        sq = reinterpret_cast<float*>(p);                   p += 2 * C::SQ_BYTES;
+        sf = reinterpret_cast<float*>(p);                   p += 2 * 16 * 4;
+        item_tab = reinterpret_cast<uint4*>(p);             p += kItemSlots * kMaxItemBlocks * 16;
+        item = reinterpret_cast<ItemDesc*>(p);              p += kItemSlots * sizeof(ItemDesc);
+        desc = reinterpret_cast<Desc*>(p);                  p += kStreams * kNSlot * sizeof(Desc);
+        full = reinterpret_cast<uint64_t*>(p);              p += kStreams * kNSlot * 8;
+        empty = reinterpret_cast<uint64_t*>(p);             p += kStreams * kNSlot * 8;
+        item_full = reinterpret_cast<uint64_t*>(p);         p += kItemSlots * 8;
+        item_empty = reinterpret_cast<uint64_t*>(p);        p += kItemSlots * 8;
+        qready = reinterpret_cast<uint64_t*>(p);
     }
 };
-
-// ================================ producer ====================================================
-// Work items are numbered chunk-major: item = chunk * rows + row, and a chunk is a run of p.chunk
-// consecutive entries of the row's rung-sorted block list.  The whole grid therefore walks the
-// ladder together — all bf16 blocks first, the centroids last: the warps that share an SM run
-// the same unpack code at the same time (with the rungs interleaved the kernel spent ~15 % of
-// its time refetching instructions), and the cheapest items come last, which trims the tail.
-struct Span { int row, b_lo, nblk; };
-__device__ __forceinline__ Span span_of(const Params& p, int it) {
-    if (it >= p.items) return Span{0, 0, 0};
-    const int c = it / p.rows;
-    const int b_lo = c < p.nbig ? c * p.chunk : p.nbig * p.chunk + (c - p.nbig) * p.chunk2;
-    return Span{it % p.rows, b_lo, min(c < p.nbig ? p.chunk : p.chunk2, p.nb - b_lo)};     // nblk <= 32
-}
 
 // ---- rung-sorted block lists -----------------------------------------------------------------------
 // One CTA per metadata row: a stable counting sort of the row's blocks by rung (16, 8, 4, 2,
 // centroid, then blocks with nothing to do).  An entry is everything the producer needs to know
-// about a block: byte offset in the row (64 bit), level | nvalid << 8 (level 0: skip), block index.  Every thread owns a contiguous run of blocks, counts
-// its classes, an in-order scan over (class, thread) gives it a write cursor per class, and it
-// walks its run once more.  Deterministic: no atomics.  Also clears the workspace header.
+// about a block: byte offset in the row (64 bit), level | nvalid << 8 (level 0: skip), block index.
+// Every thread owns a contiguous run of blocks, counts its classes, an in-order scan over
+// (class, thread) gives it a write cursor per class, and it walks its run once more.  Deterministic:
+// no atomics.  The start of every class in the list goes to the row's table.  Also clears the
+// workspace header when given one.
 constexpr int kPlanMaxThreads = 1024;
 __device__ __forceinline__ int rung_class(int lv, int nv) {
     return nv <= 0 ? 5 : lv == 16 ? 0 : lv == 8 ? 1 : lv == 4 ? 2 : lv == 2 ? 3 : lv == 1 ? 4 : 5;
 }
 __global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* level, const int32_t* valid, const int64_t* offs,
-                                                                uint4* plan, int nb, int* header, int header_ints) {
+                                                                uint4* plan, int32_t* plan_tab, int nb, int* header,
+                                                                int header_ints) {
     // the decode kernel's work counter and status word start at zero
-    if (blockIdx.x == 0)
+    if (blockIdx.x == 0 && header)
         for (int i = threadIdx.x; i < header_ints; i += blockDim.x) header[i] = 0;
     __shared__ int wsum[kPlanMaxThreads / 32][6];   // per-warp class totals, then their exclusive scan
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
@@ -354,8 +361,12 @@ __global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* le
     __syncthreads();
     if (tid == 0) {
         int run = 0;
-        for (int k = 0; k < 6; ++k)
+        int32_t* tab = plan_tab + (size_t)blockIdx.x * kPlanTabInts;
+        for (int k = 0; k < 6; ++k) {
+            tab[k] = run;                           // class k occupies [tab[k], tab[k+1]) of the list
             for (int w = 0; w < nwarp; ++w) { const int t = wsum[w][k]; wsum[w][k] = run; run += t; }
+        }
+        tab[6] = nb; tab[7] = 0;
     }
     __syncthreads();
 #pragma unroll
@@ -371,196 +382,270 @@ __global__ void __launch_bounds__(kPlanMaxThreads) plan_kernel(const int32_t* le
     }
 }
 
-// The producer warp announces items (one item ahead), and for every block of the current item's
-// table (built by the query warp) lane 0 waits for room in the ring, allocates, publishes the slot
-// descriptor and starts the bulk copy of the block's bytes; the four scale planes (a few hundred
-// bytes each) are then fetched by all 32 lanes with 16-byte asynchronous copies that report to the
-// same barrier.  (Five bulk copies per block from one lane cost ~600 cycles of issue time per
-// block and made the producer the slowest stage; so did building the tables here.)
-template <int D, int G>
-__device__ void producer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
-    using C = Cfg<D, G>;
-    const int lane = threadIdx.x & 31;
+// ================================ producers ===================================================
+// Item `id` = slot * rows + row.  Slot s of a row is the s-th chunk when each rung's run of the
+// row's sorted list is cut into chunks of p.chunk blocks; slots beyond the row's last chunk are
+// empty (rows have a fixed number of slots, enough for any mix of rungs).
+struct Span { int row, level, b_lo, nblk; };
+__device__ __forceinline__ Span span_of(const Params& p, int id) {
+    Span sp{0, 0, 0, 0};
+    if (id >= p.items) return sp;
+    int slot = id / p.rows;
+    sp.row = id % p.rows;
+    const int32_t* tab = p.plan_tab + (size_t)(p.per_row_meta ? sp.row : 0) * kPlanTabInts;
+    int start = tab[0];
+#pragma unroll 1
+    for (int k = 0; k < 5; ++k) {
+        const int next = tab[k + 1], cnt = next - start;
+        const int n = (cnt + p.chunk - 1) / p.chunk;
+        if (slot < n) {
+            sp.level = ladder_level(k);
+            sp.b_lo = start + slot * p.chunk;
+            sp.nblk = min(p.chunk, cnt - slot * p.chunk);
+            return sp;
+        }
+        slot -= n;
+        start = next;
+    }
+    return sp;
+}
+
+struct ProducerState {
     uint32_t head = 0, used = 0;
     int seq_alloc = 0, seq_free = 0;
-#ifdef GKV_DBG_TIMING
-    long long p_all = clock64(), p_wait = 0, p_issue = 0, p_meta = 0, p_scale = 0, p_n = 0;
-#endif
+};
 
-    auto release_oldest = [&]() -> bool {     // all lanes, same result everywhere
-        const int s = seq_free % kNSlot;
-        if (!mbar_wait(&sm.empty[s], (uint32_t)(seq_free / kNSlot) & 1u)) return false;
-        used -= (uint32_t)sm.desc[s].pad;
-        ++seq_free;
-        return true;
-    };
-    // Lane 0: announce item number j of this CTA (its descriptor slot is free once the consumers
-    // finished item j - kItemSlots, long ago in practice).
-    auto announce = [&](int j, int id, const Span& sp, int end_seq) -> bool {
-        const int s = j % kItemSlots;
-        if (j >= kItemSlots && !mbar_wait(&sm.item_empty[s], (uint32_t)(j / kItemSlots - 1) & 1u)) return false;
-        ItemDesc it;
-        it.item = id; it.row = sp.row; it.end_seq = end_seq; it.exit = id >= p.items ? 1 : 0;
-        sm.item[s] = it;
-        mbar_arrive(&sm.item_full[s]);
-        return true;
-    };
+// One stream's blocks of one item.  Ring bookkeeping is done by all lanes alike (same values
+// everywhere, so nothing has to be broadcast); lane 0 publishes the slot descriptor and starts ONE
+// bulk copy for the block's bytes; the four scale planes of a quantised rung are fetched by all 32
+// lanes with 16-byte asynchronous copies that arrive on the same barrier.
+// Non-blocking test of a barrier phase.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 
-    int item = 0, next_item = 0;
-    if (lane == 0) { item = atomicAdd(p.counter, 1); next_item = atomicAdd(p.counter, 1); }
-    item = __shfl_sync(0xffffffffu, item, 0);
-    next_item = __shfl_sync(0xffffffffu, next_item, 0);
-    bool ok = true;
-    if (lane == 0) ok = announce(0, item, span_of(p, item), span_of(p, item).nblk);
-    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-    // Block table of an item: entry `lane` of its run of the row's plan, with the row's base offset
-    // added.  The next item's entries are requested at the start of the current item and parked in
-    // the table when its last block has been issued, so the global-memory latency is never waited for.
-    auto fetch_entry = [&](const Span& sp) -> uint4 {
-        uint4 e = make_uint4(0, 0, 0, 0);
-        if (lane < sp.nblk) {
-            e = p.plan[(size_t)(p.per_row_meta ? sp.row : 0) * p.nb + sp.b_lo + lane];
-            const unsigned long long src = (unsigned long long)sp.row * (unsigned long long)p.stride_bh +
-                                           (((unsigned long long)e.y << 32) | e.x);
-            e.x = (uint32_t)src; e.y = (uint32_t)(src >> 32);
-        }
-        return e;
-    };
-    sm.meta_tab[lane] = fetch_entry(span_of(p, item));
-    __syncwarp();
-    for (int iseq = 0; ok; ++iseq) {
-        const bool done = item >= p.items;
-        int next2 = 0;
-#ifdef GKV_DBG_TIMING
-        const long long _pm0 = clock64();
-#endif
-        const Span cs = span_of(p, item), ns = done ? Span{0, 0, 0} : span_of(p, next_item);
-        const int row = cs.row, nblk = cs.nblk;
-        if (lane == 0 && !done) {
-            next2 = atomicAdd(p.counter, 1);       // item id two ahead
-            // the next item goes out now, a whole item early: the query warp needs the time
-            ok = announce(iseq + 1, next_item, ns, seq_alloc + nblk + ns.nblk);
-        }
-        if (done) break;
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        const uint4 next_entry = fetch_entry(ns);
-        const uint4* tab = sm.meta_tab;
-        const size_t sb0 = (size_t)row * p.nb;
-        const uint8_t* klo0 = reinterpret_cast<const uint8_t*>(p.klo) + sb0 * C::KSCALE;
-        const uint8_t* kst0 = reinterpret_cast<const uint8_t*>(p.kstep) + sb0 * C::KSCALE;
-        const uint8_t* vlo0 = reinterpret_cast<const uint8_t*>(p.vlo) + sb0 * C::VSCALE;
-        const uint8_t* vst0 = reinterpret_cast<const uint8_t*>(p.vstep) + sb0 * C::VSCALE;
-#ifdef GKV_DBG_TIMING
-        p_meta += clock64() - _pm0;
-#endif
-        for (int j = 0; j < nblk && ok; ++j, ++seq_alloc) {
-            // Ring bookkeeping is done by all lanes alike (same values everywhere, so nothing has to be
-            // broadcast); only the three operations with side effects are lane 0's.
-            const uint4 cur = tab[j];
-            const int lvj = (int)(cur.z & 0xffu), orig = (int)cur.w;
-            const bool quant = lvj == 8 || lvj == 4 || lvj == 2;
-            const uint32_t dbytes = lvj ? 2u * (uint32_t)half_bytes(lvj, D) : 0u;
-            const int slot = seq_alloc % kNSlot;
-            const uint32_t need = (dbytes + (quant ? 2u * (C::KSCALE + C::VSCALE) : 0u) + 127u) & ~127u;
-#ifdef GKV_DBG_TIMING
-            const long long _pw0 = clock64();
-#endif
-            while (ok && seq_alloc - seq_free >= kNSlot) ok = release_oldest();
-            const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
-            while (ok && used + waste + need > kRingBytes) ok = release_oldest();
-#ifdef GKV_DBG_TIMING
-            const long long _pi0 = clock64();
-            p_wait += _pi0 - _pw0; ++p_n;
-#endif
-            if (!ok) break;
-            const uint32_t dst = waste ? 0u : head;
-            used += waste + need;
-            head = dst + need;
-            if (head >= kRingBytes) head = 0;
-            if (lane == 0) {
-                Desc d;
-                d.off = dst; d.level = lvj; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)(waste + need);
-                sm.desc[slot] = d;
-                const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
-                uint8_t* d0 = sm.ring + dst;
-#ifdef GKV_DBG_NOLOAD
-                if (true) { mbar_arrive(&sm.full[slot]); } else
-#endif
-                if (lvj && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                    mbar_arrive_tx(&sm.full[slot], dbytes);
-                    bulk_g2s(d0, src, dbytes, &sm.full[slot]);
-                } else {
-                    // block start not 16-byte aligned (a cache row at an odd address): no bulk copy,
-                    // this lane copies the bytes by hand
-                    for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
-                    __threadfence_block();
-                    mbar_arrive(&sm.full[slot]);
-                }
-            }
-#ifdef GKV_DBG_TIMING
-            const long long _ps0 = clock64();
-            p_issue += _ps0 - _pi0;
-#endif
-#ifndef GKV_DBG_NOLOAD
-            if (quant) {
-                const uint32_t sdst = smem_u32(sm.ring) + dst + dbytes;
-                const size_t ko = (size_t)orig * C::KSCALE, vo = (size_t)orig * C::VSCALE;
-                constexpr int K = C::KSCALE, V = C::VSCALE;
+// One stream's blocks of one item, in BATCHES: the warp reclaims the slots the consumers have
+// finished, works out (all lanes alike, plain integer arithmetic) how many of the item's next blocks
+// fit into the ring right now and where, and then lane i takes block i of the batch: it publishes the
+// slot descriptor, arms the slot's barrier and starts ONE bulk copy for the block's bytes.  The four
+// scale planes of a quantised rung are then fetched block by block by all 32 lanes with 16-byte
+// asynchronous copies that arrive on the same barrier.  A producer that handles one block per loop
+// iteration is bound by the latency of its own chain of ~60 dependent instructions (~1300 cycles per
+// block measured); batches overlap those chains, and a producer that has fallen behind catches up.
+template <int D, int G>
+__device__ __forceinline__ bool produce_item(const Params& p, Smem<D, G>& sm, ProducerState& ps, int s,
+                                             const ItemDesc& it, int islot) {
+    using C = Cfg<D, G>;
+    const int lane = threadIdx.x & 31;
+    if (it.level == 1 || it.nblk == 0) return true;     // centroid items are read straight from global memory
+    const int j0 = (s ^ it.first) & 1;                   // this stream's first block of the item
+    const int n_mine = (it.nblk - j0 + 1) >> 1;
+    const uint32_t tab = smem_u32(sm.item_tab + islot * kMaxItemBlocks + j0);      // this stream's blocks: every second entry
+    const int lv = it.level;
+    const bool quant = lv != 16;
+    const uint32_t dbytes = 2u * (uint32_t)half_bytes(lv, D);
+    constexpr int K = C::KSCALE;                         // == VSCALE: every scale plane has the same bytes per block
+    static_assert(C::KSCALE == C::VSCALE && (4 * K) % 512 == 0, "scale planes");
+    constexpr int NR = 4 * K / 512;                      // rounds of 32 lanes x 16 bytes that cover the four planes
+    const uint32_t need = (dbytes + (quant ? 4u * K : 0u) + 127u) & ~127u;
+    // This lane's 16 bytes of every round: which plane, and where inside a block's K bytes — fixed for the item.
+    const uint8_t* splane[NR];
 #pragma unroll
-                for (int o0 = 0; o0 < 2 * (K + V); o0 += 512) {
-                    const int o = o0 + lane * 16;
-                    if (o < 2 * (K + V)) {
-                        const uint8_t* src = o < K ? klo0 + ko + o : o < 2 * K ? kst0 + ko + (o - K)
-                                           : o < 2 * K + V ? vlo0 + vo + (o - 2 * K) : vst0 + vo + (o - 2 * K - V);
-                        cp_async16(sdst + (uint32_t)o, src);
-                    }
-                }
-            }
-#endif
-            cp_async_arrive(&sm.full[slot]);                    // one arrival per lane once its copies have landed
-#ifdef GKV_DBG_TIMING
-            p_scale += clock64() - _ps0;
-#endif
+    for (int i = 0; i < NR; ++i) {
+        const int o = i * 512 + lane * 16, which = o / K;           // 0 klo, 1 kstep, 2 vlo, 3 vstep
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(which == 0 ? p.klo : which == 1 ? p.kstep
+                                                               : which == 2 ? p.vlo : p.vstep);
+        splane[i] = base + (size_t)it.row * p.nb * K + (o - which * K);
+    }
+    uint64_t* full = sm.full + s * kNSlot;
+    uint64_t* empty = sm.empty + s * kNSlot;
+    Desc* desc = sm.desc + s * kNSlot;
+    const uint32_t ring = smem_u32(sm.ring) + (uint32_t)s * kRingBytes;
+    for (int j = 0; j < n_mine;) {
+        // slots the consumers are done with (oldest first; all lanes, same result everywhere)
+        while (ps.seq_free < ps.seq_alloc) {
+            const int sl = ps.seq_free % kNSlot;
+            if (!mbar_test(&empty[sl], (uint32_t)(ps.seq_free / kNSlot) & 1u)) break;
+            ps.used -= (uint32_t)desc[sl].pad;
+            ++ps.seq_free;
         }
-        if (!ok) break;
-        __syncwarp();
-        sm.meta_tab[lane] = next_entry;
-        __syncwarp();
-        item = next_item;
-        next_item = __shfl_sync(0xffffffffu, next2, 0);
-    }
-#ifdef GKV_DBG_TIMING
-    if (lane == 0) {
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.counter) + 4;
-        atomicAdd(dbg + 0, (unsigned long long)(clock64() - p_all));
-        atomicAdd(dbg + 1, (unsigned long long)p_wait);
-        atomicAdd(dbg + 2, (unsigned long long)p_issue);
-        atomicAdd(dbg + 3, (unsigned long long)p_meta);
-        atomicAdd(dbg + 4, (unsigned long long)p_scale);
-        atomicAdd(dbg + 5, (unsigned long long)p_n);
-    }
+        // how many of the next blocks fit, and where this lane's block goes
+        int nfit = 0;
+        uint32_t my_dst = 0, my_pad = 0;
+        {
+            uint32_t head = ps.head, used = ps.used;
+            const int slots = kNSlot - (ps.seq_alloc - ps.seq_free);
+            const int want = min(min(n_mine - j, 32), slots);
+            while (nfit < want) {
+                const uint32_t waste = (head + need > kRingBytes) ? kRingBytes - head : 0u;
+                if (used + waste + need > kRingBytes) break;
+                const uint32_t dst = waste ? 0u : head;
+                if (lane == nfit) { my_dst = dst; my_pad = waste + need; }
+                used += waste + need;
+                head = dst + need;
+                if (head >= kRingBytes) head = 0;
+                ++nfit;
+            }
+            if (nfit == 0) {                             // nothing fits: wait for the oldest block to be released
+                const int sl = ps.seq_free % kNSlot;
+                if (!mbar_wait(&empty[sl], (uint32_t)(ps.seq_free / kNSlot) & 1u)) return false;
+                ps.used -= (uint32_t)desc[sl].pad;
+                ++ps.seq_free;
+                continue;
+            }
+            ps.head = head;
+            ps.used = used;
+        }
+        const int my_seq = ps.seq_alloc + lane;
+        const int my_slot = my_seq % kNSlot;
+        uint4 cur = make_uint4(0, 0, 0, 0);
+        bool withhold = false;
+        if (lane < nfit) {
+            cur = lds_v4(tab + 32u * (uint32_t)(j + lane));
+#ifdef GKV_TEST_WITHHOLD_BLOCK
+            // test build only: the second block of stream 0 never arrives, so the waits on it run out
+            withhold = s == 0 && my_seq == 1;
 #endif
+            Desc d;
+            d.off = my_dst; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)my_pad; d.unused = 0;
+            desc[my_slot] = d;
+            const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
+            if (withhold) {
+            } else if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                mbar_arrive_tx(&full[my_slot], dbytes);
+                bulk_g2s(ring + my_dst, src, dbytes, &full[my_slot]);
+            } else {
+                // block start not 16-byte aligned (a cache row at an odd address): no bulk copy,
+                // this lane copies the bytes by hand
+                uint8_t* d0 = sm.ring + (size_t)s * kRingBytes + my_dst;
+                for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
+                __threadfence_block();
+                mbar_arrive(&full[my_slot]);
+            }
+        }
+        __syncwarp();
+        // the four scale planes (a few hundred bytes each) of every block of the batch: 16 bytes per lane
+        // and round, asynchronous, reporting to the block's barrier (one bulk copy per plane would cost
+        // the warp ~200 cycles each)
+        const unsigned held = __ballot_sync(0xffffffffu, withhold);
+#pragma unroll 2
+        for (int i = 0; i < nfit; ++i) {
+            const uint32_t dst_i = __shfl_sync(0xffffffffu, my_dst, i);
+            const uint32_t orig_i = __shfl_sync(0xffffffffu, cur.w, i);
+            const int slot_i = (ps.seq_alloc + i) % kNSlot;
+            if ((held >> i) & 1u) continue;
+            if (quant) {
+                const uint32_t sdst = ring + dst_i + dbytes + (uint32_t)lane * 16u;
+                const size_t so = (size_t)orig_i * K;
+#pragma unroll
+                for (int r = 0; r < NR; ++r) cp_async16(sdst + (uint32_t)(r * 512), splane[r] + so);
+            }
+            cp_async_arrive(&full[slot_i]);              // one arrival per lane once its copies have landed
+        }
+        ps.seq_alloc += nfit;
+        j += nfit;
+    }
+    return true;
+}
+
+// The scheduler warp draws the work items (an atomic counter), looks up what each one is, fetches
+// its block entries into the item's table in shared memory and announces it — up to kItemSlots - 1
+// items ahead of the consumers, so none of this global-memory latency is ever waited for by the
+// producers or the consumers.  Items without blocks are not announced: their records are marked
+// empty right here.
+template <int D, int G>
+__device__ void scheduler_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
+    const int lane = threadIdx.x & 31;
+    int tot0 = 0, tot1 = 0, nfirst = 0;
+    bool ok = true;
+    for (int j = 0; ok; ++j) {
+        ItemDesc it;
+        for (;;) {                                          // draw the next item that has blocks
+            int id = 0;
+            if (lane == 0) id = atomicAdd(p.counter, 1);
+            id = __shfl_sync(0xffffffffu, id, 0);
+            const Span sp = span_of(p, id);                 // same loads in every lane (broadcast)
+            it.item = id; it.row = sp.row; it.level = sp.level; it.b_lo = sp.b_lo; it.nblk = sp.nblk;
+            it.exit = id >= p.items ? 1 : 0;
+            it.pad[0] = it.pad[1] = it.pad[2] = 0;
+            if (it.exit || sp.nblk > 0) break;
+            // an empty slot of the row: every consumer warp's record says "nothing" (m = -inf)
+            const size_t rec_idx = (size_t)sp.row * p.items_per_row + (size_t)(id / p.rows);
+            float* rec = p.part + rec_idx * kConsumerWarps * p.rep * (D + 2);
+            for (int i = lane; i < kConsumerWarps * p.rep; i += 32) {
+                rec[(size_t)i * (D + 2)] = -INFINITY;
+                rec[(size_t)i * (D + 2) + 1] = 0.f;
+            }
+        }
+        it.first = nfirst & 1;
+        if (!it.exit && it.level != 1) {
+            const int n0 = (it.nblk + 1) >> 1, n1 = it.nblk >> 1;       // the first stream gets the odd block
+            if (it.first) { tot1 += n0; tot0 += n1; } else { tot0 += n0; tot1 += n1; }
+            ++nfirst;
+        }
+        it.end_seq0 = tot0;
+        it.end_seq1 = tot1;
+        // the item's block entries, two per lane, with the row's base offset added
+        uint4 e[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            e[h] = make_uint4(0, 0, 0, 0);
+            const int i = lane + 32 * h;
+            if (!it.exit && i < it.nblk) {
+                e[h] = p.plan[(size_t)(p.per_row_meta ? it.row : 0) * p.nb + it.b_lo + i];
+                const unsigned long long src = (unsigned long long)it.row * (unsigned long long)p.stride_bh +
+                                               (((unsigned long long)e[h].y << 32) | e[h].x);
+                e[h].x = (uint32_t)src; e[h].y = (uint32_t)(src >> 32);
+            }
+        }
+        // the descriptor slot is free once everybody has finished item j - kItemSlots
+        const int sl = j % kItemSlots;
+        if (j >= kItemSlots) ok = mbar_wait(&sm.item_empty[sl], (uint32_t)(j / kItemSlots - 1) & 1u);
+        if (!ok) break;
+        sm.item_tab[sl * kMaxItemBlocks + lane] = e[0];
+        sm.item_tab[sl * kMaxItemBlocks + lane + 32] = e[1];
+        if (lane == 0) sm.item[sl] = it;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.item_full[sl]);
+        if (it.exit) return;
+        if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+    }
     if (!ok && lane == 0) {
         atomicExch(p.status, 1);
         atomicExch(abort_flag, 1);
     }
 }
 
-// ================================ consumers ===================================================
+// Producer of stream s: for every announced item, streams the item's blocks of its stream into its ring.
 template <int D, int G>
-struct WarpState {
-    using C = Cfg<D, G>;
-    float o[C::NTILE][4];   // rows r (c0,c1) and r+8 (c2,c3) of every output n-tile, scaled 2^-16
-    float ob[4];            // sum_j p_j * vlo[j][cg], scaled 2^8
-    float m;                // running max of head r (log2 domain), replicated over the quad
-    float l;              // this thread's share of the running sum
-};
+__device__ void producer_loop(const Params& p, Smem<D, G>& sm, int s, int* abort_flag) {
+    const int lane = threadIdx.x & 31;
+    ProducerState ps;
+    bool ok = true;
+    for (int j = 0; ok; ++j) {
+        const int sl = j % kItemSlots;
+        if (!mbar_wait(&sm.item_full[sl], (uint32_t)(j / kItemSlots) & 1u)) { ok = false; break; }
+        const ItemDesc it = sm.item[sl];
+        if (it.exit) return;
+        ok = produce_item<D, G>(p, sm, ps, s, it, sl);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.item_empty[sl]);      // this warp no longer needs the item's descriptor and table
+        if (*reinterpret_cast<volatile int*>(abort_flag)) return;
+    }
+    if (!ok && lane == 0) {
+        atomicExch(p.status, 9 + s);
+        atomicExch(abort_flag, 1);
+    }
+}
 
 // ================================ query warp ==================================================
 // For every announced item: the row's query heads as fp32 (for the centroid path), a per-head
-// power-of-two scale, and the MMA A-fragment planes of every channel arrangement, into the
-// buffer of the item's parity.  Runs one item ahead of the consumers.
-template <int D, int G>
+// power-of-two scale, and the MMA A-fragment planes (hi, lo) in the channel arrangement of the
+// item's rung, into the buffer of the item's parity.  Runs one item ahead of the consumers.
+template <int D, int G, bool DUP>
 __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     const int lane = threadIdx.x & 31;
@@ -594,38 +679,28 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
             }
         }
         __syncwarp();
-        // which rungs does the item hold?  (its run of the sorted plan; usually one or two)
-        const Span sp = span_of(p, it.item);
-        int lvl = 0;
-        if (lane < sp.nblk) lvl = (int)(p.plan[(size_t)(p.per_row_meta ? sp.row : 0) * p.nb + sp.b_lo + lane].z & 0xffu);
-        const bool need8 = __any_sync(0xffffffffu, lvl == 8), need4 = __any_sync(0xffffffffu, lvl == 4);
-        const bool need2 = __any_sync(0xffffffffu, lvl == 2), need16 = __any_sync(0xffffffffu, lvl == 16);
         // This lane writes its own fragment lane of every chunk: 8 halves (two k-steps x four slots)
-        // per plane and chunk, as one 16-byte store.  Only the arrangements of rungs that occur.
-        {
+        // per plane and chunk, as one 16-byte store.
+        if (it.level != 1) {
             const int r = lane >> 2, t = lane & 3;
-            const float sc = sf[8 + r];
-            const float* qr = sq + r * D + C::DT * t;
-#pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const int bits = a == 0 ? 8 : a == 1 ? 4 : a == 2 ? 2 : 16;
-                const bool need = a == 0 ? need8 : a == 1 ? need4 : a == 2 ? need2 : need16;
-                if (!need) continue;
+            const int head = head_of_row<DUP>(r);
+            const float sc = sf[8 + head];
+            const float* qr = sq + head * D + C::DT * t;
+            const int bits = it.level;
 #pragma unroll 1
-                for (int i = 0; i < C::CH; ++i) {
-                    uint32_t hi[4], lo[4];
+            for (int i = 0; i < C::CH; ++i) {
+                uint32_t hi[4], lo[4];
 #pragma unroll
-                    for (int jp = 0; jp < 4; ++jp) {            // halves 2jp, 2jp+1: k-step 2i + (jp >> 1), slots 2(jp & 1) + {0, 1}
-                        const int ks = 2 * i + (jp >> 1), e0 = 2 * (jp & 1);
-                        const float x0 = qr[arr_chan(bits, ks, e0)] * sc * arr_scale(bits, e0);
-                        const float x1 = qr[arr_chan(bits, ks, e0 + 1)] * sc * arr_scale(bits, e0 + 1);
-                        if (a < 3) split_f16x2(x0, x1, hi[jp], lo[jp]);
-                        else split_bf16x2(x0, x1, hi[jp], lo[jp]);
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(qp + (size_t)(2 * a) * C::QPLANE + ((size_t)i * 32 + lane) * 8);
-                    dst[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    dst[C::QPLANE / 8] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                for (int jp = 0; jp < 4; ++jp) {            // halves 2jp, 2jp+1: k-step 2i + (jp >> 1), slots 2(jp & 1) + {0, 1}
+                    const int ks = 2 * i + (jp >> 1), e0 = 2 * (jp & 1);
+                    const float x0 = qr[arr_chan(bits, ks, e0)] * sc * arr_scale(bits, e0);
+                    const float x1 = qr[arr_chan(bits, ks, e0 + 1)] * sc * arr_scale(bits, e0 + 1);
+                    if (bits != 16) split_f16x2(x0, x1, hi[jp], lo[jp]);
+                    else split_bf16x2(x0, x1, hi[jp], lo[jp]);
                 }
+                uint4* dst = reinterpret_cast<uint4*>(qp + ((size_t)i * 32 + lane) * 8);
+                dst[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                dst[C::QPLANE / 8] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
         }
         __syncwarp();
@@ -637,12 +712,10 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     }
 }
 
+// ================================ consumers ===================================================
 // The blocks are processed in UNITS of G tokens (one token group of the K scales): scores of
-// the unit, online-softmax update, value product of the unit.  Loops over the contraction
-// (chunks of two k-steps on the K side, 16-token k-steps on the V side) are real loops, not
-// unrolled: the fully unrolled kernel was 130 KB of code and spent most of its time waiting
-// for instruction fetches.  All shared-memory operands are addressed by 32-bit shared
-// addresses built from one per-thread base plus compile-time offsets.
+// the unit, online-softmax update, value product of the unit.  All shared-memory operands are
+// addressed by 32-bit shared addresses built from one per-thread base plus compile-time offsets.
 template <int D, int G>
 struct Unit {
     static constexpr int U = G;          // tokens
@@ -651,19 +724,22 @@ struct Unit {
     static constexpr int ZN = G / 4;     // scores held per thread
 };
 
-// Inside every 8-token n-tile of a quantised block, score column c stands for token
-// token_of_column(c) = (0, 1, 3, 2, 4, 5, 7, 6)[c].  On the K side that is just which row a lane
-// reads; on the V side it makes the four lanes of a quad read token rows of alternating parity
-// (t, t+1 swapped for odd t), which halves the bank conflicts of the 4-bit value rows, while a
-// lane's two tokens of a k-pair stay neighbours so their scales still come from one load.
-__device__ __forceinline__ int token_of_column(int c) { return c ^ ((c >> 1) & 1); }
+template <int D, int G>
+struct WarpState {
+    using C = Cfg<D, G>;
+    float o[C::MT][4];      // transposed output: channel rows (c0,c1) and their partners (c2,c3), head columns 2t, 2t+1; scaled 2^-16
+    float ob[4];            // sum_j p_j * vlo[j][cg] for cg = r mod GV (c0, c1), head columns 2t, 2t+1; scaled 2^8
+    float m;                // running reference of this thread's head (log2 domain), uniform over the quad
+    float l;                // this thread's share of the running sum
+};
 
 template <int D, int G>
 struct Ctx {                             // per-thread constants of the consumer role
-    uint32_t qprep;                      // shared address of this lane's first prepared-query chunk (plane 0)
+    uint32_t qprep;                      // shared address of this lane's first prepared-query chunk (hi plane)
     uint32_t sq;                         // shared address of the fp32 query rows
-    float f;                             // 2^-eq * log2(e) of head r
+    float f;                             // 2^-eq * log2(e) of this thread's head
     int r, t, lane;
+    bool part;                           // with head pairs in the rows: this thread feeds the lo column of its head
 };
 
 template <int D, int G>
@@ -672,13 +748,13 @@ __device__ __forceinline__ uint4 qchunk(const Ctx<D, G>& c, int plane, int i) {
 }
 
 // ---- K side of one unit of a quantised block: scores in the log2 domain ---------------------------
+// Score column n of n-tile j stands for token 8j + n of the unit.
 template <int D, int G, int BITS>
 __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, int tg, float (&z)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
     constexpr int RB = D * BITS / 8;                     // bytes per token row
     constexpr int TB = RB / 4;                           // bytes per thread per row
-    constexpr int plane = BITS == 8 ? 0 : BITS == 4 ? 2 : 4;
     const uint32_t nat = blk + (uint32_t)(2 * (kP * RB) + C::KSCALE + (tg * D + C::DT * c.t) * 2);
     // The thread's codes of a token row are fetched with the widest load that fits (all chunks at
     // once for 4- and 2-bit codes): a quarter warp then reads whole rows side by side, free of the
@@ -689,7 +765,7 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     constexpr int CG = LB / CB;                          // chunks per fetch
     constexpr int LW = LB / 4;
     static_assert(LB >= 4 && C::CH % CG == 0, "unsupported shape");
-    const uint32_t row0 = blk + (uint32_t)((tg * UU::U + token_of_column(c.r)) * RB + c.t * TB);
+    const uint32_t row0 = blk + (uint32_t)((tg * UU::U + c.r) * RB + c.t * TB);
 
     float acc[UU::NU][4];
 #pragma unroll
@@ -698,11 +774,7 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     // group's klo (so every thread ends up with its own head's value, no shuffle); two accumulators,
     // one per k-step of a chunk, keep the MMAs independent.
     float bias0[4] = {0.f, 0.f, 0.f, 0.f}, bias1[4] = {0.f, 0.f, 0.f, 0.f};
-#ifndef GKV_K_ROLLED
 #pragma unroll
-#else
-#pragma unroll 1
-#endif
     for (int g = 0; g < C::CH / CG; ++g) {
         uint32_t W[UU::NU][LW];
 #pragma unroll
@@ -715,7 +787,7 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
 #pragma unroll
         for (int ii = 0; ii < CG; ++ii) {                // two k-steps at a time
             const int i = g * CG + ii;
-            const uint4 qh = qchunk(c, plane, i), ql = qchunk(c, plane + 1, i);
+            const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
             uint32_t sp[4], lp[4];                       // kstep / klo pairs of k-steps 2i and 2i+1 in this arrangement
             if (BITS == 8) {
                 const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
@@ -790,9 +862,9 @@ __device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t bl
     float acc[UU::NU][4];
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-#pragma unroll 1
+#pragma unroll 2
     for (int i = 0; i < C::CH; ++i) {
-        const uint4 qh = qchunk(c, 6, i), ql = qchunk(c, 7, i);
+        const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
         uint4 w[UU::NU];
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) w[n] = lds_v4(row0 + 16 * i + n * 8 * D * 2);
@@ -811,12 +883,14 @@ __device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t bl
 // ---- online-softmax update ---------------------------------------------------------------------
 // The running reference m only moves when a score exceeds it by more than kLazy (log2 domain):
 // until then weights are taken against the stale reference and may reach 2^kLazy.  That keeps
-// the accumulator rescale (one FMUL per output register) off the common path; the fp16 weight
-// operands still fit (p * 2^8 * step < 65504 for any step < 16).
+// the accumulator rescale off the common path; the fp16 weight operands still fit
+// (p * 2^8 * step < 65504 for any step < 16).
 constexpr float kLazy = 4.0f;
 
-template <int D, int G>
-__device__ __forceinline__ float move_reference(WarpState<D, G>& st, float mx) {
+// The accumulators are indexed by head COLUMN (2t, 2t+1) while the reference belongs to the head of
+// the thread's ROW, so the rescale factors of the two columns come from the lanes that own them.
+template <int D, int G, bool DUP>
+__device__ __forceinline__ float move_reference(const Ctx<D, G>& c, WarpState<D, G>& st, float mx) {
     using C = Cfg<D, G>;
     const bool need = mx > st.m + kLazy || st.m == -INFINITY;   // per head (uniform over the quad)
     if (__any_sync(0xffffffffu, need)) {
@@ -824,30 +898,38 @@ __device__ __forceinline__ float move_reference(WarpState<D, G>& st, float mx) {
         const float corr = ex2(st.m - mnew);          // 0 when st.m = -inf, 1 for the heads that stay
         st.m = mnew;
         st.l *= corr;
+        // column 2t is head t (and 2t+1 its lo column), or heads 2t and 2t+1; row 2h (resp. h) is a thread of head h
+        const float c0 = __shfl_sync(0xffffffffu, corr, 8 * c.t);
+        const float c1 = DUP ? c0 : __shfl_sync(0xffffffffu, corr, 8 * c.t + 4);
 #pragma unroll
-        for (int n = 0; n < C::NTILE; ++n) {
-            st.o[n][0] *= corr; st.o[n][1] *= corr; st.o[n][2] *= corr; st.o[n][3] *= corr;
+        for (int n = 0; n < C::MT; ++n) {
+            st.o[n][0] *= c0; st.o[n][1] *= c1; st.o[n][2] *= c0; st.o[n][3] *= c1;
         }
-        st.ob[0] *= corr; st.ob[1] *= corr; st.ob[2] *= corr; st.ob[3] *= corr;
+        st.ob[0] *= c0; st.ob[1] *= c1; st.ob[2] *= c0; st.ob[3] *= c1;
     }
     return st.m;
 }
 
-// z: scores of head r for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid tokens
-// left in this unit (>= 1).  Returns the weights in z.
-template <int D, int G, bool PERM>
+// z: scores of this thread's head for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid
+// tokens left in this unit (>= 1).  Returns the weights in z.
+template <int D, int G, bool DUP>
 __device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel) {
     using UU = Unit<D, G>;
     float mx = -INFINITY;
+    if (nrel >= UU::U) {                                 // full unit (the common case): no masks
 #pragma unroll
-    for (int i = 0; i < UU::ZN; ++i) {
-        const int tok = (i >> 1) * 8 + (PERM ? token_of_column(2 * c.t + (i & 1)) : 2 * c.t + (i & 1));
-        if (tok >= nrel) z[i] = -INFINITY;
-        mx = fmaxf(mx, z[i]);
+        for (int i = 0; i < UU::ZN; ++i) mx = fmaxf(mx, z[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < UU::ZN; ++i) {
+            const int tok = (i >> 1) * 8 + 2 * c.t + (i & 1);
+            if (tok >= nrel) z[i] = -INFINITY;
+            mx = fmaxf(mx, z[i]);
+        }
     }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m = move_reference(st, mx);
+    const float m = move_reference<D, G, DUP>(c, st, mx);
     float ls = 0.f;
 #pragma unroll
     for (int i = 0; i < UU::ZN; ++i) {
@@ -857,134 +939,190 @@ __device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>
     st.l += ls;
 }
 
-// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane at shared address `row` (token `tok`, even);
-// `odd` swaps the two tokens of every pair (see token_of_column).
+// Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane at shared address `row` (token `tok`, even).
 template <int GV>
-__device__ __forceinline__ void scale_pairs(uint32_t row, bool odd, uint32_t (&out)[GV]) {
-    const uint32_t lo = odd ? 0x1054u : 0x5410u, hi = odd ? 0x3276u : 0x7632u;
-    if (GV == 4) {
+__device__ __forceinline__ void scale_pairs(uint32_t row, uint32_t (&out)[GV]) {
+    if (GV == 8) {
+        const uint4 a = lds_v4(row), b = lds_v4(row + 16);
+        out[0] = prmt(a.x, b.x, 0x5410); out[1 % GV] = prmt(a.x, b.x, 0x7632);
+        out[2 % GV] = prmt(a.y, b.y, 0x5410); out[3 % GV] = prmt(a.y, b.y, 0x7632);
+        out[4 % GV] = prmt(a.z, b.z, 0x5410); out[5 % GV] = prmt(a.z, b.z, 0x7632);
+        out[6 % GV] = prmt(a.w, b.w, 0x5410); out[7 % GV] = prmt(a.w, b.w, 0x7632);
+    } else if (GV == 4) {
         const uint4 v = lds_v4(row);
-        out[0] = prmt(v.x, v.z, lo); out[1] = prmt(v.x, v.z, hi);
-        out[2 % GV] = prmt(v.y, v.w, lo); out[3 % GV] = prmt(v.y, v.w, hi);
+        out[0] = prmt(v.x, v.z, 0x5410); out[1 % GV] = prmt(v.x, v.z, 0x7632);
+        out[2 % GV] = prmt(v.y, v.w, 0x5410); out[3 % GV] = prmt(v.y, v.w, 0x7632);
     } else if (GV == 2) {
         const uint2 v = lds_v2(row);
-        out[0] = prmt(v.x, v.y, lo); out[1 % GV] = prmt(v.x, v.y, hi);
+        out[0] = prmt(v.x, v.y, 0x5410); out[1 % GV] = prmt(v.x, v.y, 0x7632);
     } else {
-        const uint32_t ra = row + (odd ? 2 * GV : 0), rb = row + (odd ? 0 : 2 * GV);
 #pragma unroll
-        for (int cg = 0; cg < GV; ++cg) out[cg] = lds_u16(ra + 2 * cg) | (lds_u16(rb + 2 * cg) << 16);
+        for (int cg = 0; cg < GV; ++cg) out[cg] = lds_u16(row + 2 * cg) | (lds_u16(row + 2 * GV + 2 * cg) << 16);
     }
 }
 
-// ---- V side of one unit of a quantised block -------------------------------------------------------
+// ---- V side: the transposed product O^T[channel][head] += V^T[channel][token] * (p*vstep)[token][head] -------
+// How a thread's value codes reach its A registers.  A SPAN is the set of channels whose codes one
+// fetch delivers: the 16-byte chunk of a token row that ldmatrix.trans hands out (128/BITS channels;
+// used for 8-bit codes, and for 4-bit codes when a channel group is at least a chunk), or one
+// channel group fetched with a plain byte load (2-bit codes, and 4-bit codes with 16-channel groups).
+// Either way thread r owns F = SP/8 neighbouring fields of every span, fields 2k and 2k+1 feed rows r
+// and r+8 of the span's m-tile k, and the register R = {fields of token a | fields of token a+1 << 16}
+// is unpacked by one shift and two masks per m-tile: the even field lands on bit POS, the odd one
+// BITS higher, so rows r+8 carry 2^BITS more weight, which the epilogue takes back out.
 template <int D, int G, int BITS>
+struct VT {
+    static constexpr bool LDSM = BITS == 8 || (BITS == 4 && G >= 32);
+    static constexpr int SP = LDSM ? 128 / BITS : G;     // channels per span
+    static constexpr int F = SP / 8;                     // fields per thread and span
+    static constexpr int MTS = F / 2;                    // m-tiles per span
+    static constexpr int SPC = G / SP;                   // spans per channel group
+    static constexpr int NSPAN = D / SP;
+    static constexpr int RB = D * BITS / 8;
+    static constexpr int POS = BITS == 4 ? 3 : BITS == 2 ? 6 : 0;
+    static constexpr int LOAD_BITS = F * BITS;           // bits of one token a thread needs per span (plain-load path)
+    static_assert(F >= 2 && F % 2 == 0 && SPC >= 1, "unsupported shape");
+};
+__host__ __device__ constexpr float v_pscale(int bits) { return bits == 4 ? 32.f : bits == 2 ? 4.f : 256.f; }   // 2^(8-POS)
+__host__ __device__ constexpr float v_rowscale(int bits) { return bits == 4 ? 16.f : bits == 2 ? 4.f : 1.f; }   // weight of rows r+8 over rows r
+
+// A registers (rows r, r+8) of m-tile k of a span from R (the thread's first field at bit 0 of each half).
+template <int BITS, int POS>
+__device__ __forceinline__ void extract_pair(uint32_t R, int k, uint32_t& even, uint32_t& odd) {
+    if (BITS == 8) {
+        even = prmt(R, 0u, 0x4240);
+        odd = prmt(R, 0u, 0x4341);
+    } else {
+        constexpr uint32_t FM = (1u << BITS) - 1u;
+        const int sh = POS - 2 * k * BITS;
+        const uint32_t u = sh >= 0 ? (R << sh) : (R >> (-sh));
+        even = u & ((FM << POS) * 0x00010001u);
+        odd = u & ((FM << (POS + BITS)) * 0x00010001u);
+    }
+}
+
+// Part of (ph + pl) * s that this thread's column carries: hi = rn(ph*s) or lo = rn(pl*s + (ph*s - hi)).
+__device__ __forceinline__ uint32_t mul_part(uint32_t ph, uint32_t pl, uint32_t s, bool lo_part) {
+    const __half2 h = __hmul2(u32_as_h2(ph), u32_as_h2(s));
+    const __half2 e = __hfma2(u32_as_h2(ph), u32_as_h2(s), __hneg2(h));
+    const __half2 l = __hfma2(u32_as_h2(pl), u32_as_h2(s), e);
+    return lo_part ? h2_as_u32(l) : h2_as_u32(h);
+}
+
+template <int D, int G, int BITS, bool DUP>
 __device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int unit,
-                                            float (&pz)[Unit<D, G>::ZN]) {
+                                            const float (&pz)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
-    constexpr int RB = D * BITS / 8;
-    constexpr int NB = C::NT * BITS;                 // bits one thread reads per token per channel group
-    constexpr int POS = v_pos(BITS);                 // codes are brought to bits [POS, POS+BITS) of each half
-    constexpr uint32_t MASK = (((1u << BITS) - 1u) << POS) * 0x00010001u;
-    constexpr float PSCALE = (float)(256 >> POS);    // weights carry 2^(8-POS) so that every rung adds p*v*2^-16
-    const __half2 lo_scale = __float2half2_rn((float)(1 << POS));
-    const int tok0 = unit * UU::U + 2 * c.t;         // lower token of this thread's pair in k-step 0
-    const bool odd = c.t & 1;                        // odd lanes of a quad take their pair in swapped order
-    const uint32_t sw = odd ? RB : 0;
-    // codes of (token tok0, channels NT*r .. of group 0); scale rows of token tok0
-    uint32_t vrow = blk + (uint32_t)(kP * RB + tok0 * RB + (C::NT * c.r * BITS) / 8);
-    uint32_t srow = blk + (uint32_t)(2 * (kP * RB) + 2 * C::KSCALE + tok0 * C::GV * 2);
-    constexpr int SUB = ((C::NT * BITS) % 8) ? 1 : 0;  // thread's field starts inside a byte (g=16, 2-bit)
-    const int subshift = SUB ? ((C::NT * c.r * BITS) & 7) : 0;
-#pragma unroll 1
-    for (int ku = 0; ku < UU::KU; ++ku, vrow += 16 * RB, srow += 16 * C::GV * 2) {
+    using V = VT<D, G, BITS>;
+    constexpr int RB = V::RB;
+    constexpr float PSCALE = v_pscale(BITS);
+    const uint32_t vbase = blk + (uint32_t)(kP * RB);
+    const uint32_t sbase = blk + (uint32_t)(2 * (kP * RB) + 2 * C::KSCALE);       // vlo plane; vstep follows
+    const int tok0 = unit * UU::U + 2 * c.t;            // lower token of this thread's first pair
+    // ldmatrix row of this lane: token (lane & 7) of the first or second half of a k-step, chunk +0 / +1
+    const uint32_t ldsm_lane = vbase + (uint32_t)((unit * UU::U + (c.lane & 7) + 8 * ((c.lane >> 3) & 1)) * RB + 16 * (c.lane >> 4));
+    // plain-load path: this thread's fields of (token tok0, span 0)
+    const uint32_t lds_lane = vbase + (uint32_t)(tok0 * RB + (c.r * V::LOAD_BITS) / 8);
+    const int sub = (V::LOAD_BITS % 8) ? ((c.r * V::LOAD_BITS) & 7) : 0;
+    const int cgr = c.r % C::GV;
+#pragma unroll
+    for (int ku = 0; ku < UU::KU; ++ku) {
         uint32_t ph[2], pl[2];
-        split_f16x2(pz[0] * PSCALE, pz[1] * PSCALE, ph[0], pl[0]);
-        split_f16x2(pz[2] * PSCALE, pz[3] * PSCALE, ph[1], pl[1]);
-#pragma unroll
-        for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];       // next k-step's weights move to the front
-        uint32_t sa[C::GV], sb[C::GV], la[C::GV], lb[C::GV];
-        scale_pairs<C::GV>(srow + C::VSCALE, odd, sa);                // vstep, the lane's token pair of n-tile 2ku
-        scale_pairs<C::GV>(srow + C::VSCALE + 8 * C::GV * 2, odd, sb);  // vstep, its pair of n-tile 2ku+1
-        scale_pairs<C::GV>(srow, odd, la);                            // vlo
-        scale_pairs<C::GV>(srow + 8 * C::GV * 2, odd, lb);
-        // p . vlo: column n of this n-tile is channel group n
+        split_f16x2(pz[4 * ku + 0] * PSCALE, pz[4 * ku + 1] * PSCALE, ph[0], pl[0]);
+        split_f16x2(pz[4 * ku + 2] * PSCALE, pz[4 * ku + 3] * PSCALE, ph[1], pl[1]);
+        const uint32_t srow = sbase + (uint32_t)((tok0 + 16 * ku) * C::GV * 2);
+        uint32_t sa[C::GV], sb[C::GV];
+        scale_pairs<C::GV>(srow + C::VSCALE, sa);                      // vstep of the pair in n-tile 2ku
+        scale_pairs<C::GV>(srow + C::VSCALE + 8 * C::GV * 2, sb);      // ... and of the pair in n-tile 2ku+1
+        // p . vlo: row r of this tile is channel group r mod GV
         {
-            uint32_t b0 = 0, b1 = 0;
-#pragma unroll
-            for (int cg = 0; cg < C::GV; ++cg)
-                if (c.r == cg) { b0 = la[cg]; b1 = lb[cg]; }
-            if (POS) {                                 // keep the 2^8 scale of the p . vlo accumulator
-                b0 = h2_as_u32(__hmul2(u32_as_h2(b0), lo_scale));
-                b1 = h2_as_u32(__hmul2(u32_as_h2(b1), lo_scale));
+            uint32_t la = lds_u16(srow + 2 * cgr) | (lds_u16(srow + 2 * C::GV + 2 * cgr) << 16);
+            uint32_t lb = lds_u16(srow + 16 * C::GV + 2 * cgr) | (lds_u16(srow + 18 * C::GV + 2 * cgr) << 16);
+            if (V::POS) {                               // keep the 2^8 scale of the p . vlo accumulator
+                const __half2 lo_scale = __float2half2_rn((float)(1 << V::POS));
+                la = h2_as_u32(__hmul2(u32_as_h2(la), lo_scale));
+                lb = h2_as_u32(__hmul2(u32_as_h2(lb), lo_scale));
             }
-            mma_f16(st.ob, ph[0], pl[0], ph[1], pl[1], b0, b1);
+            if (DUP) {
+                mma_f16(st.ob, la, 0u, lb, 0u, c.part ? pl[0] : ph[0], c.part ? pl[1] : ph[1]);
+            } else {
+                mma_f16(st.ob, la, 0u, lb, 0u, ph[0], ph[1]);
+                mma_f16(st.ob, la, 0u, lb, 0u, pl[0], pl[1]);
+            }
+        }
+        // value codes of this k-step: Rlo[s] / Rhi[s] = span s, token pairs of n-tiles 2ku / 2ku+1
+        uint32_t Rlo[V::NSPAN], Rhi[V::NSPAN];
+        if (V::LDSM) {
+#pragma unroll
+            for (int s2 = 0; s2 < V::NSPAN / 2; ++s2)
+                ldsm_x4_trans(ldsm_lane + (uint32_t)(ku * 16 * RB + 32 * s2), Rlo[2 * s2], Rhi[2 * s2],
+                              Rlo[(2 * s2 + 1) % V::NSPAN], Rhi[(2 * s2 + 1) % V::NSPAN]);
+        } else {
+#pragma unroll
+            for (int s = 0; s < V::NSPAN; ++s) {
+                uint32_t x[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t src = lds_lane + (uint32_t)((16 * ku + ((k & 2) ? 8 : 0) + (k & 1)) * RB + (s * V::SP * BITS) / 8);
+                    x[k] = V::LOAD_BITS > 8 ? lds_u16(src) : (lds_u8(src) >> sub);
+                }
+                Rlo[s] = prmt(x[0], x[1], 0x5410);
+                Rhi[s] = prmt(x[2], x[3], 0x5410);
+            }
         }
 #pragma unroll
         for (int cg = 0; cg < C::GV; ++cg) {
-            uint32_t a0, a1, a2, a3;
-            mul_split(ph[0], pl[0], sa[cg], a0, a1);
-            mul_split(ph[1], pl[1], sb[cg], a2, a3);
-            // codes of this thread's NT channels for the four tokens ta, ta+1, tb, tb+1
-            uint32_t x[4][(NB + 31) / 32];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t src = vrow + ((k & 1) ? RB - sw : sw) + (uint32_t)(((k & 2) ? 8 : 0) * RB + (G * cg * BITS) / 8);
-                if (NB >= 32) {
-#pragma unroll
-                    for (int w = 0; w < (NB + 31) / 32; ++w) x[k][w] = lds_u32(src + 4 * w);
-                } else if (NB == 16) {
-                    x[k][0] = lds_u16(src);
-                } else {
-                    x[k][0] = lds_u8(src) >> subshift;
-                }
+            uint32_t b0h, b0l, b1h, b1l;
+            if (DUP) {
+                b0h = mul_part(ph[0], pl[0], sa[cg], c.part);
+                b1h = mul_part(ph[1], pl[1], sb[cg], c.part);
+                b0l = b1l = 0u;
+            } else {
+                mul_split(ph[0], pl[0], sa[cg], b0h, b0l);
+                mul_split(ph[1], pl[1], sb[cg], b1h, b1l);
             }
 #pragma unroll
-            for (int i = 0; i < C::NT; ++i) {
-                const int bp = i * BITS;              // bit position of channel i inside x
-                const int w = bp / 32, wb = bp % 32;
-                // pack the two tokens' 16-bit halves that contain the field, then shift/mask
-                const uint32_t selA = (wb < 16) ? 0x5410u : 0x7632u;
-                const uint32_t pa = prmt(x[0][w], x[1][w], selA), pb = prmt(x[2][w], x[3][w], selA);
-                const int sh = wb % 16;
-                const uint32_t b0 = (sh >= POS ? pa >> (sh - POS) : pa << (POS - sh)) & MASK;
-                const uint32_t b1 = (sh >= POS ? pb >> (sh - POS) : pb << (POS - sh)) & MASK;
-                mma_f16(st.o[cg * C::NT + i], a0, a1, a2, a3, b0, b1);
+            for (int sc = 0; sc < V::SPC; ++sc) {
+                const int s = cg * V::SPC + sc;
+#pragma unroll
+                for (int k = 0; k < V::MTS; ++k) {
+                    uint32_t a0, a1, a2, a3;
+                    extract_pair<BITS, V::POS>(Rlo[s], k, a0, a1);
+                    extract_pair<BITS, V::POS>(Rhi[s], k, a2, a3);
+                    float (&acc)[4] = st.o[s * V::MTS + k];
+                    mma_f16(acc, a0, a1, a2, a3, b0h, b1h);
+                    if (!DUP) mma_f16(acc, a0, a1, a2, a3, b0l, b1l);
+                }
             }
         }
     }
 }
 
-template <int D, int G>
+// Raw bf16 values: m-tile m is channels 16m .. 16m+15 in natural order; ldmatrix.trans delivers the
+// four A registers of a (k-step, m-tile) directly.
+template <int D, int G, bool DUP>
 __device__ __forceinline__ void values_unit_bf16(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int unit,
-                                                 float (&pz)[Unit<D, G>::ZN]) {
+                                                 const float (&pz)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
     constexpr float kScale = 1.52587890625e-05f;      // 2^-16: same accumulator scale as the code path
-    uint32_t vrow = blk + (uint32_t)(kP * D * 2 + ((unit * UU::U + 2 * c.t) * D + C::NT * c.r) * 2);
-#pragma unroll 1
-    for (int ku = 0; ku < UU::KU; ++ku, vrow += 16 * D * 2) {
-        uint32_t a0, a1, a2, a3;
-        split_bf16x2(pz[0] * kScale, pz[1] * kScale, a0, a1);
-        split_bf16x2(pz[2] * kScale, pz[3] * kScale, a2, a3);
+    constexpr int RB = D * 2;
+    // matrices: (tokens of n-tile 2ku, channels 16m..), (same tokens, 16m+8..), (n-tile 2ku+1, 16m..), (n-tile 2ku+1, 16m+8..)
+    const uint32_t ldsm_lane = blk + (uint32_t)(kP * RB + (unit * UU::U + (c.lane & 7) + 8 * (c.lane >> 4)) * RB + 16 * ((c.lane >> 3) & 1));
 #pragma unroll
-        for (int j = 0; j + 4 < UU::ZN; ++j) pz[j] = pz[j + 4];
+    for (int ku = 0; ku < UU::KU; ++ku) {
+        uint32_t ph[2], pl[2];
+        split_bf16x2(pz[4 * ku + 0] * kScale, pz[4 * ku + 1] * kScale, ph[0], pl[0]);
+        split_bf16x2(pz[4 * ku + 2] * kScale, pz[4 * ku + 3] * kScale, ph[1], pl[1]);
+        const uint32_t b0 = DUP ? (c.part ? pl[0] : ph[0]) : ph[0];
+        const uint32_t b1 = DUP ? (c.part ? pl[1] : ph[1]) : ph[1];
 #pragma unroll
-        for (int cg = 0; cg < C::GV; ++cg) {
-            uint32_t x[4][C::NT / 2];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t src = vrow + (uint32_t)((((k & 2) ? 8 : 0) + (k & 1)) * D * 2 + G * cg * 2);
-#pragma unroll
-                for (int w = 0; w < C::NT / 2; ++w) x[k][w] = lds_u32(src + 4 * w);
-            }
-#pragma unroll
-            for (int i = 0; i < C::NT; ++i) {
-                const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-                const uint32_t b0 = prmt(x[0][i / 2], x[1][i / 2], sel);
-                const uint32_t b1 = prmt(x[2][i / 2], x[3][i / 2], sel);
-                mma_bf16(st.o[cg * C::NT + i], a0, a1, a2, a3, b0, b1);
-            }
+        for (int m = 0; m < C::MT; ++m) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4_trans(ldsm_lane + (uint32_t)(ku * 16 * RB + 32 * m), a0, a1, a2, a3);
+            mma_bf16(st.o[m], a0, a1, a2, a3, b0, b1);
+            if (!DUP) mma_bf16(st.o[m], a0, a1, a2, a3, pl[0], pl[1]);
         }
     }
 }
@@ -1006,229 +1144,250 @@ __device__ __forceinline__ void clear_invalid_tail(uint8_t* blk, int level, int 
     __syncwarp();
 }
 
-// One quantised block, units [u0, u1).
+// Channel of row r (odd = 0) or r+8 (odd = 1) of output m-tile mt, for each rung's value layout.
 template <int D, int G, int BITS>
-__device__ __forceinline__ void quant_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid, int u0, int u1) {
-    using C = Cfg<D, G>;
-    using UU = Unit<D, G>;
-    if (u1 <= u0 || nvalid <= u0 * UU::U) return;
-#pragma unroll 1
-    for (int unit = u0; unit < u1; ++unit) {
-        const int nrel = nvalid - unit * UU::U;
-        if (nrel <= 0) break;
-        float z[UU::ZN];
-#ifdef GKV_DBG_NOK
-        for (int i = 0; i < UU::ZN; ++i) z[i] = (float)(i + c.r);
-#else
-        scores_unit<D, G, BITS>(c, blk, unit, z);
-#endif
-        softmax_unit<D, G, true>(c, st, z, nrel);
-#ifndef GKV_DBG_NOV
-        values_unit<D, G, BITS>(c, st, blk, unit, z);
-#else
-        st.l += z[0];
-#endif
-    }
+__device__ __forceinline__ int out_channel(int mt, int r, int odd) {
+    if (BITS == 16) return 16 * mt + r + 8 * odd;
+    using V = VT<D, G, BITS == 16 ? 8 : BITS>;
+    return V::SP * (mt / V::MTS) + V::F * r + 2 * (mt % V::MTS) + odd;
 }
 
-template <int D, int G>
-__device__ __forceinline__ void bf16_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid, int u0, int u1) {
-    using UU = Unit<D, G>;
-#pragma unroll 1
-    for (int unit = u0; unit < u1; ++unit) {
-        const int nrel = nvalid - unit * UU::U;
-        if (nrel <= 0) break;
-        float z[UU::ZN];
-        scores_unit_bf16(c, blk, unit, z);
-        softmax_unit<D, G, false>(c, st, z, nrel);
-        values_unit_bf16(c, st, blk, unit, z);
-    }
-}
-
-// ---- a centroid block: one key and one value stand for nvalid tokens ------------------------------
-template <int D, int G>
-__device__ __forceinline__ void centroid_block(const Ctx<D, G>& c, WarpState<D, G>& st, uint32_t blk, int nvalid) {
+// This warp's record of an item (natural-log domain): m, l, o[D] per head.
+template <int D, int G, int BITS, bool DUP>
+__device__ __forceinline__ void write_record(const Params& p, const Ctx<D, G>& c, const WarpState<D, G>& st, float* rec0) {
     using C = Cfg<D, G>;
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < C::DT / 8; ++i) {
-        const uint4 k8 = lds_v4(blk + (uint32_t)(C::DT * c.t * 2 + 16 * i));
-        const uint4 qa = lds_v4(c.sq + (uint32_t)((c.r * D + C::DT * c.t + 8 * i) * 4));
-        const uint4 qb = lds_v4(c.sq + (uint32_t)((c.r * D + C::DT * c.t + 8 * i + 4) * 4));
-        const float2 k0 = __half22float2(u32_as_h2(k8.x)), k1 = __half22float2(u32_as_h2(k8.y));
-        const float2 k2 = __half22float2(u32_as_h2(k8.z)), k3 = __half22float2(u32_as_h2(k8.w));
-        s = fmaf(__uint_as_float(qa.x), k0.x, s); s = fmaf(__uint_as_float(qa.y), k0.y, s);
-        s = fmaf(__uint_as_float(qa.z), k1.x, s); s = fmaf(__uint_as_float(qa.w), k1.y, s);
-        s = fmaf(__uint_as_float(qb.x), k2.x, s); s = fmaf(__uint_as_float(qb.y), k2.y, s);
-        s = fmaf(__uint_as_float(qb.z), k3.x, s); s = fmaf(__uint_as_float(qb.w), k3.y, s);
+    float l = st.l;
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int myhead = head_of_row<DUP>(c.r);
+    if (c.t == 0 && myhead < p.rep && (!DUP || (c.r & 1) == 0)) {
+        float* rec = rec0 + (size_t)myhead * (D + 2);
+        rec[0] = st.m * 0.6931471805599453f;
+        rec[1] = l;
     }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    const float z = s * 1.4426950408889634f;
-    const float m = move_reference(st, z);
-    const float w = ex2(z - m) * (float)nvalid;
-    if (c.t == 0) st.l += w;
-    const float ws = w * 1.52587890625e-05f;
-    const uint32_t cv = blk + (uint32_t)(D * 2);
+    // p . vlo of channel group cg and column n sits in the lane of row cg, quad position n / 2, scaled 2^8
+    const float ob0 = DUP ? st.ob[0] + st.ob[1] : st.ob[0], ob1 = st.ob[1];
+    constexpr float kRow = 65536.f, kRow8 = 65536.f / v_rowscale(BITS);
 #pragma unroll
-    for (int cg = 0; cg < C::GV; ++cg) {
-        // this thread's output columns of group cg: channels NT*(2t) .. and NT*(2t+1) .., 2*NT contiguous halves
-        uint32_t h[C::NT];
-        const uint32_t src = cv + (uint32_t)((G * cg + C::NT * 2 * c.t) * 2);
-        if (C::NT == 2) {
-            const uint2 v = lds_v2(src);
-            h[0] = v.x; h[1 % C::NT] = v.y;
-        } else {
-#pragma unroll
-            for (int w = 0; w < C::NT / 4; ++w) {
-                const uint4 v = lds_v4(src + 16 * w);
-                h[(4 * w) % C::NT] = v.x; h[(4 * w + 1) % C::NT] = v.y; h[(4 * w + 2) % C::NT] = v.z; h[(4 * w + 3) % C::NT] = v.w;
+    for (int mt = 0; mt < C::MT; ++mt) {
+        const int ch0 = out_channel<D, G, BITS>(mt, c.r, 0), ch1 = out_channel<D, G, BITS>(mt, c.r, 1);
+        float bias00 = 0.f, bias01 = 0.f, bias10 = 0.f, bias11 = 0.f;      // [channel row][column]
+        if (BITS != 16) {
+            const int l0 = ((ch0 / G) % 8) * 4 + c.t, l1 = ((ch1 / G) % 8) * 4 + c.t;
+            bias00 = __shfl_sync(0xffffffffu, ob0, l0) * 0.00390625f;
+            bias10 = __shfl_sync(0xffffffffu, ob0, l1) * 0.00390625f;
+            if (!DUP) {
+                bias01 = __shfl_sync(0xffffffffu, ob1, l0) * 0.00390625f;
+                bias11 = __shfl_sync(0xffffffffu, ob1, l1) * 0.00390625f;
             }
         }
-        // h holds 2*NT halves: first NT for column 2t, next NT for column 2t+1
-#pragma unroll
-        for (int i = 0; i < C::NT; ++i) {
-            const uint32_t w0 = h[i / 2], w1 = h[(C::NT + i) / 2];
-            const float v0 = __half2float(__ushort_as_half((uint16_t)((i & 1) ? (w0 >> 16) : (w0 & 0xffffu))));
-            const float v1 = __half2float(__ushort_as_half((uint16_t)(((C::NT + i) & 1) ? (w1 >> 16) : (w1 & 0xffffu))));
-            st.o[cg * C::NT + i][0] = fmaf(ws, v0, st.o[cg * C::NT + i][0]);
-            st.o[cg * C::NT + i][1] = fmaf(ws, v1, st.o[cg * C::NT + i][1]);
+        if (DUP) {
+            if (c.t < p.rep) {
+                float* rec = rec0 + (size_t)c.t * (D + 2) + 2;
+                rec[ch0] = fmaf(st.o[mt][0] + st.o[mt][1], kRow, bias00);
+                rec[ch1] = fmaf(st.o[mt][2] + st.o[mt][3], kRow8, bias10);
+            }
+        } else {
+            if (2 * c.t < p.rep) {
+                float* rec = rec0 + (size_t)(2 * c.t) * (D + 2) + 2;
+                rec[ch0] = fmaf(st.o[mt][0], kRow, bias00);
+                rec[ch1] = fmaf(st.o[mt][2], kRow8, bias10);
+            }
+            if (2 * c.t + 1 < p.rep) {
+                float* rec = rec0 + (size_t)(2 * c.t + 1) * (D + 2) + 2;
+                rec[ch0] = fmaf(st.o[mt][1], kRow, bias01);
+                rec[ch1] = fmaf(st.o[mt][3], kRow8, bias11);
+            }
         }
     }
 }
 
+// An item of one of the byte-ring rungs: this warp's blocks of its stream, then its record.
+template <int D, int G, int BITS, bool DUP>
+__device__ __forceinline__ int ring_item(
+                                         const Params& p, Smem<D, G>& sm, const Ctx<D, G>& c, const ItemDesc& it,
+                                      int stream, int u0, int u1, int& seq, float* rec0) {
+    using C = Cfg<D, G>;
+    using UU = Unit<D, G>;
+    WarpState<D, G> st;
+#pragma unroll
+    for (int n = 0; n < C::MT; ++n) st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.f;
+    st.ob[0] = st.ob[1] = st.ob[2] = st.ob[3] = 0.f;
+    st.m = -INFINITY;
+    st.l = 0.f;
+    const uint32_t ring = smem_u32(sm.ring) + (uint32_t)stream * kRingBytes;
+    uint64_t* full = sm.full + stream * kNSlot;
+    uint64_t* empty = sm.empty + stream * kNSlot;
+    const Desc* desc = sm.desc + stream * kNSlot;
+    const int end = stream ? it.end_seq1 : it.end_seq0;
+    for (; seq < end; seq += kPairsPerStream) {
+        const int slot = seq % kNSlot;
+        if (!mbar_wait(&full[slot], (uint32_t)(seq / kNSlot) & 1u)) return 4;
+        const uint32_t off = desc[slot].off;
+        const int nvalid = desc[slot].nvalid;
+        const uint32_t blk = ring + off;
+        // both warps of the pair clear the tail (same zeros, so the overlap is harmless)
+        if (nvalid < kP) clear_invalid_tail<D, G>(sm.ring + (size_t)stream * kRingBytes + off, BITS, nvalid, c.lane);
+#pragma unroll 1
+        for (int unit = u0; unit < u1; ++unit) {
+            const int nrel = nvalid - unit * UU::U;
+            if (nrel <= 0) break;
+            float z[UU::ZN];
+            if (BITS == 16) scores_unit_bf16<D, G>(c, blk, unit, z);
+            else scores_unit<D, G, BITS == 16 ? 8 : BITS>(c, blk, unit, z);
+            softmax_unit<D, G, DUP>(c, st, z, nrel);
+            if (BITS == 16) values_unit_bf16<D, G, DUP>(c, st, blk, unit, z);
+            else values_unit<D, G, BITS == 16 ? 8 : BITS, DUP>(c, st, blk, unit, z);
+        }
+        __syncwarp();
+        if (c.lane == 0) mbar_arrive(&empty[slot]);
+    }
+    write_record<D, G, BITS, DUP>(p, c, st, rec0);
+    return 0;
+}
+
+// An item of centroid blocks (one key and one value vector stand for nvalid tokens; 512 bytes per
+// block at D = 128).  No ring: warp w takes blocks w, w + 12, ... of the item and reads each with one
+// 16-byte load per lane straight from global memory — all of its loads are in flight before the first
+// is used.  Lanes 0-15 own heads 0-3 and lanes 16-31 heads 4-7; lane l of a half owns channels
+// 8(l & 15) .. +7 of the key (for the scores, reduced over the half) and of the value.
 template <int D, int G>
+__device__ __forceinline__ void centroid_item(const Params& p, const Ctx<D, G>& c, const ItemDesc& it, const uint4* tab,
+                                              int warp, float* rec0) {
+    constexpr int kMaxMine = (kMaxItemBlocks + kConsumerWarps - 1) / kConsumerWarps;
+    constexpr int LPV = D / 8;                            // lanes that cover one vector with 16 bytes each
+    static_assert(LPV <= 16, "head dim too large for the centroid path");
+    const int lane = c.lane, hl = lane & 15, h0 = (lane >> 4) * 4;
+    // this warp's blocks are entries warp, warp + 12, ... of the item's table (shared memory)
+    const int nmine = it.nblk > warp ? (it.nblk - warp + kConsumerWarps - 1) / kConsumerWarps : 0;
+    uint4 kraw[kMaxMine], vraw[kMaxMine];
+    int nval[kMaxMine];
+#pragma unroll
+    for (int j = 0; j < kMaxMine; ++j) {
+        nval[j] = 0;
+        kraw[j] = vraw[j] = make_uint4(0, 0, 0, 0);
+        if (j < nmine) {
+            const uint4 e = tab[warp + kConsumerWarps * j];
+            nval[j] = (int)((e.z >> 8) & 0xffu);
+        }
+        if (j < nmine && hl < LPV) {
+            const uint4 e = tab[warp + kConsumerWarps * j];
+            const uint8_t* src = p.data + (((unsigned long long)e.y << 32) | e.x);
+            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                kraw[j] = __ldg(reinterpret_cast<const uint4*>(src) + hl);
+                vraw[j] = __ldg(reinterpret_cast<const uint4*>(src + 2 * D) + hl);
+            } else {                                      // a cache row at an odd address: byte loads
+                uint32_t w[8];
+                for (int i = 0; i < 8; ++i) {
+                    const uint8_t* s4 = src + (i < 4 ? 0 : 2 * D) + 16 * hl + 4 * (i & 3);
+                    w[i] = (uint32_t)s4[0] | ((uint32_t)s4[1] << 8) | ((uint32_t)s4[2] << 16) | ((uint32_t)s4[3] << 24);
+                }
+                kraw[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                vraw[j] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+        }
+    }
+    // this lane's slice of its four heads' queries (fp32 rows prepared by the query warp)
+    float q[4][8];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        const uint4 a = lds_v4(c.sq + (uint32_t)(((h0 + h) * D + 8 * (hl % LPV)) * 4));
+        const uint4 b = lds_v4(c.sq + (uint32_t)(((h0 + h) * D + 8 * (hl % LPV) + 4) * 4));
+        q[h][0] = __uint_as_float(a.x); q[h][1] = __uint_as_float(a.y); q[h][2] = __uint_as_float(a.z); q[h][3] = __uint_as_float(a.w);
+        q[h][4] = __uint_as_float(b.x); q[h][5] = __uint_as_float(b.y); q[h][6] = __uint_as_float(b.z); q[h][7] = __uint_as_float(b.w);
+    }
+    float m[4], l[4], o[4][8];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[h][i] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxMine; ++j) {
+        if (j >= nmine) break;                            // warp-uniform
+        const uint32_t kw[4] = {kraw[j].x, kraw[j].y, kraw[j].z, kraw[j].w};
+        const uint32_t vw[4] = {vraw[j].x, vraw[j].y, vraw[j].z, vraw[j].w};
+        float kf[8], vf[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(u32_as_h2(kw[i])), b = __half22float2(u32_as_h2(vw[i]));
+            kf[2 * i] = a.x; kf[2 * i + 1] = a.y; vf[2 * i] = b.x; vf[2 * i + 1] = b.y;
+        }
+        const float cnt = (float)nval[j];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = fmaf(q[h][i], kf[i], s);
+            if (hl >= LPV) s = 0.f;
+#pragma unroll
+            for (int o2 = 1; o2 < 16; o2 <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
+            if (s > m[h]) {                               // exact running maximum (natural-log domain)
+                const float corr = expf(m[h] - s);
+                l[h] *= corr;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[h][i] *= corr;
+                m[h] = s;
+            }
+            const float w = expf(s - m[h]) * cnt;
+            l[h] += w;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[h][i] = fmaf(w, vf[i], o[h][i]);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        if (h0 + h < p.rep && hl < LPV) {
+            float* rec = rec0 + (size_t)(h0 + h) * (D + 2);
+            if (hl == 0) { rec[0] = m[h]; rec[1] = l[h]; }
+            float2* d2 = reinterpret_cast<float2*>(rec + 2 + 8 * hl);      // records are 8-byte aligned
+            d2[0] = make_float2(o[h][0], o[h][1]); d2[1] = make_float2(o[h][2], o[h][3]);
+            d2[2] = make_float2(o[h][4], o[h][5]); d2[3] = make_float2(o[h][6], o[h][7]);
+        }
+    }
+}
+
+template <int D, int G, bool DUP>
 __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = lane >> 2, t = lane & 3;
-    WarpState<D, G> st;
     Ctx<D, G> c;
-    c.r = r; c.t = t; c.lane = lane; c.f = 0.f;
-    const uint32_t ring = smem_u32(sm.ring);
-    // A pair of warps takes every (kConsumerWarps/2)-th block of the stream; inside the block the
-    // two warps share out the units of G tokens (a block with a single unit goes to the first).
-    constexpr int kPairs = kConsumerWarps / 2;
+    c.r = lane >> 2; c.t = lane & 3; c.lane = lane; c.f = 0.f;
+    c.part = DUP && (c.r & 1);
+    // Pair pr of the CTA belongs to stream pr & 1 and takes every third block of it; inside the
+    // block the two warps share out the units of G tokens (a block with a single unit goes to the first).
     constexpr int UPB = kP / UU::U;                 // units per block
-    const int pair = warp >> 1, half = warp & 1;
+    const int pr = warp >> 1, half = warp & 1;
+    const int stream = pr & 1;
     const int u0 = UPB >= 2 ? half * (UPB / 2) : 0;
     const int u1 = UPB >= 2 ? u0 + UPB / 2 : (half == 0 ? 1 : 0);
-    int seq = pair;
+    int seq = pr >> 1;
     int code = 0;                                   // non-zero: a wait gave up
-#ifdef GKV_DBG_TIMING
-    long long c_all = clock64(), c_wait = 0, c_comp = 0, c_item = 0, c_n = 0, c_lat = 0, c_latn = 0;
-    const unsigned long long t_begin = global_ns();
-#endif
     for (int iseq = 0; code == 0; ++iseq) {
         const int is = iseq % kItemSlots, ib = iseq & 1;
-#ifdef GKV_DBG_TIMING
-        long long _ci0 = clock64();
-#endif
         if (!mbar_wait(&sm.item_full[is], (uint32_t)(iseq / kItemSlots) & 1u)) { code = 2; break; }
         const ItemDesc it = sm.item[is];
-        if (it.exit) {
-#ifdef GKV_DBG_TIMING
-            if (lane == 0) {
-                unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.counter) + 12;
-                const unsigned long long tnow = global_ns();
-                atomicMax(dbg + 8, ~tnow);                        // earliest warp exit (complemented)
-                atomicMax(dbg + 9, tnow);                         // latest warp exit
-                atomicAdd(dbg + 10, tnow - t_begin);              // sum of warp lifetimes (ns)
-                atomicMax(dbg + 11, ~t_begin);                    // earliest start (complemented)
-                atomicAdd(dbg + 0, (unsigned long long)(clock64() - c_all));
-                atomicAdd(dbg + 1, (unsigned long long)c_wait);
-                atomicAdd(dbg + 2, (unsigned long long)c_comp);
-                atomicAdd(dbg + 3, (unsigned long long)c_item);
-                atomicAdd(dbg + 4, (unsigned long long)c_n);
-                atomicAdd(dbg + 5, (unsigned long long)c_lat);
-                atomicAdd(dbg + 6, (unsigned long long)c_latn);
-            }
-#endif
-            return;
-        }
+        if (it.exit) return;
         if (!mbar_wait(&sm.qready[ib], (uint32_t)(iseq >> 1) & 1u)) { code = 3; break; }
         c.qprep = smem_u32(sm.qprep) + (uint32_t)(ib * C::QPREP_BYTES) + (uint32_t)lane * 16u;
         c.sq = smem_u32(sm.sq) + (uint32_t)(ib * C::SQ_BYTES);
-        c.f = sm.sf[ib * 16 + r];
-#pragma unroll
-        for (int n = 0; n < C::NTILE; ++n) st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.f;
-        st.ob[0] = st.ob[1] = st.ob[2] = st.ob[3] = 0.f;
-        st.m = -INFINITY;
-        st.l = 0.f;
-#ifdef GKV_DBG_TIMING
-        c_item += clock64() - _ci0;
-#endif
-
-        for (; seq < it.end_seq; seq += kPairs) {
-            const int slot = seq % kNSlot;
-#ifdef GKV_DBG_TIMING
-            long long _cw0 = clock64();
-#endif
-            if (!mbar_wait(&sm.full[slot], (uint32_t)(seq / kNSlot) & 1u)) { code = 4; break; }
-            const Desc d = sm.desc[slot];
-#ifdef GKV_DBG_TIMING
-            {
-                const long long now = clock64();
-                if (now - _cw0 > 400) { c_lat += now - _cw0; ++c_latn; }      // length of the waits that were real waits
-                c_wait += now - _cw0; _cw0 = now; ++c_n;
-            }
-#endif
-#ifdef GKV_DBG_NOCOMPUTE
-            if (false) {
-#else
-            if (d.level) {
-#endif
-                const uint32_t blk = ring + d.off;
-                if (d.level == 1) {
-                    if (half == 0) centroid_block(c, st, blk, d.nvalid);
-                } else {
-                    // both warps of the pair clear the tail (same zeros, so the overlap is harmless)
-                    if (d.nvalid < kP) clear_invalid_tail<D, G>(sm.ring + d.off, d.level, d.nvalid, lane);
-                    if (d.level == 16) bf16_block(c, st, blk, d.nvalid, u0, u1);
-                    else if (d.level == 8) quant_block<D, G, 8>(c, st, blk, d.nvalid, u0, u1);
-                    else if (d.level == 4) quant_block<D, G, 4>(c, st, blk, d.nvalid, u0, u1);
-                    else quant_block<D, G, 2>(c, st, blk, d.nvalid, u0, u1);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.empty[slot]);
-#ifdef GKV_DBG_TIMING
-            c_comp += clock64() - _cw0;
-#endif
-        }
-        if (code) break;
-#ifdef GKV_DBG_TIMING
-        _ci0 = clock64();
-#endif
-        // ---- this warp's record of the item (natural-log domain, like the generic kernel's) ----
-        float l = st.l;
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        c.f = sm.sf[ib * 16 + head_of_row<DUP>(c.r)];
         const size_t rec_idx = (size_t)it.row * p.items_per_row + (size_t)(it.item / p.rows);
-        float* rec = p.part + ((rec_idx * kConsumerWarps + warp) * p.rep + r) * (D + 2);
-        const bool live = r < p.rep;
-        if (live && t == 0) { rec[0] = st.m * 0.6931471805599453f; rec[1] = l; }
-        // p . vlo of channel group cg sits in lane 4r + cg/2, column cg & 1, scaled 2^8
-        const float ob_even = st.ob[0] + st.ob[2], ob_odd = st.ob[1] + st.ob[3];
-#pragma unroll
-        for (int cg = 0; cg < C::GV; ++cg) {
-            const float src = (cg & 1) ? ob_odd : ob_even;
-            const float bias = __shfl_sync(0xffffffffu, src, (lane & ~3) | (cg >> 1)) * 0.00390625f;
-            if (live) {
-#pragma unroll
-                for (int i = 0; i < C::NT; ++i) {
-                    const int n = cg * C::NT + i;
-                    rec[2 + G * cg + C::NT * (2 * t) + i] = fmaf(st.o[n][0] + st.o[n][2], 65536.f, bias);
-                    rec[2 + G * cg + C::NT * (2 * t + 1) + i] = fmaf(st.o[n][1] + st.o[n][3], 65536.f, bias);
-                }
-            }
-        }
+        float* rec0 = p.part + (rec_idx * kConsumerWarps + warp) * p.rep * (D + 2);
+        if (it.level == 1) centroid_item<D, G>(p, c, it, sm.item_tab + is * kMaxItemBlocks, warp, rec0);
+        else if (it.level == 16) code = ring_item<D, G, 16, DUP>(
+                p, sm, c, it, stream, u0, u1, seq, rec0);
+        else if (it.level == 8) code = ring_item<D, G, 8, DUP>(
+                p, sm, c, it, stream, u0, u1, seq, rec0);
+        else if (it.level == 4) code = ring_item<D, G, 4, DUP>(
+                p, sm, c, it, stream, u0, u1, seq, rec0);
+        else code = ring_item<D, G, 2, DUP>(
+                p, sm, c, it, stream, u0, u1, seq, rec0);
+        if (code) break;
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.item_empty[is]);
-#ifdef GKV_DBG_TIMING
-        c_item += clock64() - _ci0;
-#endif
         if (*reinterpret_cast<volatile int*>(abort_flag)) return;
     }
     if (code && lane == 0) {
@@ -1237,34 +1396,36 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     }
 }
 
-template <int D, int G>
+template <int D, int G, bool DUP>
 __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int abort_flag;
     Smem<D, G> sm(smem_raw);
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kNSlot; ++s) {
+        for (int s = 0; s < kStreams * kNSlot; ++s) {
             mbar_init(&sm.full[s], 1 + 32);         // lane 0's arrival (+ bulk-copy bytes) and 32 scale-copy arrivals
             mbar_init(&sm.empty[s], 2);             // the two warps of a pair
         }
         for (int s = 0; s < kItemSlots; ++s) {
             mbar_init(&sm.item_full[s], 1);
-            mbar_init(&sm.item_empty[s], kConsumerWarps);
+            mbar_init(&sm.item_empty[s], kConsumerWarps + kStreams);
         }
         mbar_init(&sm.qready[0], 1);
         mbar_init(&sm.qready[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-#ifdef GKV_REG_SHIFT
     if (threadIdx.x < kConsumers) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
     else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
-    if (threadIdx.x >= kConsumers + 64) return;
-#endif
-    if (threadIdx.x < kConsumers) consumer_loop<D, G>(p, sm, &abort_flag);
-    else if (threadIdx.x < kConsumers + 32) producer_loop<D, G>(p, sm, &abort_flag);
-    else query_loop<D, G>(p, sm, &abort_flag);
+    if (threadIdx.x < kConsumers) consumer_loop<D, G, DUP>(p, sm, &abort_flag);
+    // Warp w issues from scheduler w mod 4.  The consumers of stream 0 (pairs 0, 2, 4) sit on schedulers
+    // 0 and 1, those of stream 1 on 2 and 3; each producer is put on a scheduler of its OWN stream, so
+    // that it gets the issue slots exactly when its consumers are waiting for it.
+    else if (threadIdx.x < kConsumers + 32) producer_loop<D, G>(p, sm, 0, &abort_flag);        // warp 12: scheduler 0
+    else if (threadIdx.x < kConsumers + 64) query_loop<D, G, DUP>(p, sm, &abort_flag);         // warp 13: scheduler 1
+    else if (threadIdx.x < kConsumers + 96) producer_loop<D, G>(p, sm, 1, &abort_flag);        // warp 14: scheduler 2
+    else scheduler_loop<D, G>(p, sm, &abort_flag);                                             // warp 15: scheduler 3
 }
 
 }  // namespace mma

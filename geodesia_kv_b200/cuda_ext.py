@@ -16,10 +16,16 @@ Differences a caller can rely on:
   head, which still works (``Hkv == Hq``).
 * ``offs`` / ``level`` / ``valid`` may be ``(B, Hkv, nb)`` to give each cache row
   its own rungs; ``(nb,)`` is the reference's shared form.
+* Nothing is allocated per call in steady state: the scratch buffer is kept per
+  (device, stream), and the rung-sorted block lists the kernel walks are kept per
+  metadata triple and rebuilt only when ``offs`` / ``level`` / ``valid`` are other
+  tensors or have been written to since (torch's version counters).  Code that
+  writes those tensors through raw pointers calls ``invalidate_plans()``.
 """
 from __future__ import annotations
 
 import os
+from collections import OrderedDict
 from typing import Any, Optional
 
 import torch
@@ -41,8 +47,66 @@ def _stream(device) -> int:
 class _Extension:
     """Stand-in for the reference's pybind module."""
 
+    PLAN_CACHE_ENTRIES = 256
+
     def __init__(self) -> None:
         self.lib = _lib.load()
+        self._plans: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self._workspaces: dict = {}
+
+    # -- kernel choice (tensor-core kernel by shape, or always the CUDA-core kernel) ------
+    def set_decode_kernel(self, which: str) -> None:
+        _lib.check(self.lib.gkv_set_decode_kernel({"auto": 0, "generic": 1}[which]), "gkv_set_decode_kernel")
+
+    def set_decode_item_blocks(self, blocks: int) -> None:
+        """Blocks per work item of the tensor-core kernel (0 = chosen from the problem size)."""
+        _lib.check(self.lib.gkv_set_decode_item_blocks(int(blocks)), "gkv_set_decode_item_blocks")
+
+    def decode_status(self, device=None) -> int:
+        """Status word of the last decode on the current stream of ``device`` (0 = normal; non-zero
+        = a wait inside the kernel ran out and the output was filled with NaN).  Synchronises."""
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        ws = self._workspaces.get((dev.index, _stream(dev)))
+        if ws is None:
+            return 0
+        import ctypes
+        word = ctypes.c_int(0)
+        with torch.cuda.device(dev):
+            _lib.check(self.lib.gkv_decode_status(ws.data_ptr(), ctypes.byref(word), _stream(dev)), "gkv_decode_status")
+        return int(word.value)
+
+    # -- per-stream scratch and per-metadata block lists ------------------------------------
+    def _workspace(self, dev, need: int) -> torch.Tensor:
+        if torch.cuda.is_current_stream_capturing():
+            return torch.empty(need, dtype=torch.uint8, device=dev)        # lives in the graph's own pool
+        key = (dev.index, _stream(dev))
+        ws = self._workspaces.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+            self._workspaces[key] = ws
+        return ws
+
+    def invalidate_plans(self) -> None:
+        self._plans.clear()
+
+    def _plan(self, offs, level, valid, meta_rows: int, nb: int):
+        if nb == 0 or torch.cuda.is_current_stream_capturing():
+            return None                                                    # built inside the workspace by the call
+        key = (offs.data_ptr(), offs._version, level.data_ptr(), level._version, valid.data_ptr(), valid._version,
+               meta_rows, nb)
+        hit = self._plans.get(key)
+        if hit is not None:
+            self._plans.move_to_end(key)
+            return hit[0]
+        plan = torch.empty(self.lib.gkv_decode_plan_bytes(meta_rows, nb), dtype=torch.uint8, device=level.device)
+        rc = self.lib.gkv_decode_build_plan(offs.data_ptr(), level.data_ptr(), valid.data_ptr(), plan.data_ptr(),
+                                            meta_rows, nb, _stream(level.device))
+        _lib.check(rc, "gkv_decode_build_plan")
+        # the entry keeps the metadata tensors alive, so their addresses cannot be handed to other tensors
+        self._plans[key] = (plan, offs, level, valid)
+        while len(self._plans) > self.PLAN_CACHE_ENTRIES:
+            self._plans.popitem(last=False)
+        return plan
 
     # -- the reference entry point ------------------------------------------------
     def mixed_attn_decode(self, q, data, offs, klo, kstep, vlo, vstep, level, valid, block, group):
@@ -98,12 +162,13 @@ class _Extension:
         klo, kstep, vlo, vstep = (t.contiguous() for t in (klo, kstep, vlo, vstep))
         with torch.cuda.device(dev):
             need = self.lib.gkv_decode_workspace_bytes(B, Hq, Hkv, D, nb)
-            ws = torch.empty(need, dtype=torch.uint8, device=dev)
+            ws = self._workspace(dev, need)
+            plan = self._plan(offs, level, valid, meta_rows, nb)
             out = torch.empty((B, Hq, D + 2) if partial else (B, Hq, D), dtype=torch.float32, device=dev)
-            fn = self.lib.gkv_mixed_attn_decode_partial if partial else self.lib.gkv_mixed_attn_decode
-            rc = fn(q.data_ptr(), _ptr(data), _ptr(offs), _ptr(klo), _ptr(kstep), _ptr(vlo), _ptr(vstep),
-                    _ptr(level), _ptr(valid), out.data_ptr(), ws.data_ptr(), need, B, Hq, Hkv, D, nb,
-                    int(block), int(group), data.size(-1), meta_rows, _stream(dev))
+            rc = self.lib.gkv_mixed_attn_decode_planned(
+                q.data_ptr(), _ptr(data), _ptr(offs), _ptr(klo), _ptr(kstep), _ptr(vlo), _ptr(vstep),
+                _ptr(level), _ptr(valid), out.data_ptr(), _ptr(plan), 1 if partial else 0, ws.data_ptr(), ws.numel(),
+                B, Hq, Hkv, D, nb, int(block), int(group), data.size(-1), meta_rows, _stream(dev))
         _lib.check(rc, "gkv_mixed_attn_decode")
         return out, ws
 

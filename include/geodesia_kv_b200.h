@@ -3,10 +3,18 @@
  *
  * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its
  * comment says "host".  Every call is asynchronous on `stream` (a cudaStream_t
- * passed as void*), never synchronises, allocates no device memory (the caller
- * passes the workspace) and returns 0 or a negative GKV_E_* code; launch errors
- * are returned as GKV_E_CUDA and the CUDA error stays readable through
- * gkv_last_cuda_error().  The library has no global state besides that code.
+ * passed as void*), never synchronises (gkv_decode_status excepted), allocates
+ * no device memory (the caller passes the workspace) and returns 0 or a negative
+ * GKV_E_* code; launch errors are returned as GKV_E_CUDA and the CUDA error
+ * stays readable through gkv_last_cuda_error().
+ *
+ * Process-wide state, all of it small: the last CUDA error code; the kernel
+ * choice of gkv_set_decode_kernel; per-device caches filled on the first call on
+ * a device (multiprocessor count, "large shared memory opted in" flags, the
+ * device address of the built-in scratch of gkv_mixed_attn_decode_static); and
+ * that scratch array itself.  The caches are written without locks: every
+ * writer stores the same value, so concurrent first calls are harmless, but a
+ * host that wants no such race makes its first call per device from one thread.
  *
  * Each entry point names the interface of geodesia-ai/geodesia-kv it replaces.
  *
@@ -65,8 +73,34 @@ size_t gkv_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int nb);
 
 /* Number of kernels one decode call of this shape launches (host arithmetic only; for callers
  * that account for launches, e.g. a benchmark).  Assumes 16-byte aligned scale planes, which is
- * what selects the tensor-core kernel.  No counterpart in the reference.                       */
+ * what selects the tensor-core kernel.  `planned` != 0: the caller passes prebuilt block lists
+ * (gkv_mixed_attn_decode_planned), which saves one kernel.  No counterpart in the reference.   */
 int gkv_decode_kernel_launches(int B, int Hq, int Hkv, int D, int nb, int group);
+int gkv_decode_launch_count(int B, int Hq, int Hkv, int D, int nb, int group, int planned);
+
+/* Kernel choice for every later decode call of the process: 0 = by shape (tensor-core kernel
+ * for D in {64,128}, g in {16,32,64}, GQA width <= 8; the CUDA-core kernel otherwise), 1 = always
+ * the CUDA-core kernel (exact fp32 arithmetic; used to cross-check the two).  No counterpart in
+ * the reference, which has a single kernel.                                                    */
+int gkv_set_decode_kernel(int which);
+
+/* Blocks per work item of the tensor-core kernel for every later decode call of the process:
+ * 0 = chosen from the problem size (about six items per multiprocessor, between 6 and 64 blocks),
+ * 1..64 = fixed.  A tuning and test knob: results do not depend on it, only the split does (and with
+ * it gkv_decode_workspace_bytes: query the size after setting the knob).  No counterpart in the
+ * reference, whose split is fixed by its launcher (geodesia_kv_cuda/mixed_attn.cu:222-224).      */
+int gkv_set_decode_item_blocks(int blocks);
+
+/* What happens when a wait inside the tensor-core kernel runs out.  Every wait of that kernel (on
+ * a shared-memory barrier that a copy or another warp completes) gives up after about one second
+ * of wall time; the kernel then records a non-zero code in the workspace, all its warps leave,
+ * and the merge fills the WHOLE output with NaN — the call itself has long returned GKV_OK, being
+ * asynchronous.  gkv_decode_status reads that code back: it copies the status word of the most
+ * recent call that used `workspace` to *status_host (0 = completed normally) and SYNCHRONISES
+ * `stream` to do so.  A host that never sees NaN outputs need not call it.  The limit is wall
+ * time, so a context that is time-sliced or preempted for longer than the limit can trip it.
+ * The reference has no such path: its kernel has no waits.                                     */
+int gkv_decode_status(const void *workspace, int *status_host, void *stream);
 
 int gkv_mixed_attn_decode(const float *q, const uint8_t *data, const int64_t *offs,
                           const void *klo, const void *kstep, const void *vlo, const void *vstep,
@@ -74,6 +108,25 @@ int gkv_mixed_attn_decode(const float *q, const uint8_t *data, const int64_t *of
                           void *workspace, size_t workspace_bytes,
                           int B, int Hq, int Hkv, int D, int nb, int block, int group,
                           int64_t stride_bh, int meta_rows, void *stream);
+
+/* The tensor-core kernel walks every cache row's blocks sorted by rung.  Those lists depend only
+ * on offs / level / valid, so a caller whose metadata is unchanged since the last call can build
+ * them once (gkv_decode_build_plan into gkv_decode_plan_bytes(meta_rows, nb) bytes, 16-byte
+ * aligned) and pass them to gkv_mixed_attn_decode_planned, which then launches one kernel less.
+ * `plan` may be NULL (the lists are then rebuilt inside the workspace, exactly as
+ * gkv_mixed_attn_decode does); `partial` != 0 gives gkv_mixed_attn_decode_partial's output.
+ * A stale plan (metadata changed since it was built) gives wrong results, not an error.
+ * Extends mixed_attn_decode (geodesia_kv_cuda/mixed_attn.cu:202-244), which re-derives its split
+ * on every call.                                                                                */
+size_t gkv_decode_plan_bytes(int meta_rows, int nb);
+int gkv_decode_build_plan(const int64_t *offs, const int32_t *level, const int32_t *valid, void *plan,
+                          int meta_rows, int nb, void *stream);
+int gkv_mixed_attn_decode_planned(const float *q, const uint8_t *data, const int64_t *offs,
+                                  const void *klo, const void *kstep, const void *vlo, const void *vstep,
+                                  const int32_t *level, const int32_t *valid, float *out,
+                                  const void *plan, int partial, void *workspace, size_t workspace_bytes,
+                                  int B, int Hq, int Hkv, int D, int nb, int block, int group,
+                                  int64_t stride_bh, int meta_rows, void *stream);
 
 /* Same attention, but stops before the normalisation: writes, per (b, hq),
  * D+2 floats  [m, l, o[0..D)]  with o = sum_j exp(s_j - m) v_j  — the merged
@@ -113,6 +166,32 @@ int gkv_mixed_attn_decode_static(const float *q, const uint8_t *data, const int6
                                  int B, int Hq, int Hkv, int D, int nb, int block, int group,
                                  int64_t stride_bh, int meta_rows, void *stream);
 
+/* One long sequence split over the GPUs of a node, with the exchange of the per-rank (m, l, o)
+ * records done by this library's own merge kernel instead of a collective library: every rank
+ * calls this on its slice of the blocks (same q on every rank); the last merge level stores the
+ * rank's record of every output row into the INBOX of every rank with plain peer stores, raises
+ * the row's sequence number there, waits (bounded, about a second) for the records of all ranks in
+ * its own inbox and writes the normalised output — every rank ends up with the full result.
+ *
+ *   inboxes   HOST array of `world` device pointers: the inbox of every rank as addressable from
+ *             this GPU (peer mappings of one symmetric allocation of gkv_exchange_inbox_bytes()
+ *             bytes per rank, zero-filled once before the first call)
+ *   seq       (B*Hq) ints in LOCAL memory, zero-filled once; counts the calls
+ *   xstatus   1 int in local memory, zero-filled once; becomes non-zero when a wait ran out (the
+ *             output rows concerned are NaN) and stays so
+ * All ranks must make the same sequence of calls with the same inboxes.  A rank that stops calling
+ * makes the others' waits run out; it does not hang them.  `plan` as in
+ * gkv_mixed_attn_decode_planned (may be NULL).  The reference has no multi-GPU path; this extends
+ * its split-and-merge (geodesia_kv_cuda/mixed_attn.cu:58-65, 171-200) across GPUs.               */
+size_t gkv_exchange_inbox_bytes(int world, int rows, int D);
+int gkv_mixed_attn_decode_exchange(const float *q, const uint8_t *data, const int64_t *offs,
+                                   const void *klo, const void *kstep, const void *vlo, const void *vstep,
+                                   const int32_t *level, const int32_t *valid, float *out, const void *plan,
+                                   void *workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D,
+                                   int nb, int block, int group, int64_t stride_bh, int meta_rows,
+                                   void *const *inboxes, int rank, int world, int *seq, int *xstatus,
+                                   void *stream);
+
 /* LSE merge of `parts` records per output row (mixed_attn.cu:171-200):
  * partials (parts, rows, D+2) fp32 -> out (rows, D) fp32, rows = B*Hq.       */
 int gkv_combine_partials(const float *partials, float *out, int parts, int rows, int D, void *stream);
@@ -137,10 +216,12 @@ int gkv_pack_blocks(const void *k, const void *v, int src_dtype, uint8_t *data, 
 /* Demotion without a dense copy: block b of a row is read at rung level_old[b]
  * from offs_old[b], re-quantised from its CURRENT reconstruction to level_new[b]
  * (the batched demotion of geodesia_kv/policies.py:869-908) and written at
- * offs_new[b]; blocks with level_new == level_old are skipped.  Source and
- * destination may be the same bytes (a block is fully read before it is
- * written); distinct blocks must not overlap each other's destination.
- * data_new may equal data_old.                                                 */
+ * offs_new[b]; blocks with level_new == level_old are skipped.  A block's
+ * destination may overlap its OWN source (a block is fully read before it is
+ * written).  Blocks are processed concurrently, so when data_new aliases
+ * data_old a block's destination must not overlap any OTHER block's source or
+ * destination: demoting in place (offs_new == offs_old) is fine, compacting
+ * the row to the left in the same buffer is not — compact into a second buffer. */
 int gkv_demote_blocks(const uint8_t *data_old, const int64_t *offs_old, const int32_t *level_old,
                       uint8_t *data_new, const int64_t *offs_new, const int32_t *level_new,
                       void *klo, void *kstep, void *vlo, void *vstep, int rows, int nb, int D,

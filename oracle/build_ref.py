@@ -4,14 +4,15 @@ Sources are compiled where they lie in a checkout of geodesia-ai/geodesia-kv
 (``geodesia_kv_cuda/binding.cpp`` and ``geodesia_kv_cuda/mixed_attn.cu``); nothing is copied
 into this repository and the output goes to ``oracle/_ref/`` (git-ignored).  The result is a
 torch extension module ``geodesia_kv_ref_ext`` exposing the reference's ``mixed_attn_decode``;
-the GPU tests use it as a second oracle and the benchmark reports its time beside ours.
-Flags are the reference's own (geodesia_kv/cuda_ext.py:77) plus the sm_100a target.
+the GPU tests use it as a second oracle and the benchmark's CPU-baseline leg times it beside
+the CPU port.  Flags are the reference's own (geodesia_kv/cuda_ext.py:77) plus the sm_100a target.
 
-    python oracle/build_ref.py [--reference /path/to/checkout]
+    python oracle/build_ref.py [--reference /path/to/checkout]      (default: $GEODESIA_REFERENCE)
 """
 from __future__ import annotations
 
 import argparse
+import os
 import subprocess
 import sys
 import sysconfig
@@ -20,6 +21,16 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 NAME = "geodesia_kv_ref_ext"
+
+
+def reference_checkout() -> Path | None:
+    """Where the reference's sources are: $GEODESIA_REFERENCE, else a directory named ``reference``
+    beside this repository; None when neither holds the CUDA sources."""
+    cands = [os.environ.get("GEODESIA_REFERENCE"), HERE.parent.parent / "reference"]
+    for c in cands:
+        if c and (Path(c) / "geodesia_kv_cuda" / "mixed_attn.cu").exists():
+            return Path(c)
+    return None
 
 
 def build(reference: Path, force: bool = False) -> Path | None:
@@ -73,7 +84,10 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
-    print(build(Path(a.reference), a.force))
+    where = Path(a.reference) if a.reference else reference_checkout()
+    if where is None:
+        raise SystemExit("no checkout of the reference: pass --reference or set GEODESIA_REFERENCE")
+    print(build(where, a.force))

@@ -15,6 +15,7 @@ and, on a GPU, the CUDA kernels.
 from __future__ import annotations
 
 import argparse
+import os
 import importlib.util
 import sys
 from pathlib import Path
@@ -42,8 +43,12 @@ def query(seed: int, *shape):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("GEODESIA_REFERENCE"),
+                    help="checkout of geodesia-ai/geodesia-kv (default: $GEODESIA_REFERENCE)")
+    ap.add_argument("--only", default=None, help="write just this fixture (quant_grouped)")
     args = ap.parse_args()
+    if not args.reference:
+        raise SystemExit("pass --reference or set GEODESIA_REFERENCE to a checkout of the reference")
     ref = Path(args.reference)
     sys.path.insert(0, str(ref))
     import torch
@@ -57,6 +62,25 @@ def main() -> None:
     spec.loader.exec_module(rtest)
     quantize_codes = rtest.quantize_codes
     torch.set_num_threads(1)
+
+    def write_quant_grouped():
+        """policies.py:82-112: grouped min-max quantise -> dequantise with fp32 scales, both groupings."""
+        P, D = 64, 32
+        k, _ = dense_inputs(900, 2, P, D, outliers=2)
+        x = torch.from_numpy(k)
+        x[1, :32, 5] = 0.25                       # a constant group: the step clamps at 1e-8
+        blob = {}
+        for bits in (16, 8, 4, 2):
+            for group in (16, 32):
+                for pc in (True, False):
+                    rec, smax = rpol.quant_grouped(x.clone(), bits, group, pc)
+                    blob[f"rec_b{bits}_g{group}_pc{int(pc)}"] = rec.numpy()
+                    blob[f"smax_b{bits}_g{group}_pc{int(pc)}"] = smax.numpy()
+        np.savez_compressed(HERE / "quant_grouped.npz", seed=900, P=P, D=D, nb=2, outliers=2, x=x.numpy(), **blob)
+
+    if args.only == "quant_grouped":
+        write_quant_grouped()
+        return
 
     def build_row(k, v, levels, group):
         """tests/test_cuda_kernel.py:55-77 for one cache row, on CPU."""
@@ -297,6 +321,9 @@ def main() -> None:
         blob[f"out_{s}"] = out.numpy()
     blob["bits_per_value"] = np.float64(pol.report.bits_per_value)
     np.savez_compressed(HERE / "policy_decode.npz", seed=800, **blob)
+
+    # ---- J. quant_grouped (geodesia_kv/policies.py:82-112)
+    write_quant_grouped()
 
     for f in sorted(HERE.glob("*.npz")):
         print(f"{f.name:28s} {f.stat().st_size / 1024:8.1f} KiB")

@@ -11,23 +11,21 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-3          # max-abs bound on attention outputs stated for this path
 
 
-@pytest.fixture(params=["mma", "generic"], autouse=True)
-def kernel_choice(request, monkeypatch):
-    """Every test runs once per decode kernel: the tensor-core kernel (default dispatch) and the
-    exact-fp32 CUDA-core kernel that covers the shapes the former does not."""
-    if request.param == "generic":
-        monkeypatch.setenv("GKV_DECODE_KERNEL", "generic")
-    else:
-        monkeypatch.delenv("GKV_DECODE_KERNEL", raising=False)
-    return request.param
-
-
 @pytest.fixture(scope="module")
 def ext():
     from geodesia_kv_b200.cuda_ext import get_ext
     e = get_ext()
     assert e is not None, "CUDA extension must load on a GPU box"
     return e
+
+
+@pytest.fixture(params=["mma", "generic"], autouse=True)
+def kernel_choice(request, ext):
+    """Every test runs once per decode kernel: the tensor-core kernel (default dispatch) and the
+    exact-fp32 CUDA-core kernel that covers the shapes the former does not."""
+    ext.set_decode_kernel("generic" if request.param == "generic" else "auto")
+    yield request.param
+    ext.set_decode_kernel("auto")
 
 
 def run(ext, q, t, c):
@@ -175,10 +173,10 @@ def test_blocks_with_zero_valid_tokens_are_skipped(ext, oracle):
     assert np.abs(got - want).max() < 5e-5
 
 
-def test_long_rows_with_scattered_skips_and_every_item_size(ext, oracle, monkeypatch):
+def test_long_rows_with_scattered_skips_and_every_item_size(ext, oracle):
     """Rows longer than one plan-kernel pass per thread (nb > 1024), different rung vectors per row,
     blocks with no valid tokens sprinkled in, and several work-item sizes (records per row on both
-    sides of the one-level / two-level merge switch)."""
+    sides of the one-level / two-level merge switch; items smaller than the number of warp pairs)."""
     B, Hq, Hkv, nb, D, group = 1, 8, 2, 1100, 64, 32
     c = oracle_cache(oracle, 321, B, Hkv, nb, D, group, last_valid=13)
     rng = np.random.default_rng(5)
@@ -186,17 +184,139 @@ def test_long_rows_with_scattered_skips_and_every_item_size(ext, oracle, monkeyp
     c["valid"][0, 1, rng.permutation(nb - 1)[:7]] = 0
     q = rng.standard_normal((B, Hq, D), dtype=np.float32) * np.float32(D ** -0.5)
     want = oracle.mixed_attn_decode(q, *oracle_args(c))
-    for chunk in (None, "4", "9", "32"):
-        if chunk is None:
-            monkeypatch.delenv("GKV_DECODE_CHUNK", raising=False)
-        else:
-            monkeypatch.setenv("GKV_DECODE_CHUNK", chunk)
-        got = run(ext, q, to_torch(c, "cuda"), c)
-        assert np.abs(got - want).max() < 5e-5, chunk
-    monkeypatch.setenv("GKV_DECODE_CHUNK", "8")
-    monkeypatch.setenv("GKV_DECODE_TAIL", "40")
-    got = run(ext, q, to_torch(c, "cuda"), c)
-    assert np.abs(got - want).max() < 5e-5
+    try:
+        for blocks in (0, 1, 4, 9, 33, 64):
+            ext.set_decode_item_blocks(blocks)
+            got = run(ext, q, to_torch(c, "cuda"), c)
+            assert np.abs(got - want).max() < 5e-5, blocks
+    finally:
+        ext.set_decode_item_blocks(0)
+
+
+def test_million_token_row_shape(ext, oracle):
+    """The 1M-token configuration's shape: 28 query / 4 KV heads, D = 128, 16384 blocks per cache row,
+    cold rung mix (2/8/30/40/20 %), packed by the GPU packer.  One full cache row is checked against
+    the CPU oracle on the very same bytes (two-level merge, 32-bit item arithmetic, centroid items
+    read from global memory all at full length), and a 256-block slice of it against the reference's
+    own CUDA kernel when that has been built."""
+    from geodesia_kv_b200.pack_layout import pack_cache
+    Hq, Hkv, D, group, nb = 28, 4, 128, 32, 16384
+    gen = torch.Generator(device="cuda").manual_seed(3000)
+    k = torch.randn(1, Hkv, nb * 64, D, device="cuda", dtype=torch.bfloat16, generator=gen)
+    v = torch.randn(1, Hkv, nb * 64, D, device="cuda", dtype=torch.bfloat16, generator=gen)
+    k[..., ::37] *= 8.0
+    probs = torch.tensor([0.02, 0.08, 0.30, 0.40, 0.20], device="cuda")
+    ladder = torch.tensor([16, 8, 4, 2, 1], device="cuda", dtype=torch.int32)
+    level = ladder[torch.multinomial(probs, Hkv * nb, replacement=True, generator=gen)].view(1, Hkv, nb)
+    level[..., 0] = 16
+    level[..., -1] = 16
+    cache = pack_cache(k, v, level, group)
+    cache.valid[..., -1] = 37
+    del k, v
+    q = torch.randn(1, Hq, D, device="cuda", generator=gen) * D ** -0.5
+    got = ext.mixed_attn_decode(q, *cache.kernel_args())
+    torch.cuda.synchronize()
+    assert torch.isfinite(got).all()
+    rep = Hq // Hkv
+    u16 = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+    for h in (2,):                                           # one full cache row through the oracle
+        sl = slice(h, h + 1)
+        want = oracle.mixed_attn_decode(
+            q[:, h * rep:(h + 1) * rep].cpu().numpy(), cache.data[:, sl].cpu().numpy(), cache.offs[:, sl].cpu().numpy(),
+            u16(cache.klo[:, sl]), u16(cache.kstep[:, sl]), u16(cache.vlo[:, sl]), u16(cache.vstep[:, sl]),
+            cache.level[:, sl].cpu().numpy(), cache.valid[:, sl].cpu().numpy(), 64, group)
+        err = np.abs(got[:, h * rep:(h + 1) * rep].cpu().numpy() - want).max()
+        assert err < TOL and err < 5e-5, (h, err)
+    # a 256-block slice of row 0 against the reference's kernel (it needs the bytes once per query head
+    # and one metadata vector for all of them)
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "oracle"))
+    import build_ref
+    ref = build_ref.load()
+    if ref is not None and kernel_choice_is_mma(ext):
+        lo, hi = 5000, 5256
+        rows = lambda t: t[:, :1, lo:hi].expand(1, rep, -1, -1, -1).contiguous()
+        qh = q[:, :rep].contiguous()
+        offs = (cache.offs[0, 0, lo:hi] - cache.offs[0, 0, lo]).contiguous()
+        start, stop = int(cache.offs[0, 0, lo]), int(cache.offs[0, 0, hi])
+        data = cache.data[:, :1, start:stop].expand(1, rep, -1).contiguous()
+        args = (data, offs, rows(cache.klo), rows(cache.kstep), rows(cache.vlo), rows(cache.vstep),
+                cache.level[0, 0, lo:hi].contiguous(), cache.valid[0, 0, lo:hi].contiguous(), 64, group)
+        ours = ext.mixed_attn_decode(qh, *args)
+        theirs = ref.mixed_attn_decode(qh, *args)
+        assert (ours - theirs).abs().max().item() < 5e-5
+
+
+def kernel_choice_is_mma(ext):
+    return ext.lib.gkv_decode_launch_count(1, 4, 1, 128, 64, 32, 0) == 3
+
+
+def test_plan_cache_follows_metadata_edits(ext, oracle):
+    """The block lists are kept between calls; writing to level / valid through torch must rebuild them."""
+    c = oracle_cache(oracle, 17, 1, 2, 24, 128, 32)
+    t = to_torch(c, "cuda")
+    q = np.random.default_rng(8).standard_normal((1, 8, 128), dtype=np.float32) * np.float32(128 ** -0.5)
+    qd = torch.from_numpy(q).cuda()
+    first = ext.mixed_attn_decode(qd, *kernel_args(t, c)).cpu().numpy()
+    assert np.abs(first - oracle.mixed_attn_decode(q, *oracle_args(c))).max() < 5e-5
+    again = ext.mixed_attn_decode(qd, *kernel_args(t, c)).cpu().numpy()          # served from the kept lists
+    assert np.array_equal(first, again)
+    c["valid"][..., 3] = 0                                   # drop a block, shorten another: same tensors, new contents
+    c["valid"][..., 7] = 20
+    t["valid"][..., 3] = 0
+    t["valid"][..., 7] = 20
+    edited = ext.mixed_attn_decode(qd, *kernel_args(t, c)).cpu().numpy()
+    assert np.abs(edited - oracle.mixed_attn_decode(q, *oracle_args(c))).max() < 5e-5
+    assert ext.decode_status() == 0
+
+
+def test_a_wait_that_runs_out_is_reported_not_hung(oracle):
+    """A build of the same sources in which every wait gives up after 3 ms and the producer withholds
+    one block: the kernel must come back by itself, say so in its status word and poison the output;
+    the ordinary library keeps working in the same process afterwards."""
+    import ctypes
+    from geodesia_kv_b200 import _lib, build
+    so = build.WAIT_TEST_LIB
+    if not so.exists():
+        pytest.skip("the wait-test build of the library is not present")
+    lib = _lib.bind(so)
+    B, Hq, Hkv, nb, D, group = 1, 4, 1, 64, 128, 32
+    c = oracle_cache(oracle, 5, B, Hkv, nb, D, group, levels=[4] * nb)
+    t = to_torch(c, "cuda")
+    q = torch.randn(B, Hq, D, device="cuda") * D ** -0.5
+    out = torch.zeros(B, Hq, D, device="cuda")
+    need = lib.gkv_decode_workspace_bytes(B, Hq, Hkv, D, nb)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rc = lib.gkv_mixed_attn_decode(q.data_ptr(), t["data"].data_ptr(), t["offs"].data_ptr(), t["klo"].data_ptr(),
+                                   t["kstep"].data_ptr(), t["vlo"].data_ptr(), t["vstep"].data_ptr(),
+                                   t["level"].data_ptr(), t["valid"].data_ptr(), out.data_ptr(), ws.data_ptr(), need,
+                                   B, Hq, Hkv, D, nb, 64, group, t["data"].size(-1), B * Hkv, st)
+    assert rc == 0                                           # asynchronous: the launch itself succeeds
+    word = ctypes.c_int(0)
+    assert lib.gkv_decode_status(ws.data_ptr(), ctypes.byref(word), st) == 0
+    assert word.value != 0
+    assert torch.isnan(out).all()
+    from geodesia_kv_b200.cuda_ext import get_ext
+    good = get_ext().mixed_attn_decode(q, *kernel_args(t, c))
+    want = oracle.mixed_attn_decode(q.cpu().numpy(), *oracle_args(c))
+    assert np.abs(good.cpu().numpy() - want).max() < 5e-5
+    assert get_ext().decode_status() == 0
+
+
+def test_two_devices_in_one_process(oracle):
+    """Function attributes and the multiprocessor count belong to a device: decode on cuda:0, then on cuda:1."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from geodesia_kv_b200.cuda_ext import get_ext
+    c = oracle_cache(oracle, 23, 1, 2, 12, 128, 32)
+    q = np.random.default_rng(1).standard_normal((1, 8, 128), dtype=np.float32) * np.float32(128 ** -0.5)
+    want = oracle.mixed_attn_decode(q, *oracle_args(c))
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            got = get_ext().mixed_attn_decode(torch.from_numpy(q).to(dev), *kernel_args(to_torch(c, dev), c))
+            assert np.abs(got.cpu().numpy() - want).max() < 5e-5, dev
 
 
 def test_sequence_split_partials_recombine(ext, oracle):
@@ -266,6 +386,17 @@ def test_full_size_layer_properties(ext):
             cache.valid[..., lo:hi].contiguous(), 64, group))
     merged = ext.combine_partials(torch.stack(parts))
     assert (merged - whole).abs().max().item() < 1e-5
+    # a sample of the 256 cache rows against the CPU oracle on the very same bytes
+    u16 = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+    import gkv_oracle
+    rep = Hq // Hkv
+    for b, h in ((0, 0), (5, 3), (17, 6), (31, 7)):
+        bs, hs = slice(b, b + 1), slice(h, h + 1)
+        want = gkv_oracle.mixed_attn_decode(
+            q[bs, h * rep:(h + 1) * rep].cpu().numpy(), cache.data[bs, hs].cpu().numpy(), cache.offs[bs, hs].cpu().numpy(),
+            u16(cache.klo[bs, hs]), u16(cache.kstep[bs, hs]), u16(cache.vlo[bs, hs]), u16(cache.vstep[bs, hs]),
+            cache.level[bs, hs].cpu().numpy(), cache.valid[bs, hs].cpu().numpy(), 64, group)
+        assert np.abs(whole[bs, h * rep:(h + 1) * rep].cpu().numpy() - want).max() < 5e-5, (b, h)
     # softmax weights sum to one: with every value equal to 1 the output is 1.  Build that cache
     # from constant V at rung 16 and the same K.
     ones = torch.ones(1, 1, 1024, D, device="cuda")

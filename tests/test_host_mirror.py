@@ -85,3 +85,19 @@ def test_blockify_pads_with_the_last_row():
     blocks, pad = policies.blockify(x, 64)
     assert blocks.shape == (2, 64, 3) and pad == 58
     assert blocks[1, 6:].eq(x[-1]).all()
+
+
+def test_quant_grouped_matches_reference(golden):
+    """policies.py:82-112 on a reference-made fixture: every bit width, group size and both groupings."""
+    import torch
+    from geodesia_kv_b200.policies import quant_grouped
+    g = golden("quant_grouped")
+    x = torch.from_numpy(g["x"])
+    for bits in (16, 8, 4, 2):
+        for group in (16, 32):
+            for pc in (True, False):
+                rec, smax = quant_grouped(x.clone(), bits, group, pc)
+                key = f"b{bits}_g{group}_pc{int(pc)}"
+                assert rec.shape == x.shape
+                assert np.array_equal(rec.numpy(), g["rec_" + key]), key
+                assert np.array_equal(smax.numpy(), g["smax_" + key]), key
