@@ -1,5 +1,7 @@
 // Decode attention over the packed cache: planning, the LSE combine and the C ABI.
 
+#include <string.h>
+
 #include "decode_generic.cuh"
 #include "decode_mma.cuh"
 
@@ -386,19 +388,73 @@ static int opt_in_smem(Kernel kernel, unsigned char (&done)[kMaxDevices], size_t
     return GKV_OK;
 }
 
+// ---- tensor maps of the cache bytes (tiled, swizzled bulk copies) -------------------------------------
+// The encoder lives in the driver; it is looked up once through the runtime, so the library links
+// nothing but the runtime.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<TensorMapEncodeFn>(ptr);
+        else
+            cudaGetLastError();
+        tried = true;
+    }
+    return fn;
+}
+
+// The cache as a matrix of w-byte rows, a block as a box of `rows` of them.
+static bool encode_rows(CUtensorMap* map, const uint8_t* data, size_t total_bytes, int w, int rows) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc || w < 32 || rows > 256 || total_bytes / (size_t)w == 0) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)w, (cuuint64_t)(total_bytes / (size_t)w)};
+    const cuuint64_t strides[1] = {(cuuint64_t)w};
+    const cuuint32_t box[2] = {(cuuint32_t)w, (cuuint32_t)rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapSwizzle sw = w == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : w == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                                                   : CU_TENSOR_MAP_SWIZZLE_32B;
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(data), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, int G>
+static void make_tensor_maps(mma::TensorMaps& tm, const uint8_t* data, size_t total_bytes) {
+    memset(&tm, 0, sizeof(tm));
+    if (reinterpret_cast<uintptr_t>(data) & 15) return;             // the copy engine wants a 16-byte aligned base
+    bool ok = true;
+    // rows per block = both halves of the block (2 x 64 token rows) in tile rows of w bytes
+    { using L = mma::Lay<D, G, 16>; ok = ok && encode_rows(&tm.m[0], data, total_bytes, L::W, 2 * kP * L::RB / L::W); }
+    { using L = mma::Lay<D, G, 8>;  ok = ok && encode_rows(&tm.m[1], data, total_bytes, L::W, 2 * kP * L::RB / L::W); }
+    if (mma::Lay<D, G, 4>::TILED) {
+        using L = mma::Lay<D, G, 4>;
+        ok = ok && encode_rows(&tm.m[2], data, total_bytes, L::W, 2 * kP * L::RB / L::W);
+    }
+    tm.usable = ok ? 1 : 0;
+}
+
 template <int D, int G, bool DUP>
-static int launch_mma2(const mma::Params& p, int grid, cudaStream_t stream) {
+static int launch_mma2(const mma::Params& p, const mma::TensorMaps& tm, int grid, cudaStream_t stream) {
     static unsigned char done[kMaxDevices] = {0};
     if (const int rc = opt_in_smem(mma::decode_mma_kernel<D, G, DUP>, done, mma::Cfg<D, G>::SMEM)) return rc;
-    mma::decode_mma_kernel<D, G, DUP><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p);
+    mma::decode_mma_kernel<D, G, DUP><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p, tm);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }
 
 // up to four query heads per cache row: the (hi, lo) halves of a head share one MMA
 template <int D, int G>
-static int launch_mma(const mma::Params& p, int grid, cudaStream_t stream) {
-    return p.rep <= 4 ? launch_mma2<D, G, true>(p, grid, stream) : launch_mma2<D, G, false>(p, grid, stream);
+static int launch_mma(const mma::Params& p, size_t total_bytes, int grid, cudaStream_t stream) {
+    mma::TensorMaps tm;
+    make_tensor_maps<D, G>(tm, p.data, total_bytes);
+    return p.rep <= 4 ? launch_mma2<D, G, true>(p, tm, grid, stream) : launch_mma2<D, G, false>(p, tm, grid, stream);
 }
 
 static int launch_plan(const int32_t* level, const int32_t* valid, const int64_t* offs, uint4* plan, int meta_rows,
@@ -459,15 +515,16 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
         mp.stride_bh = stride_bh;
         int rc;
-        if (D == 128 && group == 32) rc = launch_mma<128, 32>(mp, pl.grid, stream);
+        const size_t total = (size_t)rows * (size_t)stride_bh;         // bytes of the cache: all rows
+        if (D == 128 && group == 32) rc = launch_mma<128, 32>(mp, total, pl.grid, stream);
 #ifdef GKV_FAST_BUILD      // development builds: only the main shape is instantiated
         else rc = GKV_E_SHAPE;
 #else
-        else if (D == 128 && group == 16) rc = launch_mma<128, 16>(mp, pl.grid, stream);
-        else if (D == 128 && group == 64) rc = launch_mma<128, 64>(mp, pl.grid, stream);
-        else if (D == 64 && group == 32) rc = launch_mma<64, 32>(mp, pl.grid, stream);
-        else if (D == 64 && group == 16) rc = launch_mma<64, 16>(mp, pl.grid, stream);
-        else rc = launch_mma<64, 64>(mp, pl.grid, stream);
+        else if (D == 128 && group == 16) rc = launch_mma<128, 16>(mp, total, pl.grid, stream);
+        else if (D == 128 && group == 64) rc = launch_mma<128, 64>(mp, total, pl.grid, stream);
+        else if (D == 64 && group == 32) rc = launch_mma<64, 32>(mp, total, pl.grid, stream);
+        else if (D == 64 && group == 16) rc = launch_mma<64, 16>(mp, total, pl.grid, stream);
+        else rc = launch_mma<64, 64>(mp, total, pl.grid, stream);
 #endif
         if (rc) return rc;
     } else {

@@ -52,10 +52,25 @@
 // accumulators.
 #pragma once
 
+#include <cuda.h>          // CUtensorMap (the type only; the encoder is looked up at run time)
+
 #include "gkv_common.cuh"
 
 namespace gkv {
 namespace mma {
+
+// Tensor maps of the cache bytes, one per rung whose blocks are fetched with a TILED bulk copy: the
+// cache is described as a 2-D byte matrix of `w`-byte rows (w = bytes of a token row, at most 128),
+// a block is a box of consecutive rows, and the copy engine writes the box into shared memory with
+// the 16-byte chunks of every row XOR-permuted by the row number (the hardware swizzle).  Eight
+// consecutive token rows then sit in eight different bank groups, which is what makes the
+// ldmatrix.trans fetches of the value codes (eight rows per matrix) conflict-free: measured on the
+// plain row-major layout, those fetches alone cost 4 to 8 shared-memory wavefronts per matrix.
+struct alignas(64) TensorMaps {
+    CUtensorMap m[3];   // 0: raw bf16 rows, 1: 8-bit codes, 2: 4-bit codes
+    int usable;         // 0: no tiled copies (base pointer not 16-byte aligned, or no encoder): blocks are copied by hand
+    int pad[15];
+};
 
 constexpr int kConsumerWarps = 12;       // three warpgroups
 constexpr int kStreams = 2;              // byte rings / producer warps per CTA
@@ -197,6 +212,36 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
+// Layout of a rung's block in the ring.  Rungs fetched by a tiled copy are SWIZZLED: byte `off` of the
+// block (whose ring address is 1024-byte aligned) lives at off ^ (((off >> 7) & (W/16 - 1)) << 4), W = bytes
+// of a tile row (32, 64 or 128) — the 16-byte chunks of a row are permuted by the row's position in
+// its group of 128 / W... rows.  W = 0: plain row-major (2-bit codes, and 4-bit codes with 16-channel groups).
+template <int D, int G, int BITS>
+struct Lay {
+    static constexpr int RB = D * BITS / 8;                               // bytes of a token row
+    static constexpr bool TILED = BITS == 16 || BITS == 8 || (BITS == 4 && G >= 32);
+    static constexpr int W = !TILED ? 0 : RB < 128 ? RB : 128;
+    static constexpr uint32_t XMASK = W == 128 ? 7u : W == 64 ? 3u : W == 32 ? 1u : 0u;
+    static_assert(!TILED || W >= 32, "tile rows of at least 32 bytes");
+};
+template <int W>
+__device__ __forceinline__ uint32_t swz(uint32_t off) {
+    constexpr uint32_t M = W == 128 ? 7u : W == 64 ? 3u : W == 32 ? 1u : 0u;
+    return off ^ (((off >> 7) & M) << 4);
+}
+// XOR term (already shifted to bits 4-6) of a row whose number is r modulo 8, for bytes b of the row
+// that do not cross a 128-byte boundary relative to b0.
+template <int D, int G, int BITS>
+__device__ __forceinline__ uint32_t swz_term(int r, int b0) {
+    using L = Lay<D, G, BITS>;
+    return ((((uint32_t)r * L::RB + (uint32_t)b0) >> 7) & L::XMASK) << 4;
+}
+
+__device__ __forceinline__ void tma_tile_g2s(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float r;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -276,7 +321,7 @@ struct Cfg {
     static constexpr int QPLANE = CH * 32 * 8;
     static constexpr int QPREP_BYTES = 2 * QPLANE * 2;
     static constexpr int SQ_BYTES = 8 * D * 4;
-    static constexpr size_t SMEM = kStreams * (size_t)kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
+    static constexpr size_t SMEM = 1024 + kStreams * (size_t)kRingBytes + 2 * (QPREP_BYTES + SQ_BYTES + 64) +
                                    kStreams * kNSlot * (sizeof(Desc) + 16) + kItemSlots * sizeof(ItemDesc) +
                                    (2 * kItemSlots + 2) * 8 + kItemSlots * kMaxItemBlocks * 16 + 128;
     static_assert(D % 32 == 0 && (G == 16 || G == 32 || G == 64) && D % G == 0, "unsupported shape");
@@ -297,7 +342,9 @@ struct Smem {
     uint64_t* item_empty;  // [kItemSlots] one arrival per consumer warp and per producer that is done with the item
     uint64_t* qready;      // [2] query warp -> consumers
     uint4* item_tab;       // [kItemSlots][kMaxItemBlocks] block entries of the announced items (row base offset added)
-    __device__ explicit Smem(uint8_t* base) {
+    __device__ explicit Smem(uint8_t* raw) {
+        // the swizzle of the tiled copies is a function of the shared-memory address: rings start on a 1024-byte boundary
+        uint8_t* base = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
         ring = base;
         uint8_t* p = base + kStreams * (size_t)kRingBytes;
         qprep = reinterpret_cast<__half*>(p);               p += 2 * C::QPREP_BYTES;
@@ -436,7 +483,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // iteration is bound by the latency of its own chain of ~60 dependent instructions (~1300 cycles per
 // block measured); batches overlap those chains, and a producer that has fallen behind catches up.
 template <int D, int G>
-__device__ __forceinline__ bool produce_item(const Params& p, Smem<D, G>& sm, ProducerState& ps, int s,
+__device__ __forceinline__ bool produce_item(const Params& p, const TensorMaps& tm, Smem<D, G>& sm, ProducerState& ps, int s,
                                              const ItemDesc& it, int islot) {
     using C = Cfg<D, G>;
     const int lane = threadIdx.x & 31;
@@ -450,7 +497,10 @@ __device__ __forceinline__ bool produce_item(const Params& p, Smem<D, G>& sm, Pr
     constexpr int K = C::KSCALE;                         // == VSCALE: every scale plane has the same bytes per block
     static_assert(C::KSCALE == C::VSCALE && (4 * K) % 512 == 0, "scale planes");
     constexpr int NR = 4 * K / 512;                      // rounds of 32 lanes x 16 bytes that cover the four planes
-    const uint32_t need = (dbytes + (quant ? 4u * K : 0u) + 127u) & ~127u;
+    const uint32_t need = (dbytes + (quant ? 4u * K : 0u) + 1023u) & ~1023u;
+    // tiled copies: the tile row width of the item's rung (0: plain bulk copy) and its tensor map
+    const int tw = lv == 16 ? Lay<D, G, 16>::W : lv == 8 ? Lay<D, G, 8>::W : lv == 4 ? Lay<D, G, 4>::W : 0;
+    const CUtensorMap* tmap = &tm.m[lv == 16 ? 0 : lv == 8 ? 1 : 2];
     // This lane's 16 bytes of every round: which plane, and where inside a block's K bytes — fixed for the item.
     const uint8_t* splane[NR];
 #pragma unroll
@@ -512,16 +562,24 @@ __device__ __forceinline__ bool produce_item(const Params& p, Smem<D, G>& sm, Pr
             Desc d;
             d.off = my_dst; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)my_pad; d.unused = 0;
             desc[my_slot] = d;
-            const uint8_t* src = p.data + (((unsigned long long)cur.y << 32) | cur.x);
+            const unsigned long long soff = ((unsigned long long)cur.y << 32) | cur.x;      // byte offset in the cache
+            const uint8_t* src = p.data + soff;
             if (withhold) {
-            } else if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            } else if (tw && tm.usable && (soff & (unsigned long long)(tw - 1)) == 0) {
+                // a box of tile rows, written swizzled (row = byte offset / row width)
+                mbar_arrive_tx(&full[my_slot], dbytes);
+                tma_tile_g2s(ring + my_dst, tmap, 0, (int)(soff / (unsigned)tw), &full[my_slot]);
+            } else if (!tw && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
                 mbar_arrive_tx(&full[my_slot], dbytes);
                 bulk_g2s(ring + my_dst, src, dbytes, &full[my_slot]);
             } else {
-                // block start not 16-byte aligned (a cache row at an odd address): no bulk copy,
-                // this lane copies the bytes by hand
+                // block start not aligned for a bulk copy (a cache row at an odd address): this lane
+                // copies the bytes by hand, into the layout the rung's consumers expect
                 uint8_t* d0 = sm.ring + (size_t)s * kRingBytes + my_dst;
-                for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
+                if (tw == 128) for (uint32_t i = 0; i < dbytes; ++i) d0[swz<128>(i)] = src[i];
+                else if (tw == 64) for (uint32_t i = 0; i < dbytes; ++i) d0[swz<64>(i)] = src[i];
+                else if (tw == 32) for (uint32_t i = 0; i < dbytes; ++i) d0[swz<32>(i)] = src[i];
+                else for (uint32_t i = 0; i < dbytes; ++i) d0[i] = src[i];
                 __threadfence_block();
                 mbar_arrive(&full[my_slot]);
             }
@@ -621,7 +679,7 @@ __device__ void scheduler_loop(const Params& p, Smem<D, G>& sm, int* abort_flag)
 
 // Producer of stream s: for every announced item, streams the item's blocks of its stream into its ring.
 template <int D, int G>
-__device__ void producer_loop(const Params& p, Smem<D, G>& sm, int s, int* abort_flag) {
+__device__ void producer_loop(const Params& p, const TensorMaps& tm, Smem<D, G>& sm, int s, int* abort_flag) {
     const int lane = threadIdx.x & 31;
     ProducerState ps;
     bool ok = true;
@@ -630,7 +688,7 @@ __device__ void producer_loop(const Params& p, Smem<D, G>& sm, int s, int* abort
         if (!mbar_wait(&sm.item_full[sl], (uint32_t)(j / kItemSlots) & 1u)) { ok = false; break; }
         const ItemDesc it = sm.item[sl];
         if (it.exit) return;
-        ok = produce_item<D, G>(p, sm, ps, s, it, sl);
+        ok = produce_item<D, G>(p, tm, sm, ps, s, it, sl);
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.item_empty[sl]);      // this warp no longer needs the item's descriptor and table
         if (*reinterpret_cast<volatile int*>(abort_flag)) return;
@@ -765,7 +823,11 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     constexpr int CG = LB / CB;                          // chunks per fetch
     constexpr int LW = LB / 4;
     static_assert(LB >= 4 && C::CH % CG == 0, "unsupported shape");
-    const uint32_t row0 = blk + (uint32_t)((tg * UU::U + c.r) * RB + c.t * TB);
+    // every fetch stays inside one 16-byte chunk, so in a swizzled block only the chunk moves (rows 8n + r of
+    // all n-tiles have the same XOR term)
+    static_assert(LB <= 16, "a fetch must not cross a 16-byte chunk");
+    const uint32_t kx = swz_term<D, G, BITS>(c.r, 0);
+    const uint32_t rowbase = blk + (uint32_t)((tg * UU::U + c.r) * RB);
 
     float acc[UU::NU][4];
 #pragma unroll
@@ -779,7 +841,7 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
         uint32_t W[UU::NU][LW];
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) {
-            const uint32_t src = row0 + (uint32_t)(g * LB + n * 8 * RB);
+            const uint32_t src = rowbase + (((uint32_t)(c.t * TB + g * LB)) ^ kx) + (uint32_t)(n * 8 * RB);
             if (LW == 4) { const uint4 v = lds_v4(src); W[n][0] = v.x; W[n][1 % LW] = v.y; W[n][2 % LW] = v.z; W[n][3 % LW] = v.w; }
             else if (LW == 2) { const uint2 v = lds_v2(src); W[n][0] = v.x; W[n][1 % LW] = v.y; }
             else W[n][0] = lds_u32(src);
@@ -858,7 +920,10 @@ template <int D, int G>
 __device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t blk, int tg, float (&z)[Unit<D, G>::ZN]) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
-    const uint32_t row0 = blk + (uint32_t)(((tg * UU::U + c.r) * D + C::DT * c.t) * 2);
+    // swizzled block: this thread's 16-byte chunks of a row all share the row's XOR term
+    const uint32_t bt = (uint32_t)(C::DT * c.t * 2);
+    const uint32_t kx = swz_term<D, G, 16>(c.r, (int)bt);
+    const uint32_t rowbase = blk + (uint32_t)((tg * UU::U + c.r) * D * 2);
     float acc[UU::NU][4];
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
@@ -866,8 +931,9 @@ __device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t bl
     for (int i = 0; i < C::CH; ++i) {
         const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
         uint4 w[UU::NU];
+        const uint32_t coff = (bt + 16u * (uint32_t)i) ^ kx;
 #pragma unroll
-        for (int n = 0; n < UU::NU; ++n) w[n] = lds_v4(row0 + 16 * i + n * 8 * D * 2);
+        for (int n = 0; n < UU::NU; ++n) w[n] = lds_v4(rowbase + coff + n * 8 * D * 2);
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w[n].x, w[n].y);
 #pragma unroll
@@ -1020,8 +1086,12 @@ __device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>&
     const uint32_t vbase = blk + (uint32_t)(kP * RB);
     const uint32_t sbase = blk + (uint32_t)(2 * (kP * RB) + 2 * C::KSCALE);       // vlo plane; vstep follows
     const int tok0 = unit * UU::U + 2 * c.t;            // lower token of this thread's first pair
-    // ldmatrix row of this lane: token (lane & 7) of the first or second half of a k-step, chunk +0 / +1
-    const uint32_t ldsm_lane = vbase + (uint32_t)((unit * UU::U + (c.lane & 7) + 8 * ((c.lane >> 3) & 1)) * RB + 16 * (c.lane >> 4));
+    // ldmatrix row of this lane: token (lane & 7) of the first or second half of a k-step, chunk +0 / +1; in a
+    // swizzled block the chunk index is XORed with the row's term (the same for every row this lane addresses)
+    const uint32_t vx = swz_term<D, G, BITS>(c.lane & 7, 0);
+    const uint32_t ldsm_lane = vbase + (uint32_t)((unit * UU::U + (c.lane & 7) + 8 * ((c.lane >> 3) & 1)) * RB) +
+                               ((uint32_t)(16 * (c.lane >> 4)) ^ (vx & 16u));
+    const uint32_t vxe = vx & ~16u;
     // plain-load path: this thread's fields of (token tok0, span 0)
     const uint32_t lds_lane = vbase + (uint32_t)(tok0 * RB + (c.r * V::LOAD_BITS) / 8);
     const int sub = (V::LOAD_BITS % 8) ? ((c.r * V::LOAD_BITS) & 7) : 0;
@@ -1056,7 +1126,7 @@ __device__ __forceinline__ void values_unit(const Ctx<D, G>& c, WarpState<D, G>&
         if (V::LDSM) {
 #pragma unroll
             for (int s2 = 0; s2 < V::NSPAN / 2; ++s2)
-                ldsm_x4_trans(ldsm_lane + (uint32_t)(ku * 16 * RB + 32 * s2), Rlo[2 * s2], Rhi[2 * s2],
+                ldsm_x4_trans(ldsm_lane + (uint32_t)(ku * 16 * RB) + ((uint32_t)(32 * s2) ^ vxe), Rlo[2 * s2], Rhi[2 * s2],
                               Rlo[(2 * s2 + 1) % V::NSPAN], Rhi[(2 * s2 + 1) % V::NSPAN]);
         } else {
 #pragma unroll
@@ -1109,7 +1179,10 @@ __device__ __forceinline__ void values_unit_bf16(const Ctx<D, G>& c, WarpState<D
     constexpr float kScale = 1.52587890625e-05f;      // 2^-16: same accumulator scale as the code path
     constexpr int RB = D * 2;
     // matrices: (tokens of n-tile 2ku, channels 16m..), (same tokens, 16m+8..), (n-tile 2ku+1, 16m..), (n-tile 2ku+1, 16m+8..)
-    const uint32_t ldsm_lane = blk + (uint32_t)(kP * RB + (unit * UU::U + (c.lane & 7) + 8 * (c.lane >> 4)) * RB + 16 * ((c.lane >> 3) & 1));
+    // swizzled: chunk (2m + b) of a row, b = (lane >> 3) & 1, is XORed with the term of its 128-byte tile row
+    const uint32_t rowb = blk + (uint32_t)(kP * RB + (unit * UU::U + (c.lane & 7) + 8 * (c.lane >> 4)) * RB);
+    const uint32_t cb = 16u * ((c.lane >> 3) & 1);
+    const uint32_t vx0 = swz_term<D, G, 16>(c.lane & 7, 0), vx1 = swz_term<D, G, 16>(c.lane & 7, 128);   // first / second 128 bytes of the row
 #pragma unroll
     for (int ku = 0; ku < UU::KU; ++ku) {
         uint32_t ph[2], pl[2];
@@ -1120,7 +1193,9 @@ __device__ __forceinline__ void values_unit_bf16(const Ctx<D, G>& c, WarpState<D
 #pragma unroll
         for (int m = 0; m < C::MT; ++m) {
             uint32_t a0, a1, a2, a3;
-            ldsm_x4_trans(ldsm_lane + (uint32_t)(ku * 16 * RB + 32 * m), a0, a1, a2, a3);
+            const uint32_t off = (uint32_t)(32 * m) + cb;                 // byte of the chunk inside the row
+            const uint32_t phys = (32 * m >= 128) ? (off ^ vx1) : (off ^ vx0);
+            ldsm_x4_trans(rowb + (uint32_t)(ku * 16 * RB) + phys, a0, a1, a2, a3);
             mma_bf16(st.o[m], a0, a1, a2, a3, b0, b1);
             if (!DUP) mma_bf16(st.o[m], a0, a1, a2, a3, pl[0], pl[1]);
         }
@@ -1397,7 +1472,8 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
 }
 
 template <int D, int G, bool DUP>
-__global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params p) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(const __grid_constant__ Params p,
+                                                                         const __grid_constant__ TensorMaps tm) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int abort_flag;
     Smem<D, G> sm(smem_raw);
@@ -1422,9 +1498,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(Params
     // Warp w issues from scheduler w mod 4.  The consumers of stream 0 (pairs 0, 2, 4) sit on schedulers
     // 0 and 1, those of stream 1 on 2 and 3; each producer is put on a scheduler of its OWN stream, so
     // that it gets the issue slots exactly when its consumers are waiting for it.
-    else if (threadIdx.x < kConsumers + 32) producer_loop<D, G>(p, sm, 0, &abort_flag);        // warp 12: scheduler 0
+    else if (threadIdx.x < kConsumers + 32) producer_loop<D, G>(p, tm, sm, 0, &abort_flag);        // warp 12: scheduler 0
     else if (threadIdx.x < kConsumers + 64) query_loop<D, G, DUP>(p, sm, &abort_flag);         // warp 13: scheduler 1
-    else if (threadIdx.x < kConsumers + 96) producer_loop<D, G>(p, sm, 1, &abort_flag);        // warp 14: scheduler 2
+    else if (threadIdx.x < kConsumers + 96) producer_loop<D, G>(p, tm, sm, 1, &abort_flag);        // warp 14: scheduler 2
     else scheduler_loop<D, G>(p, sm, &abort_flag);                                             // warp 15: scheduler 3
 }
 
