@@ -168,8 +168,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         uint32_t ok;
-        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        // the hint lets the hardware keep the thread suspended for up to ~2 us before it reports "not yet"
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(a), "r"(parity), "r"(2000u) : "memory");
         if (ok) return true;
 #ifndef GKV_NO_BACKOFF
         if (spin > 2) __nanosleep(spin < 64 ? 32 : 256);      // back off: spinning warps steal issue slots
@@ -255,6 +256,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// D = A * B (accumulator input zero: the compiler can use the zero register instead of clearing four registers)
+__device__ __forceinline__ void mma_f16_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void mma_bf16_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
@@ -317,7 +327,8 @@ struct Cfg {
     static constexpr int MT = D / 16;         // output m-tiles (16 channels each) of the transposed PV product
     static constexpr int KSCALE = TG * D * 2; // bytes of klo (or kstep) of one block
     static constexpr int VSCALE = kP * GV * 2;
-    // prepared-q planes, in halves: [plane][chunk][lane][8]; plane 0 = hi, plane 1 = lo, of the item's rung
+    // prepared-q planes, in halves: [plane][chunk][lane][8]; plane 0 = the A operand (hi, lo, hi, lo) of k-step 2i,
+    // plane 1 = that of k-step 2i+1, in the channel arrangement of the item's rung
     static constexpr int QPLANE = CH * 32 * 8;
     static constexpr int QPREP_BYTES = 2 * QPLANE * 2;
     static constexpr int SQ_BYTES = 8 * D * 4;
@@ -722,8 +733,9 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
         const float* q = p.q + ((size_t)b * p.Hq + (size_t)hk * p.rep) * D;
         for (int i = lane; i < 8 * D; i += 32) sq[i] = (i / D) < p.rep ? q[i] : 0.f;
         __syncwarp();
+        // a centroid item needs the fp32 rows only (its blocks are not scored through the MMA planes)
         // per-head power-of-two scale bringing max|q| into [8, 16)
-        for (int h = 0; h < 8; ++h) {
+        for (int h = 0; h < 8 && it.level != 1; ++h) {
             float mx = 0.f;
             for (int d = lane; d < D; d += 32) mx = fmaxf(mx, fabsf(sq[h * D + d]));
 #pragma unroll
@@ -757,8 +769,8 @@ __device__ void query_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
                     else split_bf16x2(x0, x1, hi[jp], lo[jp]);
                 }
                 uint4* dst = reinterpret_cast<uint4*>(qp + ((size_t)i * 32 + lane) * 8);
-                dst[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                dst[C::QPLANE / 8] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                dst[0] = make_uint4(hi[0], lo[0], hi[1], lo[1]);                 // A registers a0..a3 of k-step 2i
+                dst[C::QPLANE / 8] = make_uint4(hi[2], lo[2], hi[3], lo[3]);     // ... and of k-step 2i+1
             }
         }
         __syncwarp();
@@ -829,13 +841,11 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
     const uint32_t kx = swz_term<D, G, BITS>(c.r, 0);
     const uint32_t rowbase = blk + (uint32_t)((tg * UU::U + c.r) * RB);
 
-    float acc[UU::NU][4];
-#pragma unroll
-    for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    float acc[UU::NU][4];                                // first written by the MMAs of chunk 0 (accumulator input zero)
     // q . klo of this token group rides along as one more n-tile whose eight columns all carry the
     // group's klo (so every thread ends up with its own head's value, no shuffle); two accumulators,
     // one per k-step of a chunk, keep the MMAs independent.
-    float bias0[4] = {0.f, 0.f, 0.f, 0.f}, bias1[4] = {0.f, 0.f, 0.f, 0.f};
+    float bias0[4], bias1[4];
 #pragma unroll
     for (int g = 0; g < C::CH / CG; ++g) {
         uint32_t W[UU::NU][LW];
@@ -849,7 +859,7 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
 #pragma unroll
         for (int ii = 0; ii < CG; ++ii) {                // two k-steps at a time
             const int i = g * CG + ii;
-            const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
+            const uint4 qa = qchunk(c, 0, i), qb = qchunk(c, 1, i);      // (hi, lo, hi, lo) of k-steps 2i and 2i+1
             uint32_t sp[4], lp[4];                       // kstep / klo pairs of k-steps 2i and 2i+1 in this arrangement
             if (BITS == 8) {
                 const uint4 v = lds_v4(nat + 16 * i), l = lds_v4(nat - C::KSCALE + 16 * i);
@@ -874,13 +884,18 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
                 lp[0] = prmt(la.x, lb.x, 0x5410); lp[1] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.x, lb.x, 0x7632)), k4));
                 lp[2] = prmt(la.y, lb.y, 0x5410); lp[3] = h2_as_u32(__hmul2(u32_as_h2(prmt(la.y, lb.y, 0x7632)), k4));
             }
-            mma_f16(bias0, qh.x, ql.x, qh.y, ql.y, lp[0], lp[1]);
-            mma_f16(bias1, qh.z, ql.z, qh.w, ql.w, lp[2], lp[3]);
+            if (i == 0) {
+                mma_f16_z(bias0, qa.x, qa.y, qa.z, qa.w, lp[0], lp[1]);
+                mma_f16_z(bias1, qb.x, qb.y, qb.z, qb.w, lp[2], lp[3]);
+            } else {
+                mma_f16(bias0, qa.x, qa.y, qa.z, qa.w, lp[0], lp[1]);
+                mma_f16(bias1, qb.x, qb.y, qb.z, qb.w, lp[2], lp[3]);
+            }
             uint32_t a[8];
-            mul_split(qh.x, ql.x, sp[0], a[0], a[1]);
-            mul_split(qh.y, ql.y, sp[1], a[2], a[3]);
-            mul_split(qh.z, ql.z, sp[2], a[4], a[5]);
-            mul_split(qh.w, ql.w, sp[3], a[6], a[7]);
+            mul_split(qa.x, qa.y, sp[0], a[0], a[1]);
+            mul_split(qa.z, qa.w, sp[1], a[2], a[3]);
+            mul_split(qb.x, qb.y, sp[2], a[4], a[5]);
+            mul_split(qb.z, qb.w, sp[3], a[6], a[7]);
             uint32_t bb[UU::NU][4];                      // B registers of k-steps 2i (0,1) and 2i+1 (2,3)
 #pragma unroll
             for (int n = 0; n < UU::NU; ++n) {
@@ -903,7 +918,10 @@ __device__ __forceinline__ void scores_unit(const Ctx<D, G>& c, uint32_t blk, in
             }
             // k-step major: the two MMAs of an n-tile are NU issues apart, which hides the MMA latency
 #pragma unroll
-            for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[0], a[1], a[2], a[3], bb[n][0], bb[n][1]);
+            for (int n = 0; n < UU::NU; ++n) {
+                if (i == 0) mma_f16_z(acc[n], a[0], a[1], a[2], a[3], bb[n][0], bb[n][1]);
+                else mma_f16(acc[n], a[0], a[1], a[2], a[3], bb[n][0], bb[n][1]);
+            }
 #pragma unroll
             for (int n = 0; n < UU::NU; ++n) mma_f16(acc[n], a[4], a[5], a[6], a[7], bb[n][2], bb[n][3]);
         }
@@ -926,18 +944,19 @@ __device__ __forceinline__ void scores_unit_bf16(const Ctx<D, G>& c, uint32_t bl
     const uint32_t rowbase = blk + (uint32_t)((tg * UU::U + c.r) * D * 2);
     float acc[UU::NU][4];
 #pragma unroll
-    for (int n = 0; n < UU::NU; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-#pragma unroll 2
     for (int i = 0; i < C::CH; ++i) {
-        const uint4 qh = qchunk(c, 0, i), ql = qchunk(c, 1, i);
+        const uint4 qa = qchunk(c, 0, i), qb = qchunk(c, 1, i);
         uint4 w[UU::NU];
         const uint32_t coff = (bt + 16u * (uint32_t)i) ^ kx;
 #pragma unroll
         for (int n = 0; n < UU::NU; ++n) w[n] = lds_v4(rowbase + coff + n * 8 * D * 2);
 #pragma unroll
-        for (int n = 0; n < UU::NU; ++n) mma_bf16(acc[n], qh.x, ql.x, qh.y, ql.y, w[n].x, w[n].y);
+        for (int n = 0; n < UU::NU; ++n) {
+            if (i == 0) mma_bf16_z(acc[n], qa.x, qa.y, qa.z, qa.w, w[n].x, w[n].y);
+            else mma_bf16(acc[n], qa.x, qa.y, qa.z, qa.w, w[n].x, w[n].y);
+        }
 #pragma unroll
-        for (int n = 0; n < UU::NU; ++n) mma_bf16(acc[n], qh.z, ql.z, qh.w, ql.w, w[n].z, w[n].w);
+        for (int n = 0; n < UU::NU; ++n) mma_bf16(acc[n], qb.x, qb.y, qb.z, qb.w, w[n].z, w[n].w);
     }
 #pragma unroll
     for (int n = 0; n < UU::NU; ++n) {
