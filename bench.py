@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the packed-KV decode-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg0|cfg3] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg0|cfg3|cfg2] [--impl reference]
 
 One *step* is one decode step's worth of attention: every layer of the workload attends once
 over its packed cache (one `mixed_attn_decode` call per layer).  The default workload is the
@@ -10,6 +10,12 @@ Qwen3-8B-shaped configuration: 36 layers, 32 query / 8 KV heads, head_dim 128, 3
 first and last block of each row at 16-bit.  All inputs are synthetic and seeded; nothing is read
 from disk.  Sequences are independent, so N GPUs run N disjoint batches with no collective on
 the data path (weak scaling).
+
+Without --workload the line is the 16k-token workload's, and it carries under the key "cfg3" the
+same measurement of the million-token single-sequence workload (28 layers, 28 query / 4 KV heads,
+one sequence of 1,048,576 tokens): resident on one GPU at N = 1, and for N > 1 with the sequence
+split over the GPUs by bytes and the per-rank softmax records exchanged inside the merge kernel
+(strong scaling).
 
 Prints ONE JSON line on rank 0.  `value` is whole-job context-tokens/s with every input resident
 in HBM; `e2e` is the same metric through the Python entry point with the step's queries coming
@@ -54,11 +60,11 @@ METRIC = "packed_kv_decode_attn_context_tokens_per_s"
 UNIT = "context-tokens/s"
 
 
-# DRAM bytes moved per algorithmic byte by the decode kernel on the cfg1 rung mix, from the ncu
-# capture summarised in profiles/decode_mma_cfg1-small_ncu.md (dram read + write of one launch of
-# the profiling-sized slice over its algorithmic bytes).  Traffic grows with the number of blocks,
-# so a full-size launch is that ratio times its own algorithmic bytes.
-DRAM_TRAFFIC_RATIO = {"cfg1": 1.046, "cfg1-small": 1.046}
+# DRAM bytes moved per algorithmic byte by the decode kernel (dram read + write of one launch over
+# its algorithmic bytes, from an ncu capture of the profiling-sized slice of each rung mix; the extra
+# bytes are the per-warp softmax records).  Traffic grows with the number of blocks, so a full-size
+# launch is that ratio times its own algorithmic bytes.
+DRAM_TRAFFIC_RATIO = {"cfg1": 1.067, "cfg1-small": 1.067}
 
 
 def workload_config(w, world, split, cache_gb=None):
@@ -145,18 +151,10 @@ def build_layers(w, rank, device, world=1):
     split = bool(w.get("split")) and world > 1
     for layer in range(w["layers"]):
         if split:
-            from geodesia_kv_b200.distributed import block_cost_bytes, split_blocks
+            from geodesia_kv_b200.distributed import split_blocks
             level = draw_levels(1000 + layer, w["B"], w["Hkv"], nb, w["probs"])
-            cost = torch.zeros(nb, dtype=torch.int64)
-            for h in range(w["Hkv"]):
-                cost += torch.tensor(block_cost_bytes(level[0, h].tolist(), w["D"], GROUP))
-            # balance on the summed cost of the KV heads: the same cut for every head
-            bounds, acc, tot = [0], 0, int(cost.sum())
-            csum = torch.cumsum(cost, 0)
-            for r in range(1, world):
-                bounds.append(int(torch.searchsorted(csum, tot * r // world)))
-            bounds.append(nb)
-            lo, hi = bounds[rank], bounds[rank + 1]
+            # one byte-balanced cut for all KV heads (the product's own partition function)
+            lo, hi = split_blocks(level[0], w["D"], GROUP, world)[rank]
             gen = torch.Generator(device=device).manual_seed(1000 + layer)
             # the whole stream is drawn (so every rank sees the same sequence) one head at a time, the slice kept
             k = torch.empty(w["B"], w["Hkv"], (hi - lo) * 64, w["D"], device=device, dtype=torch.bfloat16)
@@ -183,38 +181,36 @@ def build_layers(w, rank, device, world=1):
     return caches
 
 
-def run_gpu(args):
+def measure_decode(wname, args, env):
+    """Build one workload on this rank, time it, and return the fields of its JSON line."""
     import torch
     import torch.distributed as dist
-    from geodesia_kv_b200 import cuda_ext
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    ext = cuda_ext.get_ext()
-    if ext is None:
-        raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
-
-    w = WORKLOADS[args.workload]
+    rank, world, device, ext = env["rank"], env["world"], env["device"], env["ext"]
+    w = WORKLOADS[wname]
     caches = build_layers(w, rank, device, world)
     split = bool(w.get("split")) and world > 1
-    if split:
-        from geodesia_kv_b200.distributed import sequence_split_decode
     L, B, Hq, D = w["layers"], w["B"], w["Hq"], w["D"]
     gen = torch.Generator(device=device).manual_seed(5 + (0 if split else rank))
     qs = [torch.randn(B, Hq, D, device=device, generator=gen) * D ** -0.5 for _ in range(L)]
     alg_bytes = [c.algorithmic_bytes() + 2 * 4 * B * Hq * D for c in caches]
     cache_bytes = sum(c.data.numel() for c in caches)
 
+    exchange = "none"
+    decoder = None
+    if split:
+        from geodesia_kv_b200.distributed import SequenceSplitDecoder, sequence_split_decode
+        decoder = SequenceSplitDecoder(B, Hq, D, device)
+        ok = torch.tensor([1 if decoder.available else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)            # every rank takes the same path
+        if int(ok.item()):
+            exchange = "peer stores inside the merge kernel (symmetric memory)"
+        else:
+            exchange = f"NCCL all-gather + local merge ({decoder.why or 'a peer could not set up symmetric memory'})"
+            decoder = None
+
     def attend(q, c):
-        if split:          # this rank's blocks -> (m, l, o) records -> all-gather -> local LSE merge
-            return sequence_split_decode(q, c, 0, c.nb)
+        if split:          # this rank's blocks -> (m, l, o) records -> exchange -> LSE merge
+            return decoder(q, c) if decoder is not None else sequence_split_decode(q, c, 0, c.nb)
         return ext.mixed_attn_decode(q, *c.kernel_args())
 
     def step_resident():
@@ -224,7 +220,6 @@ def run_gpu(args):
     q_host = [q.cpu().pin_memory() for q in qs]
     o_host = [torch.empty(B, Hq, D).pin_memory() for _ in range(L)]
     q_dev = [torch.empty_like(q) for q in qs]
-
     h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
 
     def step_e2e_body():
@@ -276,38 +271,42 @@ def run_gpu(args):
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
-    # One step (every layer's launches, and the all-gather of a split sequence) is replayed from a
-    # CUDA graph, as a serving loop would run it: at a few tens of microseconds per layer the
-    # Python and launch overhead would otherwise be what is measured.  --eager times plain launches.
-    # The sequence-split step, whose all-gather would have to be captured too, always runs eagerly.
+    # One step (every layer's launches) is replayed from a CUDA graph, as a serving loop would run it:
+    # at a few tens of microseconds per layer the Python and launch overhead would otherwise be what is
+    # measured.  --eager times plain launches.  A step whose exchange is a collective-library call is
+    # never captured; the peer-store exchange is made of this library's kernels only and is.
     launch_mode = "eager"
     run_step = step_resident
-    if not args.eager and not split:      # a step with the all-gather inside is never captured (it hung here, twice)
+    capturable = not args.eager and (not split or decoder is not None)
+    if capturable:
         try:
-            torch.cuda.synchronize()
+            barrier()
             graph = torch.cuda.CUDAGraph()
-            # thread-local capture mode: other threads of the process (the collective library's
+            # thread-local capture mode: other threads of the process (a collective library's
             # watchdog, the clock sampler) may touch CUDA while this thread captures
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 step_resident()
+            barrier()
             graph.replay()
-            torch.cuda.synchronize()
+            barrier()
             run_step, launch_mode = graph.replay, "cuda graph of one step"
-        except Exception as e:      # capture unsupported here (e.g. by the collective): fall back
+        except Exception as e:      # capture unsupported here: fall back
             launch_mode = f"eager (graph capture failed: {type(e).__name__})"
             torch.cuda.synchronize()
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(env["local"])
     if rank == 0:
         sampler.start()
     ms_total = timed(run_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     for _ in range(2):
         step_e2e()
-    run_e2e = step_e2e
+    ms_e2e_eager = timed(step_e2e, args.steps)
+    ms_e2e, e2e_mode = ms_e2e_eager, "eager"
     if launch_mode.startswith("cuda graph"):
         # the same step with its host-to-device and device-to-host copies as nodes of the graph;
         # the host still waits for the outputs of every step
         try:
+            barrier()
             graph_e2e = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph_e2e, capture_error_mode="thread_local"):
                 step_e2e_body()
@@ -315,11 +314,11 @@ def run_gpu(args):
             def run_e2e():
                 graph_e2e.replay()
                 torch.cuda.synchronize()
+            barrier()
             run_e2e()
+            ms_e2e, e2e_mode = timed(run_e2e, args.steps), "cuda graph of one step, copies included"
         except Exception:
-            run_e2e = step_e2e
             torch.cuda.synchronize()
-    ms_e2e = timed(run_e2e, args.steps)
 
     ms_step = ms_total / args.steps
     tokens_per_step = (1 if split else world) * B * w["T"]
@@ -329,28 +328,64 @@ def run_gpu(args):
     avg_launch_s = (ms_total / 1e3) / launches
     bytes_per_launch = sum(alg_bytes) / L          # this rank's bytes (ranks are byte-balanced)
     achieved = bytes_per_launch / avg_launch_s / 1e9
-
+    Hkv = w["Hkv"]
+    per_call = ext.lib.gkv_decode_launch_count(B, Hq, Hkv, D, max(caches[0].nb, 1), GROUP, 1)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if split else "weak",
         "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
-        "config": dict(workload_config(w, world, split, cache_bytes / 1e9), launch=launch_mode),
+        "config": dict(workload_config(w, world, split, cache_bytes / 1e9), launch=launch_mode, exchange=exchange),
         "per_gpu": value / world,
         "hbm_gbs_per_gpu": achieved,
         "e2e": {"value": tokens_per_step / (ms_e2e / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": L * B * Hq * D * 4, "d2h_bytes_per_step": L * B * Hq * D * 4,
-                "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": launches * (ext.lib.gkv_decode_kernel_launches(B, Hq, w["Hkv"], D, caches[0].nb, GROUP) + (1 if split else 0)),
+                "ms_per_step": ms_e2e / args.steps, "launch": e2e_mode,
+                "eager_value": tokens_per_step / (ms_e2e_eager / args.steps / 1e3),
+                "eager_ms_per_step": ms_e2e_eager / args.steps},
+        "gpu_launches": launches * per_call,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
-                     "traffic": (bytes_per_launch * DRAM_TRAFFIC_RATIO[args.workload]
-                                 if args.workload in DRAM_TRAFFIC_RATIO and not split else None),
-                     "kernel": "decode split kernel (+ its LSE combine, timed together)",
+                     "traffic": (bytes_per_launch * DRAM_TRAFFIC_RATIO[wname]
+                                 if wname in DRAM_TRAFFIC_RATIO and not split else None),
+                     "kernel": "decode split kernel (+ its LSE merge, timed together)",
                      "algorithmic_bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_launch_s * 1e6},
         "clocks": clocks,
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and env.get("cpu_baseline"):
         line["cpu_baseline"] = cpu_baseline_from_cache(caches[0], qs[0], w)
+    del caches, qs, q_dev
+    torch.cuda.empty_cache()
+    return line
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from geodesia_kv_b200 import cuda_ext
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ext = cuda_ext.get_ext()
+    if ext is None:
+        raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
+    env = {"rank": rank, "world": world, "local": local, "device": device, "ext": ext,
+           "cpu_baseline": not args.no_cpu_baseline}
+    if args.workload is not None:
+        line = measure_decode(args.workload, args, env)
+    else:
+        # the headline workload, then the million-token one under its own key
+        line = measure_decode("cfg1", args, env)
+        env["cpu_baseline"] = False
+        c3 = measure_decode("cfg3", args, env)
+        line["cfg3"] = {k: c3[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "ms_per_step", "scaling", "config",
+                                           "per_gpu", "hbm_gbs_per_gpu", "e2e", "gpu_launches", "roofline")}
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
@@ -382,9 +417,59 @@ def cpu_baseline_from_cache(cache, q, w, max_seconds=25.0):
         spent += times[-1]
     dt = sum(times) / len(times)
     tokens = nseq * w["T"] / w["layers"]          # one layer is 1/layers of a step over nseq sequences
-    return {"value": tokens / dt, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
-            "sample": f"layer 0 of the workload, {nseq} of {B} sequences, all KV heads; mean of {len(times)} passes of the "
-                      f"C oracle ({spent:.1f} s in all), scaled to a {w['layers']}-layer step"}
+    out = {"value": tokens / dt, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
+           "sample": f"layer 0 of the workload, {nseq} of {B} sequences, all KV heads; mean of {len(times)} passes of the "
+                     f"C oracle ({spent:.1f} s in all), scaled to a {w['layers']}-layer step"}
+    ref = reference_cuda_kernel_time(cache, q)
+    if ref is not None:
+        out["reference_cuda_kernel"] = ref
+    return out
+
+
+def reference_cuda_kernel_time(cache, q, nb=256):
+    """The reference's own CUDA kernel (built unmodified for sm_100a as a test checker) timed on one
+    16k-token cache row of the workload, beside this library's kernel on the very same tensors.  The
+    reference reads the bytes once per QUERY head, so the row is replicated for the heads of its group
+    and its metadata is shared by all of them.  None when that checker has not been built."""
+    import torch
+    sys.path.insert(0, str(ROOT / "oracle"))
+    try:
+        import build_ref
+        ref = build_ref.load()
+    except Exception:
+        ref = None
+    if ref is None:
+        return None
+    from geodesia_kv_b200 import cuda_ext
+    ext = cuda_ext.get_ext()
+    nb = min(nb, cache.nb)
+    rep = q.shape[1] // cache.data.shape[1]
+    start, stop = int(cache.offs[0, 0, 0]), int(cache.offs[0, 0, nb]) if nb < cache.nb else cache.data.shape[-1]
+    rows = lambda t: t[:1, :1, :nb].expand(1, rep, -1, -1, -1).contiguous()
+    data = cache.data[:1, :1, start:stop].expand(1, rep, -1).contiguous()
+    args = (data, (cache.offs[0, 0, :nb] - start).contiguous(), rows(cache.klo), rows(cache.kstep), rows(cache.vlo),
+            rows(cache.vstep), cache.level[0, 0, :nb].contiguous(), cache.valid[0, 0, :nb].contiguous(), 64, cache.group)
+    qh = q[:1, :rep].contiguous()
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    theirs = ref.mixed_attn_decode(qh, *args)
+    ours = ext.mixed_attn_decode(qh, *args)
+    us_ref = timed(lambda: ref.mixed_attn_decode(qh, *args))
+    us_ours = timed(lambda: ext.mixed_attn_decode(qh, *args))
+    return {"workload": f"one cache row of {nb} blocks replicated for its {rep} query heads (the reference reads the bytes once per head)",
+            "reference_us_per_call": us_ref, "this_library_us_per_call_same_tensors": us_ours,
+            "max_abs_difference": float((ours - theirs).abs().max())}
 
 
 def run_maintenance(args):
@@ -467,7 +552,7 @@ def run_reference(args):
     import gkv_oracle
     gkv_oracle.build()
     gkv_oracle.set_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every core
-    w = WORKLOADS[args.workload]
+    w = WORKLOADS[args.workload or "cfg1"]
     nb_full = w["T"] // 64
     # bounded sample: a few sequences (enough cache rows to occupy every host thread), ONE layer, at
     # most 256 blocks per head (the per-sequence block count of the 16k configs); packed on the CPU
@@ -498,12 +583,15 @@ def run_reference(args):
     for _ in range(args.steps):
         call()
     dt = (time.perf_counter() - t0) / args.steps
-    # one sample = nseq*nb*64 tokens of one layer; a step attends over `layers` layers
+    # One timed step here is a SAMPLE of a decode step: nseq sequences x 1 layer x nb blocks.  `ms_per_step`
+    # is the time that sample took; `value` is the sample's tokens per second divided by the number of
+    # layers, i.e. the context-tokens/s a full step would run at if every layer cost what the sample did.
     value = (nseq * nb * 64) / (dt * w["layers"])
-    sample = (f"{nseq} sequence(s) x 1 layer x {nb} blocks ({nb * 64} tokens each) per step, all {w['Hkv']} KV heads, "
-              f"scaled to a {w['layers']}-layer step")
+    frac = (nseq * nb) / (w["B"] * nb_full * w["layers"])
+    sample = (f"each timed step is {nseq} sequence(s) x 1 layer x {nb} blocks ({nb * 64} tokens each), all {w['Hkv']} KV heads "
+              f"= {frac:.5f} of a full step of the workload; value = sample tokens / time / {w['layers']} layers")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * w["layers"],
+            "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3, "sample_fraction_of_step": frac,
             "higher_is_better": True, "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "fp64 accumulate (C oracle)",
             "data": "synthetic",
             "config": workload_config(w, args.gpus, split),
@@ -520,7 +608,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS) + ["cfg2"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["cfg2"],
+                    help="one workload only; default: cfg1 with cfg3 under its own key")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time plain launches instead of a CUDA graph of the step")

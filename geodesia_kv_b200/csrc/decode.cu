@@ -133,11 +133,11 @@ struct ExchangeParams {
     int* seq;
     int* xstatus;        // sticky error word of the exchange (non-zero: a wait ran out)
     int rank, world, rows;
+    unsigned long long wait_ns;   // how long a rank waits for the others' records before it gives up
 };
 
-#ifndef GKV_EXCHANGE_WAIT_NS
-#define GKV_EXCHANGE_WAIT_NS 1000000000ull
-#endif
+// Process-wide limit of that wait (gkv_set_exchange_wait_ns); one second unless a host says otherwise.
+static unsigned long long g_exchange_wait_ns = 1000000000ull;
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     int v;
@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(kCombineThreads) exchange_combine_kernel(Combi
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > GKV_EXCHANGE_WAIT_NS) break;
+                else if (now - t0 > x.wait_ns) break;
             }
         }
         if (!got) { s_fail = 1; atomicExch(x.xstatus, 1 + (int)threadIdx.x); }
@@ -670,6 +670,12 @@ int gkv_mixed_attn_decode_partial(const float* q, const uint8_t* data, const int
                             workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream);
 }
 
+int gkv_set_exchange_wait_ns(unsigned long long ns) {
+    if (ns == 0) return GKV_E_ARG;
+    gkv::g_exchange_wait_ns = ns;
+    return GKV_OK;
+}
+
 size_t gkv_exchange_inbox_bytes(int world, int rows, int D) {
     if (world <= 0 || world > gkv::kMaxWorld || rows <= 0 || D <= 0) return 0;
     const size_t rec = (size_t)2 * world * rows * (D + 2) * sizeof(float);
@@ -695,6 +701,7 @@ int gkv_mixed_attn_decode_exchange(const float* q, const uint8_t* data, const in
         x.flags[r] = r < world ? reinterpret_cast<int*>(static_cast<uint8_t*>(inboxes[r]) + rec) : nullptr;
     }
     x.seq = seq; x.xstatus = xstatus; x.rank = rank; x.world = world; x.rows = rows;
+    x.wait_ns = gkv::g_exchange_wait_ns;
     return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, plan, workspace,
                             workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream, &x);
 }

@@ -184,6 +184,9 @@ int gkv_mixed_attn_decode_static(const float *q, const uint8_t *data, const int6
  * gkv_mixed_attn_decode_planned (may be NULL).  The reference has no multi-GPU path; this extends
  * its split-and-merge (geodesia_kv_cuda/mixed_attn.cu:58-65, 171-200) across GPUs.               */
 size_t gkv_exchange_inbox_bytes(int world, int rows, int D);
+/* How long (nanoseconds of wall time) the exchange waits for the other ranks' records before it
+ * gives up, for every later call of the process; one second by default.                          */
+int gkv_set_exchange_wait_ns(unsigned long long ns);
 int gkv_mixed_attn_decode_exchange(const float *q, const uint8_t *data, const int64_t *offs,
                                    const void *klo, const void *kstep, const void *vlo, const void *vstep,
                                    const int32_t *level, const int32_t *valid, float *out, const void *plan,
