@@ -32,6 +32,8 @@ SIGNATURES = {
     "gkv_mixed_attn_decode": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_partial": (_i, [_vp] * 10 + [_vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_mixed_attn_decode_static": (_i, [_vp] * 10 + [_i] * 7 + [_i64, _i, _vp]),
+    "gkv_decode_mass_workspace_bytes": (_sz, [_i] * 6),
+    "gkv_mixed_attn_decode_mass": (_i, [_vp] * 10 + [_vp, _vp, _vp, _sz] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_exchange_inbox_bytes": (_sz, [_i, _i, _i]),
     "gkv_set_exchange_wait_ns": (_i, [C.c_ulonglong]),
     "gkv_mixed_attn_decode_exchange": (_i, [_vp] * 10 + [_vp, _vp, _sz] + [_i] * 7 + [_i64, _i] +

@@ -59,7 +59,7 @@ def is_stale(out: Path = LIB, defines: tuple = ()) -> bool:
 # few milliseconds instead of a second, and the producer withholds the bytes of one block, so that the
 # kernel's give-up path (status word, NaN output) can be exercised without ever hanging a GPU.
 WAIT_TEST_LIB = PKG / "libgeodesia_kv_b200_waittest.so"
-WAIT_TEST_DEFINES = ("GKV_WAIT_LIMIT_NS=3000000ull", "GKV_TEST_WITHHOLD_BLOCK=1")
+WAIT_TEST_DEFINES = ("GKV_WAIT_LIMIT_NS=3000000ull", "GKV_TEST_WITHHOLD_BLOCK=1", "GKV_FAST_BUILD=1")   # D = 128, g = 32 only
 
 
 def build(force: bool = False, verbose: bool = False, defines: tuple = (), out: Path = LIB) -> Path:

@@ -24,6 +24,7 @@ struct CombineParams {
     const int* status;   // when non-null and non-zero the producing kernel gave up: poison the output
     int segs;            // > 1: blockIdx.y merges records [y*per_seg, (y+1)*per_seg) into record y of
     int per_seg;         //      an external-layout (segs, rows, D+2) buffer (normalise must be 0)
+    float2* ml_out;      // optional, final level only: (M, L) of every output row (for the per-block softmax mass)
 };
 
 constexpr int kCombineThreads = 256;
@@ -111,6 +112,35 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
         p.out[out_row * (D + 2) + 0] = M;
         p.out[out_row * (D + 2) + 1] = L;
     }
+    if (p.ml_out && p.segs <= 1 && threadIdx.x == 0) p.ml_out[out_row] = make_float2(M, L);
+}
+
+// ---- per-block softmax mass -----------------------------------------------------------------------
+// mass[row][b] = mean over the row's query heads of (sum over the block's tokens of softmax weight), the
+// quantity geodesia_kv/policies.py:1497-1509 obtains from a dense softmax over the keys.  Here it is put
+// together from what the decode kernel reported per block half and head — the reference m it was using
+// and the sum of exp(s - m) — and the final (M, L) of every head: weight = exp(m - M) * sum / L.
+__global__ void block_mass_kernel(const float2* __restrict__ part, const float2* __restrict__ ml,
+                                  const int32_t* __restrict__ level, const int32_t* __restrict__ valid,
+                                  float* __restrict__ mass, int rows, int nb, int rep, int upb, int per_row_meta) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * nb) return;
+    const int row = (int)(i / nb), b = (int)(i % nb);
+    const size_t mi = (size_t)(per_row_meta ? row : 0) * nb + b;
+    float acc = 0.f;
+    if (valid[mi] > 0 && level_ok(level[mi])) {
+        for (int h = 0; h < rep; ++h) {
+            const float2 f = ml[(size_t)row * rep + h];
+            float w = 0.f;
+            for (int u = 0; u < upb; ++u) {
+                const float2 pr = part[(i * upb + u) * rep + h];
+                if (pr.x > -INFINITY) w += expf(pr.x - f.x) * pr.y;
+            }
+            acc += w / fmaxf(f.y, 1e-20f);
+        }
+        acc /= (float)rep;
+    }
+    mass[i] = acc;
 }
 
 // ---- final merge of a sequence that is split over several GPUs ------------------------------------
@@ -377,6 +407,13 @@ static size_t workspace_bytes(int B, int Hq, int Hkv, int D, int nb) {
 }
 
 // A kernel that needs more than 48 KB of dynamic shared memory has to be opted in once per device.
+// extra scratch of a decode that also reports the per-block softmax mass: the kernel's partials and the heads' (M, L)
+static size_t mass_bytes(int B, int Hq, int Hkv, int nb, int group) {
+    const size_t rows = (size_t)B * Hkv, rep = (size_t)(Hq / (Hkv > 0 ? Hkv : 1));
+    const size_t upb = group > 0 && group <= kP ? (size_t)(kP / group) : 1;
+    return ((rows * nb * upb * rep + (size_t)B * Hq) * sizeof(float2) + 255) & ~(size_t)255;
+}
+
 template <typename Kernel>
 static int opt_in_smem(Kernel kernel, unsigned char (&done)[kMaxDevices], size_t bytes) {
     const int dev = current_device();
@@ -440,13 +477,18 @@ static void make_tensor_maps(mma::TensorMaps& tm, const uint8_t* data, size_t to
     tm.usable = ok ? 1 : 0;
 }
 
-template <int D, int G, bool DUP>
-static int launch_mma2(const mma::Params& p, const mma::TensorMaps& tm, int grid, cudaStream_t stream) {
+template <int D, int G, bool DUP, bool MASS>
+static int launch_mma3(const mma::Params& p, const mma::TensorMaps& tm, int grid, cudaStream_t stream) {
     static unsigned char done[kMaxDevices] = {0};
-    if (const int rc = opt_in_smem(mma::decode_mma_kernel<D, G, DUP>, done, mma::Cfg<D, G>::SMEM)) return rc;
-    mma::decode_mma_kernel<D, G, DUP><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p, tm);
+    if (const int rc = opt_in_smem(mma::decode_mma_kernel<D, G, DUP, MASS>, done, mma::Cfg<D, G>::SMEM)) return rc;
+    mma::decode_mma_kernel<D, G, DUP, MASS><<<grid, mma::kThreads, mma::Cfg<D, G>::SMEM, stream>>>(p, tm);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
+}
+
+template <int D, int G, bool DUP>
+static int launch_mma2(const mma::Params& p, const mma::TensorMaps& tm, int grid, cudaStream_t stream) {
+    return p.mass_part ? launch_mma3<D, G, DUP, true>(p, tm, grid, stream) : launch_mma3<D, G, DUP, false>(p, tm, grid, stream);
 }
 
 // up to four query heads per cache row: the (hi, lo) halves of a head share one MMA
@@ -472,7 +514,8 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
                        const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
                        const int32_t* valid, float* out, int normalise, const void* plan_in, void* workspace,
                        size_t ws_bytes, int B, int Hq, int Hkv, int D, int nb, int block, int group,
-                       int64_t stride_bh, int meta_rows, void* stream_, const ExchangeParams* xch = nullptr) {
+                       int64_t stride_bh, int meta_rows, void* stream_, const ExchangeParams* xch = nullptr,
+                       float* mass_out = nullptr) {
     if (block != kP) return GKV_E_BLOCK;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || nb < 0 || group <= 0) return GKV_E_SHAPE;
     if (D <= 0 || D > kMaxD || D % 8 != 0) return GKV_E_SHAPE;
@@ -482,7 +525,8 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     if (!q || !out) return GKV_E_NULL;
     if (nb > 0 && (!data || !offs || !klo || !kstep || !vlo || !vstep || !level || !valid)) return GKV_E_NULL;
     const size_t need = workspace_bytes(B, Hq, Hkv, D, nb);
-    if (!workspace || ws_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return GKV_E_WORKSPACE;
+    const size_t need_all = need + (mass_out ? mass_bytes(B, Hq, Hkv, nb, group) : 0);
+    if (!workspace || ws_bytes < need_all || (reinterpret_cast<uintptr_t>(workspace) & 255)) return GKV_E_WORKSPACE;
     if (plan_in && (reinterpret_cast<uintptr_t>(plan_in) & 15)) return GKV_E_ARG;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
@@ -492,6 +536,9 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     int* header = static_cast<int*>(workspace);
     float* records = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kHeaderBytes);
 
+    if (mass_out && !pl.mma) return GKV_E_SHAPE;           // the by-product exists in the tensor-core kernel only
+    float2* mass_part = mass_out ? reinterpret_cast<float2*>(static_cast<uint8_t*>(workspace) + need) : nullptr;
+    float2* mass_ml = mass_out ? mass_part + (size_t)rows * nb * (kP / group) * rep : nullptr;
     if (pl.mma) {
         const uint4* plan = static_cast<const uint4*>(plan_in);
         if (plan) {
@@ -511,6 +558,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
         mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);
         mp.level = level; mp.valid = valid; mp.part = records; mp.counter = header; mp.status = header + 1;
+        mp.mass_part = mass_part;
         mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps;
         mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
         mp.stride_bh = stride_bh;
@@ -548,7 +596,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     CombineParams c;
     c.rec = records; c.out = out; c.parts = pl.parts; c.D = D; c.rep = rep; c.nsplit = pl.parts;
     c.stride_s = 0; c.normalise = normalise; c.status = pl.mma ? header + 1 : nullptr;
-    c.segs = 1; c.per_seg = 0;
+    c.segs = 1; c.per_seg = 0; c.ml_out = nullptr;
     if (pl.segs > 1) {
         // level 1: (rows, parts, rep, D+2) -> (segs, B*Hq, D+2) behind the records
         float* mid = records + (size_t)B * Hq * pl.parts * (D + 2);
@@ -558,9 +606,16 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0;
         c.stride_s = (int64_t)B * Hq * (D + 2); c.normalise = normalise; c.segs = 1; c.per_seg = 0;
     }
+    c.ml_out = mass_ml;
     if (xch) exchange_combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c, *xch);
     else combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
+    if (mass_out) {
+        const size_t n = (size_t)rows * nb;
+        block_mass_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(mass_part, mass_ml, level, valid, mass_out, rows, nb,
+                                                                       rep, kP / group, meta_rows != 1);
+        GKV_LAUNCH_CHECK();
+    }
     return GKV_OK;
 }
 
@@ -670,6 +725,22 @@ int gkv_mixed_attn_decode_partial(const float* q, const uint8_t* data, const int
                             workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream);
 }
 
+size_t gkv_decode_mass_workspace_bytes(int B, int Hq, int Hkv, int D, int nb, int group) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || nb < 0 || group <= 0) return 0;
+    return gkv::workspace_bytes(B, Hq, Hkv, D, nb) + gkv::mass_bytes(B, Hq, Hkv, nb, group);
+}
+
+int gkv_mixed_attn_decode_mass(const float* q, const uint8_t* data, const int64_t* offs, const void* klo,
+                               const void* kstep, const void* vlo, const void* vstep, const int32_t* level,
+                               const int32_t* valid, float* out, float* mass, const void* plan, void* workspace,
+                               size_t workspace_bytes, int B, int Hq, int Hkv, int D, int nb, int block,
+                               int group, int64_t stride_bh, int meta_rows, void* stream) {
+    if (!mass) return GKV_E_NULL;
+    return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, plan, workspace,
+                            workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream, nullptr,
+                            mass);
+}
+
 int gkv_set_exchange_wait_ns(unsigned long long ns) {
     if (ns == 0) return GKV_E_ARG;
     gkv::g_exchange_wait_ns = ns;
@@ -711,7 +782,7 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     if (parts <= 0 || rows <= 0 || D <= 0) return GKV_E_SHAPE;
     gkv::CombineParams c;
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
-    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr; c.segs = 1; c.per_seg = 0;
+    c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr; c.segs = 1; c.per_seg = 0; c.ml_out = nullptr;
     gkv::combine_kernel<<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;

@@ -106,7 +106,7 @@ struct Desc {           // one block in a ring
     uint32_t off;       // byte offset of the block in the ring
     int32_t nvalid;
     int32_t pad;        // ring bytes the slot occupies (with alignment and wrap waste)
-    int32_t unused;
+    int32_t orig;       // the block's index in its cache row (for the per-block softmax mass)
 };
 
 struct ItemDesc {       // one work item; published one item ahead of its blocks (ring of kItemSlots)
@@ -135,6 +135,8 @@ struct Params {
     const uint4* plan;       // (metadata rows, nb) block entries of every row sorted by rung, from plan_kernel
     const int32_t* plan_tab; // (metadata rows, kPlanTabInts) start of each rung class in that list
     float* part;             // (rows, items per row, consumer warps, rep, D+2)
+    float2* mass_part;       // optional (rows, nb, 2 units, rep): (reference, sum of weights against it) per block half and head,
+                             // natural-log domain; the by-product from which the per-block softmax mass is made
     int* counter;            // work-item counter (zeroed before launch)
     int* status;             // error word (zeroed before launch)
     int B, Hq, Hkv, nb, rep;
@@ -571,7 +573,7 @@ __device__ __forceinline__ bool produce_item(const Params& p, const TensorMaps& 
             withhold = s == 0 && my_seq == 1;
 #endif
             Desc d;
-            d.off = my_dst; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)my_pad; d.unused = 0;
+            d.off = my_dst; d.nvalid = (int)((cur.z >> 8) & 0xffu); d.pad = (int32_t)my_pad; d.orig = (int32_t)cur.w;
             desc[my_slot] = d;
             const unsigned long long soff = ((unsigned long long)cur.y << 32) | cur.x;      // byte offset in the cache
             const uint8_t* src = p.data + soff;
@@ -998,7 +1000,7 @@ __device__ __forceinline__ float move_reference(const Ctx<D, G>& c, WarpState<D,
 // z: scores of this thread's head for the unit's tokens 8*n + 2t + {0,1} (log2 domain); nrel = valid
 // tokens left in this unit (>= 1).  Returns the weights in z.
 template <int D, int G, bool DUP>
-__device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel) {
+__device__ __forceinline__ float softmax_unit(const Ctx<D, G>& c, WarpState<D, G>& st, float (&z)[Unit<D, G>::ZN], int nrel) {
     using UU = Unit<D, G>;
     float mx = -INFINITY;
     if (nrel >= UU::U) {                                 // full unit (the common case): no masks
@@ -1022,6 +1024,7 @@ __device__ __forceinline__ void softmax_unit(const Ctx<D, G>& c, WarpState<D, G>
         ls += z[i];
     }
     st.l += ls;
+    return ls;                                           // this thread's share of the unit's weights (reference st.m)
 }
 
 // Pairs (x[tok][cg], x[tok+1][cg]) of a (64, GV) fp16 plane at shared address `row` (token `tok`, even).
@@ -1296,8 +1299,17 @@ __device__ __forceinline__ void write_record(const Params& p, const Ctx<D, G>& c
     }
 }
 
+// One thread per head and unit reports the head's share of a block's softmax mass: the reference in use
+// (natural-log domain) and the sum of the unit's weights against it.
+template <int D, int G, bool DUP>
+__device__ __forceinline__ void report_mass(const Params& p, const Ctx<D, G>& c, int row, int orig, int upb, int unit, float ref, float sum) {
+    const int head = head_of_row<DUP>(c.r);
+    if (c.t == 0 && head < p.rep && (!DUP || (c.r & 1) == 0))
+        p.mass_part[(((size_t)row * p.nb + orig) * upb + unit) * p.rep + head] = make_float2(ref, sum);
+}
+
 // An item of one of the byte-ring rungs: this warp's blocks of its stream, then its record.
-template <int D, int G, int BITS, bool DUP>
+template <int D, int G, int BITS, bool DUP, bool MASS>
 __device__ __forceinline__ int ring_item(
                                          const Params& p, Smem<D, G>& sm, const Ctx<D, G>& c, const ItemDesc& it,
                                       int stream, int u0, int u1, int& seq, float* rec0) {
@@ -1319,17 +1331,28 @@ __device__ __forceinline__ int ring_item(
         if (!mbar_wait(&full[slot], (uint32_t)(seq / kNSlot) & 1u)) return 4;
         const uint32_t off = desc[slot].off;
         const int nvalid = desc[slot].nvalid;
+        const int orig = MASS ? desc[slot].orig : 0;
         const uint32_t blk = ring + off;
         // both warps of the pair clear the tail (same zeros, so the overlap is harmless)
         if (nvalid < kP) clear_invalid_tail<D, G>(sm.ring + (size_t)stream * kRingBytes + off, BITS, nvalid, c.lane);
+        constexpr int UPB = kP / UU::U;
 #pragma unroll 1
         for (int unit = u0; unit < u1; ++unit) {
             const int nrel = nvalid - unit * UU::U;
-            if (nrel <= 0) break;
+            if (nrel <= 0) {                             // no valid token in this unit: it weighs nothing
+                if (MASS) report_mass<D, G, DUP>(p, c, it.row, orig, UPB, unit, -INFINITY, 0.f);
+                if (MASS) continue;
+                break;
+            }
             float z[UU::ZN];
             if (BITS == 16) scores_unit_bf16<D, G>(c, blk, unit, z);
             else scores_unit<D, G, BITS == 16 ? 8 : BITS>(c, blk, unit, z);
-            softmax_unit<D, G, DUP>(c, st, z, nrel);
+            float ls = softmax_unit<D, G, DUP>(c, st, z, nrel);
+            if (MASS) {
+                ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+                ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+                report_mass<D, G, DUP>(p, c, it.row, orig, UPB, unit, st.m * 0.6931471805599453f, ls);
+            }
             if (BITS == 16) values_unit_bf16<D, G, DUP>(c, st, blk, unit, z);
             else values_unit<D, G, BITS == 16 ? 8 : BITS, DUP>(c, st, blk, unit, z);
         }
@@ -1345,7 +1368,7 @@ __device__ __forceinline__ int ring_item(
 // 16-byte load per lane straight from global memory — all of its loads are in flight before the first
 // is used.  Lanes 0-15 own heads 0-3 and lanes 16-31 heads 4-7; lane l of a half owns channels
 // 8(l & 15) .. +7 of the key (for the scores, reduced over the half) and of the value.
-template <int D, int G>
+template <int D, int G, bool MASS>
 __device__ __forceinline__ void centroid_item(const Params& p, const Ctx<D, G>& c, const ItemDesc& it, const uint4* tab,
                                               int warp, float* rec0) {
     constexpr int kMaxMine = (kMaxItemBlocks + kConsumerWarps - 1) / kConsumerWarps;
@@ -1428,6 +1451,13 @@ __device__ __forceinline__ void centroid_item(const Params& p, const Ctx<D, G>& 
             l[h] += w;
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[h][i] = fmaf(w, vf[i], o[h][i]);
+            if (MASS && hl == 0 && h0 + h < p.rep) {     // the block's whole mass is reported as its first unit
+                constexpr int UPB = kP / G;
+                const int orig = (int)tab[warp + kConsumerWarps * j].w;
+                float2* mp = p.mass_part + ((size_t)it.row * p.nb + orig) * UPB * p.rep + (h0 + h);
+                mp[0] = make_float2(m[h], w);
+                for (int u = 1; u < UPB; ++u) mp[(size_t)u * p.rep] = make_float2(-INFINITY, 0.f);
+            }
         }
     }
 #pragma unroll
@@ -1442,7 +1472,7 @@ __device__ __forceinline__ void centroid_item(const Params& p, const Ctx<D, G>& 
     }
 }
 
-template <int D, int G, bool DUP>
+template <int D, int G, bool DUP, bool MASS>
 __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) {
     using C = Cfg<D, G>;
     using UU = Unit<D, G>;
@@ -1470,14 +1500,16 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
         c.f = sm.sf[ib * 16 + head_of_row<DUP>(c.r)];
         const size_t rec_idx = (size_t)it.row * p.items_per_row + (size_t)(it.item / p.rows);
         float* rec0 = p.part + (rec_idx * kConsumerWarps + warp) * p.rep * (D + 2);
-        if (it.level == 1) centroid_item<D, G>(p, c, it, sm.item_tab + is * kMaxItemBlocks, warp, rec0);
-        else if (it.level == 16) code = ring_item<D, G, 16, DUP>(
+        if (it.level == 1) {
+            centroid_item<D, G, MASS>(p, c, it, sm.item_tab + is * kMaxItemBlocks, warp, rec0);
+        }
+        else if (it.level == 16) code = ring_item<D, G, 16, DUP, MASS>(
                 p, sm, c, it, stream, u0, u1, seq, rec0);
-        else if (it.level == 8) code = ring_item<D, G, 8, DUP>(
+        else if (it.level == 8) code = ring_item<D, G, 8, DUP, MASS>(
                 p, sm, c, it, stream, u0, u1, seq, rec0);
-        else if (it.level == 4) code = ring_item<D, G, 4, DUP>(
+        else if (it.level == 4) code = ring_item<D, G, 4, DUP, MASS>(
                 p, sm, c, it, stream, u0, u1, seq, rec0);
-        else code = ring_item<D, G, 2, DUP>(
+        else code = ring_item<D, G, 2, DUP, MASS>(
                 p, sm, c, it, stream, u0, u1, seq, rec0);
         if (code) break;
         __syncwarp();
@@ -1490,7 +1522,9 @@ __device__ void consumer_loop(const Params& p, Smem<D, G>& sm, int* abort_flag) 
     }
 }
 
-template <int D, int G, bool DUP>
+// MASS: the variant that also reports the blocks' softmax mass.  It is a separate instantiation because the few
+// extra live values of the reporting measurably slow the plain kernel down (5 % on the 16k-token mix).
+template <int D, int G, bool DUP, bool MASS>
 __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(const __grid_constant__ Params p,
                                                                          const __grid_constant__ TensorMaps tm) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -1513,7 +1547,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSM) decode_mma_kernel(const 
     __syncthreads();
     if (threadIdx.x < kConsumers) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
     else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
-    if (threadIdx.x < kConsumers) consumer_loop<D, G, DUP>(p, sm, &abort_flag);
+    if (threadIdx.x < kConsumers) consumer_loop<D, G, DUP, MASS>(p, sm, &abort_flag);
     // Warp w issues from scheduler w mod 4.  The consumers of stream 0 (pairs 0, 2, 4) sit on schedulers
     // 0 and 1, those of stream 1 on 2 and 3; each producer is put on a scheduler of its OWN stream, so
     // that it gets the issue slots exactly when its consumers are waiting for it.

@@ -118,6 +118,12 @@ class _Extension:
         out, _ = self._decode(q, data, offs, klo, kstep, vlo, vstep, level, valid, block, group, partial=True)
         return out
 
+    def mixed_attn_decode_with_mass(self, q, data, offs, klo, kstep, vlo, vstep, level, valid, block, group):
+        """Attention output (B, Hq, D) and, as a by-product of the same kernel, the softmax mass of every
+        block (B, Hkv, nb): mean over the cache row's query heads of the block's summed softmax weight."""
+        return self._decode(q, data, offs, klo, kstep, vlo, vstep, level, valid, block, group, partial=False,
+                            mass=True)
+
     def combine_partials(self, partials: torch.Tensor) -> torch.Tensor:
         """(parts, B, Hq, D+2) records -> (B, Hq, D) attention output."""
         if partials.dim() != 4 or partials.dtype != torch.float32 or not partials.is_cuda:
@@ -131,7 +137,7 @@ class _Extension:
         _lib.check(rc, "gkv_combine_partials")
         return out
 
-    def _decode(self, q, data, offs, klo, kstep, vlo, vstep, level, valid, block, group, partial):
+    def _decode(self, q, data, offs, klo, kstep, vlo, vstep, level, valid, block, group, partial, mass=False):
         if not (q.is_cuda and q.dim() == 3):
             raise RuntimeError("q must be a CUDA tensor of shape (B, H, D)")
         if int(block) != 64:
@@ -160,6 +166,23 @@ class _Extension:
         dev = q.device
         q, data, offs, level, valid = (t.contiguous() for t in (q, data, offs, level, valid))
         klo, kstep, vlo, vstep = (t.contiguous() for t in (klo, kstep, vlo, vstep))
+        if mass:
+            with torch.cuda.device(dev):
+                need = self.lib.gkv_decode_mass_workspace_bytes(B, Hq, Hkv, D, nb, int(group))
+                ws = self._workspace(dev, need)
+                plan = self._plan(offs, level, valid, meta_rows, nb)
+                out = torch.empty((B, Hq, D), dtype=torch.float32, device=dev)
+                bm = torch.zeros((B, Hkv, nb), dtype=torch.float32, device=dev)
+                rc = 0
+                if nb:
+                    rc = self.lib.gkv_mixed_attn_decode_mass(
+                        q.data_ptr(), _ptr(data), _ptr(offs), _ptr(klo), _ptr(kstep), _ptr(vlo), _ptr(vstep),
+                        _ptr(level), _ptr(valid), out.data_ptr(), bm.data_ptr(), _ptr(plan), ws.data_ptr(), ws.numel(),
+                        B, Hq, Hkv, D, nb, int(block), int(group), data.size(-1), meta_rows, _stream(dev))
+                else:
+                    out.zero_()
+            _lib.check(rc, "gkv_mixed_attn_decode_mass")
+            return out, bm
         with torch.cuda.device(dev):
             need = self.lib.gkv_decode_workspace_bytes(B, Hq, Hkv, D, nb)
             ws = self._workspace(dev, need)

@@ -166,6 +166,23 @@ int gkv_mixed_attn_decode_static(const float *q, const uint8_t *data, const int6
                                  int B, int Hq, int Hkv, int D, int nb, int block, int group,
                                  int64_t stride_bh, int meta_rows, void *stream);
 
+/* Decode attention that also reports where the softmax mass went: mass (B, Hkv, nb) fp32, the mean
+ * over a cache row's query heads of the summed softmax weight of each block's tokens — what the
+ * reference's allocator is fed with, and what its hook obtains from a second, dense softmax over
+ * the keys (geodesia_kv/policies.py:1497-1509; prefill: :1421-1451).  Here it is a by-product of
+ * the decode kernel: per block half and head the kernel notes the reference it was using and the
+ * sum of its weights, and a small kernel turns those into masses once the heads' final (m, l) are
+ * known.  Needs gkv_decode_mass_workspace_bytes() of workspace and a shape the tensor-core kernel
+ * takes (D in {64,128}, g in {16,32,64}, GQA width <= 8), else GKV_E_SHAPE.  `plan` as in
+ * gkv_mixed_attn_decode_planned (may be NULL).  Blocks with no valid token get mass 0.           */
+size_t gkv_decode_mass_workspace_bytes(int B, int Hq, int Hkv, int D, int nb, int group);
+int gkv_mixed_attn_decode_mass(const float *q, const uint8_t *data, const int64_t *offs,
+                               const void *klo, const void *kstep, const void *vlo, const void *vstep,
+                               const int32_t *level, const int32_t *valid, float *out, float *mass,
+                               const void *plan, void *workspace, size_t workspace_bytes,
+                               int B, int Hq, int Hkv, int D, int nb, int block, int group,
+                               int64_t stride_bh, int meta_rows, void *stream);
+
 /* One long sequence split over the GPUs of a node, with the exchange of the per-rank (m, l, o)
  * records done by this library's own merge kernel instead of a collective library: every rank
  * calls this on its slice of the blocks (same q on every rank); the last merge level stores the

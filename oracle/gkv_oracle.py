@@ -166,6 +166,40 @@ def mixed_attn_decode(q, data, offs, klo, kstep, vlo, vstep, level, valid, P: in
     return out
 
 
+def block_mass(q, data, offs, klo, kstep, vlo, vstep, level, valid, P: int, group: int) -> np.ndarray:
+    """Softmax mass per block: for every cache row the mean over its query heads of the summed softmax
+    weight of each block's tokens, (B, Hkv, nb) fp32 — the `shared_mass` that the reference's hook gets
+    from a dense softmax of the current query over all keys (geodesia_kv/policies.py:1497-1509), here
+    over the de-quantised keys of the packed cache.  fp64 throughout; blocks without valid tokens get 0."""
+    q = _c(q, np.float32)
+    B, Hq, D = q.shape
+    Hkv = data.shape[1]
+    rep = Hq // Hkv
+    level, valid, offs = np.asarray(level), np.asarray(valid), np.asarray(offs)
+    nb = level.shape[-1]
+    out = np.zeros((B, Hkv, nb), np.float32)
+    for b in range(B):
+        for h in range(Hkv):
+            lv, va, of = (a if a.ndim == 1 else a[b, h] for a in (level, valid, offs))
+            scores, owner = [], []
+            for i in range(nb):
+                n = int(va[i])
+                if n <= 0:
+                    continue
+                nbytes = block_bytes(int(lv[i]), P, D)
+                kd, _ = dequant_block(data[b, h, int(of[i]): int(of[i]) + nbytes], int(lv[i]), P, D, group,
+                                      klo[b, h, i], kstep[b, h, i], vlo[b, h, i], vstep[b, h, i])
+                scores.append(q[b, h * rep:(h + 1) * rep].astype(np.float64) @ kd[:n].astype(np.float64).T)
+                owner += [i] * n
+            if not scores:
+                continue
+            s = np.concatenate(scores, 1)
+            w = np.exp(s - s.max(1, keepdims=True))
+            w /= w.sum(1, keepdims=True)
+            np.add.at(out[b, h], np.asarray(owner), w.mean(0))
+    return out
+
+
 def distortion(krec, vrec, group: int, value_weight: float = 0.0) -> np.ndarray:
     krec = _c(krec, np.float32)
     vrec = _c(vrec, np.float32)

@@ -252,6 +252,32 @@ def kernel_choice_is_mma(ext):
     return ext.lib.gkv_decode_launch_count(1, 4, 1, 128, 64, 32, 0) == 3
 
 
+@pytest.mark.parametrize("shape", [(2, 8, 2, 40, 128, 32, 37), (1, 28, 4, 64, 128, 32, 64), (1, 4, 4, 12, 64, 16, 5),
+                                   (1, 8, 1, 9, 128, 64, 64)],
+                         ids=lambda s: "B%d_Hq%d_Hkv%d_nb%d_D%d_g%d_v%d" % s)
+def test_block_mass_by_product(ext, oracle, shape, kernel_choice):
+    """The per-block softmax mass that rides out of the decode kernel against the oracle's dense softmax
+    over the de-quantised keys (geodesia_kv/policies.py:1497-1509), with every rung, a ragged last block,
+    a block without valid tokens, and the output unchanged by asking for it."""
+    if kernel_choice != "mma":
+        pytest.skip("the by-product exists in the tensor-core kernel only")
+    B, Hq, Hkv, nb, D, group, last_valid = shape
+    c = oracle_cache(oracle, 4242 + nb, B, Hkv, nb, D, group, last_valid=last_valid)
+    c["valid"][..., 3] = 0
+    t = to_torch(c, "cuda")
+    q = np.random.default_rng(6).standard_normal((B, Hq, D), dtype=np.float32) * np.float32(D ** -0.5)
+    qd = torch.from_numpy(q).cuda()
+    out, mass = ext.mixed_attn_decode_with_mass(qd, *kernel_args(t, c))
+    plain = ext.mixed_attn_decode(qd, *kernel_args(t, c))
+    assert torch.equal(out, plain)
+    want = oracle.block_mass(q, *oracle_args(c))
+    got = mass.cpu().numpy()
+    assert got.shape == (B, Hkv, nb)
+    assert np.abs(got.sum(-1) - 1.0).max() < 1e-5            # the masses of a row sum to one
+    assert np.abs(got - want).max() < 1e-5
+    assert (got[..., 3] == 0).all()
+
+
 def test_plan_cache_follows_metadata_edits(ext, oracle):
     """The block lists are kept between calls; writing to level / valid through torch must rebuild them."""
     c = oracle_cache(oracle, 17, 1, 2, 24, 128, 32)
