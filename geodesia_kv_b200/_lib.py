@@ -42,6 +42,13 @@ SIGNATURES = {
     "gkv_pack_blocks": (_i, [_vp, _vp, _i, _vp, _vp] + [_vp] * 4 + [_vp, _vp] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_demote_blocks": (_i, [_vp] * 6 + [_vp] * 4 + [_i] * 5 + [_i64, _i64, _i, _vp]),
     "gkv_unpack_blocks": (_i, [_vp] * 7 + [_vp, _vp] + [_i] * 5 + [_i64, _i, _vp]),
+    "gkv_paged_block_bytes": (_sz, [_i, _i, _i]),
+    "gkv_paged_pack_blocks": (_i, [_vp, _vp, _i, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 4 + [_vp]),
+    "gkv_paged_demote_blocks": (_i, [_vp] * 8 + [_i] * 4 + [_vp]),
+    "gkv_paged_unpack_blocks": (_i, [_vp] * 5 + [_i] * 4 + [_vp]),
+    "gkv_paged_append_token": (_i, [_vp, _vp, _i] + [_vp] * 5 + [_i] * 4 + [_vp]),
+    "gkv_paged_attn_decode": (_i, [_vp, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz] + [_i] * 7 + [_vp]),
+    "gkv_allocate_ragged": (_i, [_vp] * 4 + [C.POINTER(_f), _vp, _f, _vp, _vp, _vp, _i, _i, _vp]),
     "gkv_allocate": (_i, [_vp] * 4 + [C.POINTER(_f), _vp, _f, _vp, _vp, _i, _i, _vp]),
     "gkv_block_distortion": (_i, [_vp] * 4 + [_i] * 5 + [_f, _i64, _i, _vp]),
 }

@@ -29,6 +29,7 @@ struct AllocParams {
     float bits[5];
     float mass_power;
     int nb;
+    const int32_t* nb_of;      // optional: blocks in use per problem (rows of a ragged batch); the rest keep their rung
 };
 
 template <typename T, typename Op>
@@ -58,13 +59,16 @@ __device__ __forceinline__ int landing(const float* __restrict__ r4, int idx, bo
 __global__ void __launch_bounds__(kAllocThreads) allocate_kernel(AllocParams p) {
     __shared__ double sd[kAllocThreads / 32];
     __shared__ uint32_t su[kAllocThreads / 32];
-    const int prob = blockIdx.x, nb = p.nb, tid = threadIdx.x;
-    const float* mass = p.mass + (size_t)prob * nb;
-    const float* E = p.E + (size_t)prob * nb * 5;
-    const int32_t* idx = p.idx + (size_t)prob * nb;
-    const uint8_t* hot = p.hot + (size_t)prob * nb;
-    float* ratio = p.ratio + (size_t)prob * nb * 4;
-    int32_t* tgt = p.tgt + (size_t)prob * nb;
+    const int prob = blockIdx.x, tid = threadIdx.x;
+    const int nb_all = p.nb;
+    const int nb = p.nb_of ? max(0, min(nb_all, p.nb_of[prob])) : nb_all;
+    const float* mass = p.mass + (size_t)prob * nb_all;
+    const float* E = p.E + (size_t)prob * nb_all * 5;
+    const int32_t* idx = p.idx + (size_t)prob * nb_all;
+    const uint8_t* hot = p.hot + (size_t)prob * nb_all;
+    float* ratio = p.ratio + (size_t)prob * nb_all * 4;
+    int32_t* tgt = p.tgt + (size_t)prob * nb_all;
+    for (int b = nb + tid; b < nb_all; b += kAllocThreads) tgt[b] = idx[b];
     const float big = 3.4028234663852886e38f / 4.0f;
 
     uint32_t kmin = 0xffffffffu, kmax = 0u;
@@ -238,6 +242,13 @@ extern "C" {
 int gkv_allocate(const float* mass, const float* E, const int32_t* idx, const uint8_t* hot,
                  const float* bits_host, const double* target_bits, float mass_power, float* ratio,
                  int32_t* tgt_idx, int problems, int nb, void* stream) {
+    return gkv_allocate_ragged(mass, E, idx, hot, bits_host, target_bits, mass_power, ratio, tgt_idx, nullptr,
+                               problems, nb, stream);
+}
+
+int gkv_allocate_ragged(const float* mass, const float* E, const int32_t* idx, const uint8_t* hot,
+                        const float* bits_host, const double* target_bits, float mass_power, float* ratio,
+                        int32_t* tgt_idx, const int32_t* nb_of, int problems, int nb, void* stream) {
     using namespace gkv;
     if (problems <= 0 || nb < 0) return GKV_E_SHAPE;
     if (!bits_host) return GKV_E_NULL;
@@ -245,7 +256,7 @@ int gkv_allocate(const float* mass, const float* E, const int32_t* idx, const ui
     if (!mass || !E || !idx || !hot || !target_bits || !ratio || !tgt_idx) return GKV_E_NULL;
     AllocParams p;
     p.mass = mass; p.E = E; p.idx = idx; p.hot = hot; p.target_bits = target_bits; p.ratio = ratio;
-    p.tgt = tgt_idx; p.mass_power = mass_power; p.nb = nb;
+    p.tgt = tgt_idx; p.mass_power = mass_power; p.nb = nb; p.nb_of = nb_of;
     for (int i = 0; i < 5; ++i) p.bits[i] = bits_host[i];
     allocate_kernel<<<problems, kAllocThreads, 0, (cudaStream_t)stream>>>(p);
     GKV_LAUNCH_CHECK();

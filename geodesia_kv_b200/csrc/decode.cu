@@ -515,7 +515,8 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
                        const int32_t* valid, float* out, int normalise, const void* plan_in, void* workspace,
                        size_t ws_bytes, int B, int Hq, int Hkv, int D, int nb, int block, int group,
                        int64_t stride_bh, int meta_rows, void* stream_, const ExchangeParams* xch = nullptr,
-                       float* mass_out = nullptr) {
+                       float* mass_out = nullptr, size_t pool_bytes = 0) {
+    const bool paged = pool_bytes != 0;        // `data` is a block pool with the scale planes behind each block
     if (block != kP) return GKV_E_BLOCK;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || nb < 0 || group <= 0) return GKV_E_SHAPE;
     if (D <= 0 || D > kMaxD || D % 8 != 0) return GKV_E_SHAPE;
@@ -523,20 +524,22 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     if (rep > 16) return GKV_E_SHAPE;
     if (meta_rows != 1 && meta_rows != rows) return GKV_E_SHAPE;
     if (!q || !out) return GKV_E_NULL;
-    if (nb > 0 && (!data || !offs || !klo || !kstep || !vlo || !vstep || !level || !valid)) return GKV_E_NULL;
+    if (nb > 0 && (!data || !offs || !level || !valid)) return GKV_E_NULL;
+    if (nb > 0 && !paged && (!klo || !kstep || !vlo || !vstep)) return GKV_E_NULL;
     const size_t need = workspace_bytes(B, Hq, Hkv, D, nb);
     const size_t need_all = need + (mass_out ? mass_bytes(B, Hq, Hkv, nb, group) : 0);
     if (!workspace || ws_bytes < need_all || (reinterpret_cast<uintptr_t>(workspace) & 255)) return GKV_E_WORKSPACE;
     if (plan_in && (reinterpret_cast<uintptr_t>(plan_in) & 15)) return GKV_E_ARG;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
-    const bool scales_aligned = ((reinterpret_cast<uintptr_t>(klo) | reinterpret_cast<uintptr_t>(kstep) |
-                                  reinterpret_cast<uintptr_t>(vlo) | reinterpret_cast<uintptr_t>(vstep)) & 15) == 0;
+    const bool scales_aligned = paged ? (reinterpret_cast<uintptr_t>(data) & 15) == 0
+                                      : ((reinterpret_cast<uintptr_t>(klo) | reinterpret_cast<uintptr_t>(kstep) |
+                                          reinterpret_cast<uintptr_t>(vlo) | reinterpret_cast<uintptr_t>(vstep)) & 15) == 0;
     const Plan pl = make_plan(rows, nb, D, group, rep, scales_aligned && nb > 0);
     int* header = static_cast<int*>(workspace);
     float* records = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kHeaderBytes);
 
-    if (mass_out && !pl.mma) return GKV_E_SHAPE;           // the by-product exists in the tensor-core kernel only
+    if ((mass_out || paged) && !pl.mma) return GKV_E_SHAPE;  // the by-product and the pool form exist in the tensor-core kernel only
     float2* mass_part = mass_out ? reinterpret_cast<float2*>(static_cast<uint8_t*>(workspace) + need) : nullptr;
     float2* mass_ml = mass_out ? mass_part + (size_t)rows * nb * (kP / group) * rep : nullptr;
     if (pl.mma) {
@@ -561,9 +564,10 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         mp.mass_part = mass_part;
         mp.B = B; mp.Hq = Hq; mp.Hkv = Hkv; mp.nb = nb; mp.rep = rep; mp.chunk = pl.bps;
         mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
-        mp.stride_bh = stride_bh;
+        mp.stride_bh = paged ? 0 : stride_bh;
+        mp.paged = paged ? 1 : 0;
         int rc;
-        const size_t total = (size_t)rows * (size_t)stride_bh;         // bytes of the cache: all rows
+        const size_t total = paged ? pool_bytes : (size_t)rows * (size_t)stride_bh;   // bytes the tensor maps span
         if (D == 128 && group == 32) rc = launch_mma<128, 32>(mp, total, pl.grid, stream);
 #ifdef GKV_FAST_BUILD      // development builds: only the main shape is instantiated
         else rc = GKV_E_SHAPE;
@@ -739,6 +743,16 @@ int gkv_mixed_attn_decode_mass(const float* q, const uint8_t* data, const int64_
     return gkv::decode_impl(q, data, offs, klo, kstep, vlo, vstep, level, valid, out, 1, plan, workspace,
                             workspace_bytes, B, Hq, Hkv, D, nb, block, group, stride_bh, meta_rows, stream, nullptr,
                             mass);
+}
+
+int gkv_paged_attn_decode(const float* q, const uint8_t* pool, size_t pool_bytes, const int64_t* offs,
+                          const int32_t* level, const int32_t* valid, float* out, float* mass_out, const void* plan,
+                          void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int nb, int block,
+                          int group, void* stream) {
+    if (pool_bytes == 0 && nb > 0) return GKV_E_ARG;
+    return gkv::decode_impl(q, pool, offs, nullptr, nullptr, nullptr, nullptr, level, valid, out, 1, plan, workspace,
+                            workspace_bytes, B, Hq, Hkv, D, nb, block, group, 0, B * Hkv, stream, nullptr, mass_out,
+                            pool_bytes ? pool_bytes : 1);
 }
 
 int gkv_set_exchange_wait_ns(unsigned long long ns) {

@@ -144,6 +144,8 @@ struct Params {
     int items_per_row, items;
     int per_row_meta;
     int rows;
+    int paged;               // 1: `data` is a block pool, offs are pool offsets, and the four scale planes of a quantised
+                             // block sit right behind its bytes ([klo][kstep][vlo][vstep]); klo..vstep above are unused
     int64_t stride_bh;
 };
 
@@ -610,9 +612,17 @@ __device__ __forceinline__ bool produce_item(const Params& p, const TensorMaps& 
             if ((held >> i) & 1u) continue;
             if (quant) {
                 const uint32_t sdst = ring + dst_i + dbytes + (uint32_t)lane * 16u;
-                const size_t so = (size_t)orig_i * K;
+                if (p.paged) {
+                    // the planes follow the block's bytes in the pool, in the order the ring keeps them
+                    const uint32_t ox = __shfl_sync(0xffffffffu, cur.x, i), oy = __shfl_sync(0xffffffffu, cur.y, i);
+                    const uint8_t* sp = p.data + ((((unsigned long long)oy) << 32) | ox) + dbytes + (uint32_t)lane * 16u;
 #pragma unroll
-                for (int r = 0; r < NR; ++r) cp_async16(sdst + (uint32_t)(r * 512), splane[r] + so);
+                    for (int r = 0; r < NR; ++r) cp_async16(sdst + (uint32_t)(r * 512), sp + r * 512);
+                } else {
+                    const size_t so = (size_t)orig_i * K;
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) cp_async16(sdst + (uint32_t)(r * 512), splane[r] + so);
+                }
             }
             cp_async_arrive(&full[slot_i]);              // one arrival per lane once its copies have landed
         }

@@ -9,7 +9,17 @@
 // max(hi-lo, 1e-8)/(2^b-1) with IEEE division, lo and step rounded to fp16 BEFORE the codes
 // are taken, code = clamp(rint((x-lo16)/step16), 0, 2^b-1), codes packed little-endian in the
 // byte (geodesia_kv/packed.py:23-40).  This file is compiled without fast-math.
+//
+// Head dims 64 and 128 (with a group that is a multiple of 8) take the register-resident path of
+// requantise.cuh instead: no fp32 tile in shared memory, every load of the block in flight at once.
+// The tile kernels below remain for the other shapes.
+//
+// Two addressings share the block code: cache ROWS (a byte string per row, dense scale tensors
+// (rows, nb, ...) beside it — the reference's layout) and a paged POOL (every block an offset into
+// one byte pool, the four scale planes of a quantised block stored right behind its bytes as
+// [klo][kstep][vlo][vstep], so a block moves, shrinks and is freed as one piece).
 #include "gkv_common.cuh"
+#include "requantise.cuh"
 
 namespace gkv {
 
@@ -289,6 +299,166 @@ __global__ void __launch_bounds__(kPackThreads) unpack_blocks_kernel(UnpackParam
                            p.vstep + sb * kP * p.gv, p.k_out + sb * kP * D, p.v_out + sb * kP * D, D);
 }
 
+
+// ---- register-resident kernels (requantise.cuh) --------------------------------------------------
+// Scale planes of a block of the paged pool: right behind the block's bytes.
+__device__ __forceinline__ void scales_behind(const uint8_t* blk, int lv, int D, int G, int gv, const __half*& klo,
+                                              const __half*& kstep, const __half*& vlo, const __half*& vstep) {
+    const __half* base = reinterpret_cast<const __half*>(blk + 2 * half_bytes(lv, D));
+    klo = base; kstep = klo + G * D; vlo = kstep + G * D; vstep = vlo + kP * gv;
+}
+
+template <int D>
+__global__ void __launch_bounds__(rq::kThreads, 2) pack_rows_fast_kernel(PackParams p) {
+    __shared__ rq::Shared sm;
+    const int blk = p.b_lo + blockIdx.x, row = blockIdx.y;
+    const int mrow = p.per_row_meta ? row : 0;
+    const int lv = p.level[(size_t)mrow * p.nb + blk];
+    if (!level_ok(lv)) return;
+    int nvalid = p.valid ? p.valid[(size_t)mrow * p.nb + blk] : kP;
+    nvalid = max(1, min(nvalid, kP));
+    const size_t src0 = ((size_t)row * p.nb + blk) * kP * D;
+    const size_t esz = p.src_dtype == 0 ? 4 : 2;
+    rq::Job j;
+    j.src_kind = p.src_dtype; j.src_stride = D; j.nvalid = nvalid;
+    j.ksrc = static_cast<const uint8_t*>(p.k) + src0 * esz;
+    j.vsrc = static_cast<const uint8_t*>(p.v) + src0 * esz;
+    j.old_blk = nullptr; j.old_level = 0; j.oklo = j.okstep = j.ovlo = j.ovstep = nullptr;
+    j.dst = p.data + (size_t)row * p.stride_bh + p.offs[(size_t)mrow * p.nb + blk];
+    j.level = lv; j.group = p.group; j.ek = j.ev = nullptr; j.zero_scales = 1;
+    const size_t sb = (size_t)row * p.nb + blk;
+    j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
+    j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
+    rq::requantise<D>(j, sm);
+}
+
+template <int D>
+__global__ void __launch_bounds__(rq::kThreads, 2) demote_rows_fast_kernel(DemoteParams p) {
+    __shared__ rq::Shared sm;
+    const int blk = blockIdx.x, row = blockIdx.y;
+    const int mrow = p.per_row_meta ? row : 0;
+    const size_t mi = (size_t)mrow * p.nb + blk;
+    const int lo = p.level_old[mi], ln = p.level_new[mi];
+    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo) return;   // never promote
+    const size_t sb = (size_t)row * p.nb + blk;
+    rq::Job j;
+    j.src_kind = 3; j.ksrc = j.vsrc = nullptr; j.src_stride = 0; j.nvalid = kP;
+    j.old_blk = p.data_old + (size_t)row * p.stride_old + p.offs_old[mi]; j.old_level = lo;
+    j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
+    j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
+    j.oklo = j.klo; j.okstep = j.kstep; j.ovlo = j.vlo; j.ovstep = j.vstep;     // rewritten in place
+    j.dst = p.data_new + (size_t)row * p.stride_new + p.offs_new[mi];
+    j.level = ln; j.group = p.group; j.ek = j.ev = nullptr; j.zero_scales = 1;
+    rq::requantise<D>(j, sm);
+}
+
+struct PagedPackParams {
+    const void* k; const void* v; int src_dtype;
+    const int64_t* src_off; int64_t token_stride; const int32_t* nvalid;
+    uint8_t* pool; const int64_t* dst_off; const int32_t* level;
+    float* ek; float* ev;
+    int group, G, gv;
+};
+
+template <int D>
+__global__ void __launch_bounds__(rq::kThreads, 2) paged_pack_kernel(PagedPackParams p) {
+    __shared__ rq::Shared sm;
+    const int i = blockIdx.x;
+    const int lv = p.level[i];
+    const int64_t off = p.dst_off[i];
+    if (!level_ok(lv) || off < 0) return;
+    const size_t esz = p.src_dtype == 0 ? 4 : 2;
+    rq::Job j;
+    j.src_kind = p.src_dtype; j.src_stride = p.token_stride;
+    j.nvalid = p.nvalid ? max(1, min(p.nvalid[i], kP)) : kP;
+    j.ksrc = static_cast<const uint8_t*>(p.k) + (size_t)p.src_off[i] * esz;
+    j.vsrc = static_cast<const uint8_t*>(p.v) + (size_t)p.src_off[i] * esz;
+    j.old_blk = nullptr; j.old_level = 0; j.oklo = j.okstep = j.ovlo = j.ovstep = nullptr;
+    j.dst = p.pool + off; j.level = lv; j.group = p.group; j.zero_scales = 0;
+    j.ek = p.ek ? p.ek + i : nullptr; j.ev = p.ev ? p.ev + i : nullptr;
+    const __half *a, *b, *c, *d;
+    scales_behind(j.dst, lv, D, p.G, p.gv, a, b, c, d);
+    j.klo = const_cast<__half*>(a); j.kstep = const_cast<__half*>(b);
+    j.vlo = const_cast<__half*>(c); j.vstep = const_cast<__half*>(d);
+    rq::requantise<D>(j, sm);
+}
+
+struct PagedDemoteParams {
+    const uint8_t* pool_old; uint8_t* pool_new;
+    const int64_t* off_old; const int32_t* level_old;
+    const int64_t* off_new; const int32_t* level_new;
+    float* ek; float* ev;
+    int group, G, gv;
+};
+
+template <int D>
+__global__ void __launch_bounds__(rq::kThreads, 2) paged_demote_kernel(PagedDemoteParams p) {
+    __shared__ rq::Shared sm;
+    const int i = blockIdx.x;
+    const int lo = p.level_old[i], ln = p.level_new[i];
+    const int64_t oo = p.off_old[i], on = p.off_new[i];
+    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo || oo < 0 || on < 0) return;   // never promote
+    rq::Job j;
+    j.src_kind = 3; j.ksrc = j.vsrc = nullptr; j.src_stride = 0; j.nvalid = kP;
+    j.old_blk = p.pool_old + oo; j.old_level = lo;
+    scales_behind(j.old_blk, lo, D, p.G, p.gv, j.oklo, j.okstep, j.ovlo, j.ovstep);
+    j.dst = p.pool_new + on; j.level = ln; j.group = p.group; j.zero_scales = 0;
+    j.ek = p.ek ? p.ek + i : nullptr; j.ev = p.ev ? p.ev + i : nullptr;
+    const __half *a, *b, *c, *d;
+    scales_behind(j.dst, ln, D, p.G, p.gv, a, b, c, d);
+    j.klo = const_cast<__half*>(a); j.kstep = const_cast<__half*>(b);
+    j.vlo = const_cast<__half*>(c); j.vstep = const_cast<__half*>(d);
+    rq::requantise<D>(j, sm);
+}
+
+struct PagedUnpackParams {
+    const uint8_t* pool; const int64_t* offs; const int32_t* level; float* k_out; float* v_out;
+    int D, group, G, gv;
+};
+
+__global__ void __launch_bounds__(kPackThreads) paged_unpack_kernel(PagedUnpackParams p) {
+    const int i = blockIdx.x, D = p.D;
+    const int lv = p.level[i];
+    const int64_t off = p.offs[i];
+    if (!level_ok(lv) || off < 0) return;
+    const __half *klo, *kstep, *vlo, *vstep;
+    scales_behind(p.pool + off, lv, D, p.G, p.gv, klo, kstep, vlo, vstep);
+    dequant_block_to_tiles(p.pool + off, lv, D, p.group, p.gv, klo, kstep, vlo, vstep,
+                           p.k_out + (size_t)i * kP * D, p.v_out + (size_t)i * kP * D, D);
+}
+
+
+// One new token per cache row, written into the row's open rung-16 block (bf16 rows, so an append is a
+// plain store of two rows of D values) — the block table, the valid count and the row length are
+// advanced on the device, so a decode step needs no host work unless a row starts a new block.
+struct AppendParams {
+    const void* k; const void* v; int src_dtype;
+    uint8_t* pool; const int64_t* offs; int32_t* valid; int32_t* lens; int32_t* status;
+    int cap, D;
+};
+
+__global__ void paged_append_kernel(AppendParams p) {
+    const int row = blockIdx.x, D = p.D;
+    const int len = p.lens[row];
+    const int blk = len / kP, t = len - blk * kP;
+    const int64_t off = blk < p.cap ? p.offs[(size_t)row * p.cap + blk] : -1;
+    __syncthreads();                                   // every thread has read the length
+    if (off < 0) {                                     // no slot was provided for the row's next block
+        if (threadIdx.x == 0) atomicExch(p.status, 1);
+        return;
+    }
+    __nv_bfloat16* kd = reinterpret_cast<__nv_bfloat16*>(p.pool + off) + (size_t)t * D;
+    __nv_bfloat16* vd = kd + (size_t)kP * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        kd[d] = __float2bfloat16_rn(load_src(p.k, p.src_dtype, (size_t)row * D + d));
+        vd[d] = __float2bfloat16_rn(load_src(p.v, p.src_dtype, (size_t)row * D + d));
+    }
+    if (threadIdx.x == 0) {
+        p.valid[(size_t)row * p.cap + blk] = t + 1;
+        p.lens[row] = len + 1;
+    }
+}
+
 static size_t tile_smem(int D) { return (size_t)kP * (2 * tile_ld(D) * sizeof(float) + D); }
 
 static int set_smem(const void* fn, size_t bytes) {
@@ -318,6 +488,12 @@ int gkv_pack_blocks(const void* k, const void* v, int src_dtype, uint8_t* data, 
     p.level = level; p.valid = valid; p.nb = nb; p.b_lo = b_lo; p.D = D; p.group = group;
     p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.per_row_meta = meta_rows != 1;
     p.stride_bh = stride_bh;
+    if (rq::shape_ok(D, group)) {
+        if (D == 128) pack_rows_fast_kernel<128><<<dim3(b_hi - b_lo, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+        else pack_rows_fast_kernel<64><<<dim3(b_hi - b_lo, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+        GKV_LAUNCH_CHECK();
+        return GKV_OK;
+    }
     int rc = set_smem((const void*)pack_blocks_kernel, tile_smem(kMaxD));
     if (rc) return rc;
     pack_blocks_kernel<<<dim3(b_hi - b_lo, rows), kPackThreads, tile_smem(D), (cudaStream_t)stream>>>(p);
@@ -343,6 +519,12 @@ int gkv_demote_blocks(const uint8_t* data_old, const int64_t* offs_old, const in
     p.klo = (__half*)klo; p.kstep = (__half*)kstep; p.vlo = (__half*)vlo; p.vstep = (__half*)vstep;
     p.nb = nb; p.D = D; p.group = group; p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group;
     p.per_row_meta = meta_rows != 1; p.stride_old = stride_old; p.stride_new = stride_new;
+    if (rq::shape_ok(D, group)) {
+        if (D == 128) demote_rows_fast_kernel<128><<<dim3(nb, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+        else demote_rows_fast_kernel<64><<<dim3(nb, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+        GKV_LAUNCH_CHECK();
+        return GKV_OK;
+    }
     int rc = set_smem((const void*)demote_blocks_kernel, tile_smem(kMaxD));
     if (rc) return rc;
     demote_blocks_kernel<<<dim3(nb, rows), kPackThreads, tile_smem(D), (cudaStream_t)stream>>>(p);
@@ -366,6 +548,84 @@ int gkv_unpack_blocks(const uint8_t* data, const int64_t* offs, const void* klo,
     p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.per_row_meta = meta_rows != 1;
     p.stride_bh = stride_bh;
     unpack_blocks_kernel<<<dim3(nb, rows), kPackThreads, 0, (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+size_t gkv_paged_block_bytes(int level, int D, int group) {
+    using namespace gkv;
+    if (!level_ok(level) || D <= 0 || group <= 0) return 0;
+    const int kg = group < kP ? group : kP, vg = group < D ? group : D;
+    const size_t scales = (level == 8 || level == 4 || level == 2) ? (size_t)4 * ((size_t)(kP / kg) * D + (size_t)kP * (D / vg)) : 0;
+    return (size_t)2 * half_bytes(level, D) + scales;
+}
+
+int gkv_paged_pack_blocks(const void* k, const void* v, int src_dtype, const int64_t* src_off, int64_t token_stride,
+                          const int32_t* nvalid, uint8_t* pool, const int64_t* dst_off, const int32_t* level,
+                          float* ek, float* ev, int n, int D, int block, int group, void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (n < 0 || !rq::shape_ok(D, group) || token_stride < D) return GKV_E_SHAPE;
+    if (src_dtype < 0 || src_dtype > 2 || (ek == nullptr) != (ev == nullptr)) return GKV_E_ARG;
+    if (n == 0) return GKV_OK;
+    if (!k || !v || !src_off || !pool || !dst_off || !level) return GKV_E_NULL;
+    PagedPackParams p;
+    p.k = k; p.v = v; p.src_dtype = src_dtype; p.src_off = src_off; p.token_stride = token_stride; p.nvalid = nvalid;
+    p.pool = pool; p.dst_off = dst_off; p.level = level; p.ek = ek; p.ev = ev; p.group = group;
+    p.G = kP / min(group, kP); p.gv = D / min(group, D);
+    if (D == 128) paged_pack_kernel<128><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+    else paged_pack_kernel<64><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+int gkv_paged_demote_blocks(const uint8_t* pool_old, const int64_t* off_old, const int32_t* level_old,
+                            uint8_t* pool_new, const int64_t* off_new, const int32_t* level_new, float* ek,
+                            float* ev, int n, int D, int block, int group, void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (n < 0 || !rq::shape_ok(D, group)) return GKV_E_SHAPE;
+    if ((ek == nullptr) != (ev == nullptr)) return GKV_E_ARG;
+    if (n == 0) return GKV_OK;
+    if (!pool_old || !off_old || !level_old || !pool_new || !off_new || !level_new) return GKV_E_NULL;
+    PagedDemoteParams p;
+    p.pool_old = pool_old; p.pool_new = pool_new; p.off_old = off_old; p.level_old = level_old;
+    p.off_new = off_new; p.level_new = level_new; p.ek = ek; p.ev = ev; p.group = group;
+    p.G = kP / min(group, kP); p.gv = D / min(group, D);
+    if (D == 128) paged_demote_kernel<128><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+    else paged_demote_kernel<64><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+int gkv_paged_unpack_blocks(const uint8_t* pool, const int64_t* offs, const int32_t* level, float* k_out,
+                            float* v_out, int n, int D, int block, int group, void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (n < 0 || !rq::shape_ok(D, group)) return GKV_E_SHAPE;
+    if (n == 0) return GKV_OK;
+    if (!pool || !offs || !level || !k_out || !v_out) return GKV_E_NULL;
+    PagedUnpackParams p;
+    p.pool = pool; p.offs = offs; p.level = level; p.k_out = k_out; p.v_out = v_out; p.D = D; p.group = group;
+    p.G = kP / min(group, kP); p.gv = D / min(group, D);
+    paged_unpack_kernel<<<n, kPackThreads, 0, (cudaStream_t)stream>>>(p);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+int gkv_paged_append_token(const void* k, const void* v, int src_dtype, uint8_t* pool, const int64_t* offs,
+                           int32_t* valid, int32_t* lens, int32_t* status, int rows, int cap, int D, int block,
+                           void* stream) {
+    using namespace gkv;
+    if (block != kP) return GKV_E_BLOCK;
+    if (rows < 0 || cap <= 0 || D <= 0 || D > kMaxD) return GKV_E_SHAPE;
+    if (src_dtype < 0 || src_dtype > 2) return GKV_E_ARG;
+    if (rows == 0) return GKV_OK;
+    if (!k || !v || !pool || !offs || !valid || !lens || !status) return GKV_E_NULL;
+    AppendParams p;
+    p.k = k; p.v = v; p.src_dtype = src_dtype; p.pool = pool; p.offs = offs; p.valid = valid; p.lens = lens;
+    p.status = status; p.cap = cap; p.D = D;
+    paged_append_kernel<<<rows, D <= 64 ? 64 : 128, 0, (cudaStream_t)stream>>>(p);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }

@@ -255,6 +255,65 @@ int gkv_unpack_blocks(const uint8_t *data, const int64_t *offs, const void *klo,
                       float *v_out, int rows, int nb, int D, int block, int group, int64_t stride_bh,
                       int meta_rows, void *stream);
 
+/* ---- paged pool ----------------------------------------------------------------------
+ * The reference's serving plugin keeps one cache object per sequence and frees nothing when a
+ * block is demoted (vllm_plugin/kv_cache.py:15-104); its capacity claim (README.md:243-248) needs
+ * demotion to give memory back.  The pool form below is what makes that real: every block of
+ * every sequence, head and layer is an offset into ONE byte pool, and the four scale planes of a
+ * quantised block are stored right behind its bytes, in the order [klo][kstep][vlo][vstep] (fp16,
+ * shapes (G, D), (G, D), (64, gv), (64, gv)), so that a block is allocated, moved, shrunk and freed
+ * as one piece of gkv_paged_block_bytes(level, D, group) bytes (32768 / 18432 / 10240 / 6144 / 512
+ * at D = 128, g = 32).  Slot management (size-class free lists) is the caller's; these entry points
+ * only read and write blocks.  Block offsets must be multiples of 16 (of 128 for the tiled copies
+ * of the decode kernel to be used; other offsets fall back to a slower copy).  D in {64, 128},
+ * group a multiple of 8; else GKV_E_SHAPE.  No counterpart in the reference's C++ (its kernel
+ * takes dense side tensors, mixed_attn.cu:202-216).                                          */
+size_t gkv_paged_block_bytes(int level, int D, int group);
+
+/* Quantise n blocks from dense rows into pool slots.  Block i reads 64 token rows of D elements
+ * starting at element src_off[i] of k and of v (consecutive tokens token_stride elements apart;
+ * rows beyond nvalid[i] repeat the last real row; nvalid may be NULL = all 64) and is written at
+ * rung level[i] to pool + dst_off[i]; entries with dst_off < 0 are skipped.  ek, ev (n floats,
+ * both or neither): += max over the block's tokens of the L2 norm of the quantisation error of
+ * K and of V — the radii the reference accumulates when it demotes (policies.py:905-906).    */
+int gkv_paged_pack_blocks(const void *k, const void *v, int src_dtype, const int64_t *src_off,
+                          int64_t token_stride, const int32_t *nvalid, uint8_t *pool,
+                          const int64_t *dst_off, const int32_t *level, float *ek, float *ev, int n,
+                          int D, int block, int group, void *stream);
+
+/* Demote n blocks: block i is read at (pool_old + off_old[i], level_old[i]), dequantised exactly
+ * and re-quantised at level_new[i] into pool_new + off_new[i] (policies.py:870-908).  Entries
+ * with level_new >= level_old or a negative offset are skipped.  pool_new may be pool_old as
+ * long as a destination slot overlaps no OTHER entry's source or destination.  ek, ev as above. */
+int gkv_paged_demote_blocks(const uint8_t *pool_old, const int64_t *off_old, const int32_t *level_old,
+                            uint8_t *pool_new, const int64_t *off_new, const int32_t *level_new,
+                            float *ek, float *ev, int n, int D, int block, int group, void *stream);
+
+/* Exact dequantisation of n pool blocks -> fp32 k_out, v_out (n, 64, D) (tests, debugging).   */
+int gkv_paged_unpack_blocks(const uint8_t *pool, const int64_t *offs, const int32_t *level,
+                            float *k_out, float *v_out, int n, int D, int block, int group,
+                            void *stream);
+
+/* Append ONE token to every cache row: k, v (rows, D) of src_dtype are rounded to bf16 and stored
+ * as token lens[r] of row r, i.e. into block lens[r] / 64 of the row's table (offs, valid: (rows,
+ * cap)), which must already hold a rung-16 slot; valid and lens are advanced on the device.  A row
+ * whose next block has no slot (offset < 0, or beyond cap) is left alone and *status is set to 1.
+ * What live_cache.py:84-111 of the reference does with torch.cat on dense tensors.            */
+int gkv_paged_append_token(const void *k, const void *v, int src_dtype, uint8_t *pool, const int64_t *offs,
+                           int32_t *valid, int32_t *lens, int32_t *status, int rows, int cap, int D,
+                           int block, void *stream);
+
+/* Decode attention over a block table: offs, level, valid are (B*Hkv, nb) with nb the longest
+ * row's block count; shorter rows are padded with valid = 0 entries (never read).  Same output
+ * as gkv_mixed_attn_decode on the equivalent row caches (mixed_attn.cu:8-197).  pool_bytes is the
+ * size of the pool (the span the copy engine may address).  mass_out may be NULL; otherwise
+ * (B*Hkv, nb) fp32 as in gkv_mixed_attn_decode_mass, and the workspace must hold
+ * gkv_decode_mass_workspace_bytes().  `plan` as in gkv_mixed_attn_decode_planned (may be NULL). */
+int gkv_paged_attn_decode(const float *q, const uint8_t *pool, size_t pool_bytes, const int64_t *offs,
+                          const int32_t *level, const int32_t *valid, float *out, float *mass_out,
+                          const void *plan, void *workspace, size_t workspace_bytes, int B, int Hq,
+                          int Hkv, int D, int nb, int block, int group, void *stream);
+
 /* ---- allocator ----------------------------------------------------------------------
  * Replaces the Lagrangian rung allocation of Policy.attend,
  * geodesia_kv/policies.py:810-868, for `problems` independent cache rows.
@@ -270,6 +329,14 @@ int gkv_unpack_blocks(const uint8_t *data, const int64_t *offs, const void *klo,
 int gkv_allocate(const float *mass, const float *E, const int32_t *idx, const uint8_t *hot,
                  const float *bits_host, const double *target_bits, float mass_power, float *ratio,
                  int32_t *tgt_idx, int problems, int nb, void *stream);
+
+/* The same for a ragged batch: problem p uses only its first nb_of[p] blocks (arrays keep the
+ * common stride nb); blocks beyond that come back with their current index.  nb_of == NULL is
+ * gkv_allocate.                                                                              */
+int gkv_allocate_ragged(const float *mass, const float *E, const int32_t *idx, const uint8_t *hot,
+                        const float *bits_host, const double *target_bits, float mass_power,
+                        float *ratio, int32_t *tgt_idx, const int32_t *nb_of, int problems, int nb,
+                        void *stream);
 
 /* Distortion table of policies.py:774-808 computed from rung-16 (bf16) blocks
  * of the packed cache: E (rows, nb, 5).  Blocks at other rungs get a zero row
