@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the packed-KV decode-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg0|cfg3|cfg2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg0|cfg3|cfg4|cfg2] [--impl reference]
 
 One *step* is one decode step's worth of attention: every layer of the workload attends once
 over its packed cache (one `mixed_attn_decode` call per layer).  The default workload is the
@@ -22,6 +22,12 @@ in HBM; `e2e` is the same metric through the Python entry point with the step's 
 from pinned host memory and the outputs read back; `roofline` compares the decode kernel's
 algorithmic bytes per launch with the measured HBM copy bandwidth; `cpu_baseline` times the CPU
 oracle on a bounded sample (rank 0, N=1 only).
+
+`--workload cfg4` is paged batched serving: 256 sequences of lognormal length in ONE block pool with
+per-block rungs from this library's allocator at 4 bits/value; a step appends one token to every
+sequence and attends over the ragged batch, layer by layer; `value` is decode tokens/s.
+`--workload cfg2` is the cache-maintenance loop: one block appended per row and step, then the
+distortion, allocator and demotion kernels.
 
 `--impl reference` times the CPU restatement of the reference's path on the host cores instead
 (the reference ships no CPU kernel and its Python cannot travel to the GPU box).
@@ -54,6 +60,17 @@ WORKLOADS = {
     "cfg3": dict(layers=28, Hq=28, Hkv=4, D=128, B=1, T=1048576, probs=(0.02, 0.08, 0.30, 0.40, 0.20), split=True,
                  name="qwen2.5-7b-1m-shape decode attention, 28 layers, 1 seq x 1048576 tok"),
 }
+PAGED = {
+    # 256 concurrent sequences, length = clip(round(exp(N(ln 8192, sigma))), 1024, 32768) rounded up to whole blocks;
+    # sigma is not part of the published configuration: 0.6 is this benchmark's choice
+    "cfg4": dict(layers=36, Hq=16, Hkv=2, D=128, seqs=256, median=8192, sigma=0.6, lo=1024, hi=32768, budget=4.0, seed=4000,
+                 name="qwen2.5-3b-shape paged batched serving, 36 layers, 256 sequences of lognormal length, 4 bits/value"),
+    "cfg4-small": dict(layers=2, Hq=16, Hkv=2, D=128, seqs=256, median=8192, sigma=0.6, lo=1024, hi=32768, budget=4.0, seed=4000,
+                       name="profiling-sized slice of the paged serving workload: 2 layers, 256 sequences"),
+}
+# share of blocks per rung (16, 8, 4, 2, centroid) the allocator leaves at 4 bits/value on the paged workload;
+# the CPU arm, which has no allocator kernel to run, samples its rungs from it
+PAGED_RUNG_MIX = (0.04, 0.02, 0.30, 0.40, 0.24)
 GROUP = 32
 LADDER = (16, 8, 4, 2, 1)
 METRIC = "packed_kv_decode_attn_context_tokens_per_s"
@@ -358,6 +375,217 @@ def measure_decode(wname, args, env):
     return line
 
 
+def lognormal_lengths(w):
+    """Seeded sequence lengths of the paged workload, rounded up to whole 64-token blocks."""
+    import numpy as np
+    rng = np.random.default_rng(w["seed"])
+    n = np.clip(np.rint(np.exp(rng.normal(np.log(w["median"]), w["sigma"], size=w["seqs"]))), w["lo"], w["hi"])
+    return ((n.astype(np.int64) + 63) // 64) * 64
+
+
+def measure_paged(wname, args, env):
+    """Paged batched serving on this rank's share of the sequences (no collective on the data path)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from geodesia_kv_b200.paged import PagedLayerCache, PagedPool
+    rank, world, device = env["rank"], env["world"], env["device"]
+    w = PAGED[wname]
+    L, Hq, Hkv, D = w["layers"], w["Hq"], w["Hkv"], w["D"]
+    lengths_all = lognormal_lengths(w)
+    lengths = lengths_all[rank::world]                           # sequences are dealt round-robin to the GPUs
+    B = int(lengths.size)
+    steps_ahead = 64 * (2 + (3 * (max(args.warmup, 3) + args.steps) + 8) // 64)
+    dense_layer = int(lengths.sum()) * Hkv * D * 2 * 2
+    # room for the final caches (about budget/16 of dense plus the exact blocks), one layer's rung-16
+    # transient while it is being built, and the blocks the timed steps will open
+    cap = int(L * dense_layer * (w["budget"] / 16.0) * 1.25 + L * B * Hkv * 8 * 32768 + 2 * dense_layer + (1 << 30))
+    pool = PagedPool(cap, D, GROUP, device)
+    layers = []
+    Tmax = int(lengths.max())
+    k = torch.empty(B, Hkv, Tmax, D, device=device, dtype=torch.bfloat16)
+    v = torch.empty_like(k)
+    nblk = lengths // 64
+    demoted = 0
+    for layer in range(L):
+        gen = torch.Generator(device=device).manual_seed(w["seed"] + layer + 100003 * rank)
+        k.normal_(generator=gen)
+        v.normal_(generator=gen)
+        c = PagedLayerCache(pool, B, Hkv, cap_blocks=int(nblk.max()) + steps_ahead // 64 + 2)
+        c.prefill(k, v, lengths)
+        # mass ~ (distance in blocks from the newest + 1)^-1.2, normalised, + 0.1 on block 0
+        nbr = np.repeat(nblk, Hkv)
+        b = np.arange(c.nb)[None, :]
+        m = np.where(b < nbr[:, None], np.maximum(nbr[:, None] - b, 1).astype(np.float64) ** -1.2, 0.0)
+        m /= m.sum(1, keepdims=True)
+        m[:, 0] += 0.1
+        demoted += c.maintain(w["budget"], mass=torch.from_numpy(m.astype(np.float32)).to(device))
+        c.reserve(steps_ahead)
+        layers.append(c)
+    del k, v
+    torch.cuda.empty_cache()
+    bpv = float(np.mean([c.bits_per_value() for c in layers]))
+    hist = np.zeros(5)
+    for c in layers:
+        hist += np.array([int((c.level_h == r).sum()) for r in LADDER])
+    rung_mix = [round(float(x), 4) for x in hist / hist.sum()]
+    gen = torch.Generator(device=device).manual_seed(5 + rank)
+    qs = [torch.randn(B, Hq, D, device=device, generator=gen) * D ** -0.5 for _ in range(L)]
+    kn = [torch.randn(B, Hkv, D, device=device, generator=gen).to(torch.bfloat16) for _ in range(L)]
+    vn = [torch.randn(B, Hkv, D, device=device, generator=gen).to(torch.bfloat16) for _ in range(L)]
+    decay = 0.9
+
+    def layer_step(c, q, k1, v1):
+        c.append_device(k1, v1)
+        out, mass = c.attend(q, want_mass=True)
+        c.observe(mass, decay)
+        return out
+
+    def step_resident():
+        for c, q, k1, v1 in zip(layers, qs, kn, vn):
+            layer_step(c, q, k1, v1)
+
+    q_host = [q.cpu().pin_memory() for q in qs]
+    k_host = [x.cpu().pin_memory() for x in kn]
+    v_host = [x.cpu().pin_memory() for x in vn]
+    o_host = [torch.empty(B, Hq, D).pin_memory() for _ in range(L)]
+    q_dev, k_dev, v_dev = [torch.empty_like(x) for x in qs], [torch.empty_like(x) for x in kn], [torch.empty_like(x) for x in vn]
+    h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def step_e2e_body():
+        # the step's queries and new K/V rows come from pinned host memory, layer by layer on a copy
+        # stream, and every layer's output goes back to the host on another; all inside the timed region
+        cur = torch.cuda.current_stream()
+        h2d_stream.wait_stream(cur)
+        d2h_stream.wait_stream(cur)
+        ready = []
+        with torch.cuda.stream(h2d_stream):
+            for i in range(L):
+                q_dev[i].copy_(q_host[i], non_blocking=True)
+                k_dev[i].copy_(k_host[i], non_blocking=True)
+                v_dev[i].copy_(v_host[i], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(h2d_stream)
+                ready.append(ev)
+        for i, c in enumerate(layers):
+            cur.wait_event(ready[i])
+            out = layer_step(c, q_dev[i], k_dev[i], v_dev[i])
+            done = torch.cuda.Event()
+            done.record(cur)
+            d2h_stream.wait_event(done)
+            with torch.cuda.stream(d2h_stream):
+                o_host[i].copy_(out, non_blocking=True)
+            out.record_stream(d2h_stream)
+        cur.wait_stream(d2h_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    launch_mode, run_step = "eager", step_resident
+    if not args.eager:
+        try:
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                step_resident()
+            barrier()
+            run_step, launch_mode = graph.replay, "cuda graph of one step"
+        except Exception as e:
+            launch_mode = f"eager (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+    sampler = ClockSampler(env["local"])
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(run_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    def step_e2e():
+        step_e2e_body()
+        torch.cuda.synchronize()
+    step_e2e()
+    ms_e2e_eager = timed(step_e2e, args.steps)
+    ms_e2e, e2e_mode = ms_e2e_eager, "eager"
+    if launch_mode.startswith("cuda graph"):
+        try:
+            barrier()
+            graph_e2e = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_e2e, capture_error_mode="thread_local"):
+                step_e2e_body()
+
+            def run_e2e():
+                graph_e2e.replay()
+                torch.cuda.synchronize()
+            barrier()
+            run_e2e()
+            ms_e2e, e2e_mode = timed(run_e2e, args.steps), "cuda graph of one step, copies included"
+        except Exception:
+            torch.cuda.synchronize()
+    status = max(int(c.status.item()) for c in layers)
+    for c in layers:
+        c.sync_lengths()
+    # bytes one step reads: every block at its rung with its scale planes, 16 B of table entry per block,
+    # plus the query/output/new-row traffic (the lengths grew by a few tokens while timing: negligible)
+    alg = sum(c.bytes_in_pool() + int(c.blocks_per_seq().sum()) * Hkv * 16 for c in layers) / L + 2 * 4 * B * Hq * D
+    ms_step = ms_total / args.steps
+    seqs_total = int(lengths_all.size)
+    value = seqs_total / (ms_step / 1e3)
+    peak, peak_kind = measured_peak_gbs()
+    achieved = alg / (ms_step / 1e3 / L) / 1e9
+    ctx_tokens = int(lengths_all.sum())
+    per_call = env["ext"].lib.gkv_decode_launch_count(B, Hq, Hkv, D, layers[0].cap, GROUP, 0) + 2   # + block-mass kernel, + append
+    line = {
+        "metric": "paged_kv_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
+        "config": {"workload": w["name"], "layers": L, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "group": GROUP,
+                   "sequences": seqs_total, "sequences_per_gpu": B, "length_distribution":
+                   f"lognormal, median {w['median']}, sigma {w['sigma']} (this benchmark's choice), clipped to {w['lo']}..{w['hi']}, "
+                   f"whole blocks; seed {w['seed']}",
+                   "context_tokens_total": ctx_tokens, "mean_context_tokens": ctx_tokens / seqs_total,
+                   "rungs": f"this library's allocator at {w['budget']} bits/value, power-law mass (exponent 1.2, sink 0.1)",
+                   "bits_per_value": bpv, "rung_mix_16_8_4_2_c": rung_mix, "blocks_demoted_while_building": demoted,
+                   "pool_bytes_in_use": pool.bytes_in_use, "pool_bytes_reserved": pool.bytes_reserved,
+                   "dense_bf16_bytes": L * dense_layer,
+                   "step": "per layer: append one token per sequence, attend over the ragged batch (one kernel call, "
+                           "per-block mass as a by-product), fold the mass into its running mean; attention only, no model weights",
+                   "sharding": f"dp{world}: sequences dealt round-robin, no collective", "launch": launch_mode,
+                   "l2": f"inputs larger than L2: {pool.bytes_in_use / 1e9:.1f} GB of packed cache per GPU, each layer read once per step"},
+        "context_tokens_per_s": ctx_tokens / (ms_step / 1e3),
+        "hbm_gbs_per_gpu": achieved,
+        "e2e": {"value": seqs_total / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": L * (B * Hq * D * 4 + 2 * B * Hkv * D * 2), "d2h_bytes_per_step": L * B * Hq * D * 4,
+                "ms_per_step": ms_e2e / args.steps, "launch": e2e_mode,
+                "eager_value": seqs_total / (ms_e2e_eager / args.steps / 1e3), "eager_ms_per_step": ms_e2e_eager / args.steps},
+        "gpu_launches": args.steps * L * per_call,
+        "append_status": status,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "kernel": "decode split kernel over the block table (+ append, merge and mass kernels, timed together)",
+                     "algorithmic_bytes_per_launch": alg, "avg_launch_us": ms_step * 1e3 / L},
+        "clocks": clocks,
+    }
+    del layers
+    torch.cuda.empty_cache()
+    return line
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -377,7 +605,9 @@ def run_gpu(args):
         raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
     env = {"rank": rank, "world": world, "local": local, "device": device, "ext": ext,
            "cpu_baseline": not args.no_cpu_baseline}
-    if args.workload is not None:
+    if args.workload in PAGED:
+        line = measure_paged(args.workload, args, env)
+    elif args.workload is not None:
         line = measure_decode(args.workload, args, env)
     else:
         # the headline workload, then the million-token one under its own key
@@ -473,71 +703,147 @@ def reference_cuda_kernel_time(cache, q, nb=256):
 
 
 def run_maintenance(args):
-    """`--workload cfg2`: the kernels that keep the packed cache within its budget, timed one by one.
+    """`--workload cfg2`: the loop that keeps the packed cache within its budget.
 
-    288 independent cache rows (36 layers x 8 KV heads) of 256 blocks, D = 128, g = 32: distortion
-    table from the rung-16 blocks, Lagrangian allocation at 4 bits/value with a power-law mass, and
-    packing of the dense blocks at the rungs the allocator chose.  One JSON line; `value` is blocks
-    packed per second by the pack kernel, `stages` holds the per-kernel times."""
+    288 independent cache rows (36 layers x 8 KV heads), D = 128, g = 32, in one paged pool.  Each row
+    starts with 192 blocks; a step appends ONE 64-token block to every row (packed at rung 16) and then
+    runs the distortion, allocator and demotion kernels, for 64 steps (192 -> 256 blocks), once per
+    budget in {2, 3, 4, 5} bits/value.  Mass per block follows a power law (exponent 1.2) over the
+    distance from the newest block plus 0.1 on block 0.  `value` is blocks demoted per second of the
+    whole loop (host bookkeeping and the one read-back per step included); `stages` holds the device
+    time of each kernel, and the two bulk passes the roofline is quoted on: all 288 x 256 blocks packed
+    from dense bf16 at the rungs the allocator chose (gkv_pack_blocks), and all of them demoted from
+    rung 16 to those rungs (gkv_paged_demote_blocks)."""
+    import numpy as np
     import torch
     from geodesia_kv_b200 import cuda_ext
     from geodesia_kv_b200.pack_layout import pack_cache
-    from geodesia_kv_b200.policies import allocate_rungs, block_distortion, hot_mask, LADDER as LAD
+    from geodesia_kv_b200.paged import PagedLayerCache, PagedPool
     if cuda_ext.get_ext() is None:
         raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    rows, nb, D = 288, 256, 128
+    small = args.workload == "cfg2-small"          # profiling-sized: a quarter of the rows, one budget
+    B, Hkv, nb0, nb1, D = (9 if small else 36), 8, 192, 256, 128
+    rows = B * Hkv
     gen = torch.Generator(device=dev).manual_seed(2000)
-    k = torch.randn(1, rows, nb * 64, D, device=dev, dtype=torch.bfloat16, generator=gen)
-    v = torch.randn(1, rows, nb * 64, D, device=dev, dtype=torch.bfloat16, generator=gen)
-    dist_blocks = torch.arange(nb, 0, -1, device=dev, dtype=torch.float32)          # distance from the newest block
-    mass = dist_blocks.pow(-1.2)
-    mass = (mass / mass.sum()).repeat(1, rows, 1).contiguous()
-    mass[..., 0] += 0.1
-    hot = hot_mask(nb, nb * 64 - 1).to(dev).expand(1, rows, nb).contiguous()
-    lv16 = torch.full((1, rows, nb), 16, dtype=torch.int32, device=dev)
+    k = torch.randn(B, Hkv, nb1 * 64, D, device=dev, dtype=torch.bfloat16, generator=gen)
+    v = torch.randn(B, Hkv, nb1 * 64, D, device=dev, dtype=torch.bfloat16, generator=gen)
+    pool = PagedPool(int(2.2 * 4 * k.numel()), D, GROUP, dev)
 
+    def mass_for(nb):
+        m = torch.arange(nb, 0, -1, device=dev, dtype=torch.float32).pow(-1.2)
+        m = (m / m.sum()).repeat(rows, 1).contiguous()
+        m[:, 0] += 0.1
+        return m
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    per_budget, dev_us = {}, {"append_block": [], "distortion_and_allocate": [], "demote": []}
+    total_demoted, total_wall = 0, 0.0
+    budgets = (4.0,) if small else (2.0, 3.0, 4.0, 5.0)
+    for budget in budgets:
+        layer = PagedLayerCache(pool, B, Hkv, cap_blocks=nb1 + 1)
+        layer.extend(k[:, :, :nb0 * 64], v[:, :, :nb0 * 64])
+        layer.maintain(budget, mass=mass_for(nb0))
+        torch.cuda.synchronize()
+        marks, demoted = [], 0
+        t0 = time.perf_counter()
+        for nb in range(nb0 + 1, nb1 + 1):
+            e0 = ev()
+            layer.extend(k[:, :, (nb - 1) * 64:nb * 64], v[:, :, (nb - 1) * 64:nb * 64])
+            e1 = ev()
+            tgt = layer.plan_demotion(budget, mass=mass_for(nb))
+            e2 = ev()
+            tgt_h = tgt.cpu().numpy()                      # the one read-back of the step
+            e3 = ev()
+            demoted += layer.apply_demotion(tgt_h)
+            e4 = ev()
+            marks.append((e0, e1, e2, e3, e4))
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        for e0, e1, e2, e3, e4 in marks:
+            dev_us["append_block"].append(e0.elapsed_time(e1) * 1e3)
+            dev_us["distortion_and_allocate"].append(e1.elapsed_time(e2) * 1e3)
+            dev_us["demote"].append(e3.elapsed_time(e4) * 1e3)
+        per_budget[str(budget)] = {"us_per_step": wall / (nb1 - nb0) * 1e6, "blocks_demoted": demoted,
+                                   "bits_per_value": layer.bits_per_value(), "pool_bytes_in_use": pool.bytes_in_use,
+                                   "dense_bf16_bytes": rows * nb1 * 4 * 64 * D}
+        total_demoted += demoted
+        total_wall += wall
+        layer.release()
+
+    # ---- the two bulk passes the roofline is quoted on -----------------------------------------------
     def timed(fn, reps):
         for _ in range(3):
             out = fn()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+        e0 = ev()
         for _ in range(reps):
             out = fn()
-        e1.record()
+        e1 = ev()
         torch.cuda.synchronize()
         return out, e0.elapsed_time(e1) / reps * 1e3          # microseconds
 
     reps = max(args.steps, 5)
-    c16, us_pack16 = timed(lambda: pack_cache(k, v, lv16, GROUP), reps)
-    E, us_dist = timed(lambda: block_distortion(c16), reps)
-    idx0 = torch.zeros(1, rows, nb, dtype=torch.int32, device=dev)
-    tgt, us_alloc = timed(lambda: allocate_rungs(mass, E, idx0, hot, 4.0, 64, D, GROUP), reps)
-    level = torch.tensor(LAD, dtype=torch.int32, device=dev)[tgt.long()]
+    layer = PagedLayerCache(pool, B, Hkv, cap_blocks=nb1 + 1)
+    layer.extend(k, v)
+    tgt = layer.plan_demotion(4.0, mass=mass_for(nb1))
+    level = torch.tensor(LADDER, dtype=torch.int32, device=dev)[tgt.long()].view(B, Hkv, nb1)
     cmix, us_pack = timed(lambda: pack_cache(k, v, level, GROUP), reps)
+    lv16 = torch.full((B, Hkv, nb1), 16, dtype=torch.int32, device=dev)
+    _, us_pack16 = timed(lambda: pack_cache(k, v, lv16, GROUP), reps)
+    # demotion of every block from rung 16 to its allocated rung, into fresh slots of the same pool
+    lvn = level.reshape(-1).cpu().numpy()
+    off_old = layer.offs_h[:, :nb1].reshape(-1)
+    off_new = off_old.copy()
+    for rung in LADDER[1:]:
+        sel = np.nonzero(lvn == rung)[0]
+        off_new[sel] = pool.alloc(rung, sel.size)
+    up = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dev).to(dt)
+    oo, on = up(off_old, torch.int64), up(off_new, torch.int64)
+    lo, ln = torch.full((rows * nb1,), 16, dtype=torch.int32, device=dev), up(lvn, torch.int32)
+    lib = cuda_ext.get_ext().lib
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def demote_all():
+        rc = lib.gkv_paged_demote_blocks(pool.data.data_ptr(), oo.data_ptr(), lo.data_ptr(), pool.data.data_ptr(),
+                                         on.data_ptr(), ln.data_ptr(), None, None, rows * nb1, D, 64, GROUP, stream)
+        assert rc == 0
+    _, us_demote = timed(demote_all, reps)
+    moved = int((lvn != 16).sum())
+    out_bytes = sum(int((lvn == r).sum()) * pool.slot[r] for r in LADDER[1:])
     dense_bytes = 2 * k.numel() * 2
-    out_bytes = lambda c: int(c.algorithmic_bytes())
     peak, peak_kind = measured_peak_gbs()
-    blocks = rows * nb
     gbs = lambda b, us: b / us / 1e3
+    mean = lambda xs: float(sum(xs) / max(len(xs), 1))
     stages = {
-        "pack_rung16": {"us": us_pack16, "GB/s": gbs(dense_bytes + out_bytes(c16), us_pack16)},
-        "distortion_table": {"us": us_dist, "GB/s": gbs(out_bytes(c16), us_dist)},
-        "allocate_288_rows": {"us": us_alloc},
-        "pack_allocated_rungs": {"us": us_pack, "GB/s": gbs(dense_bytes + out_bytes(cmix), us_pack),
-                                 "bits_per_value": float(cmix.algorithmic_bytes() * 8 / (2 * blocks * 64 * D))},
+        "loop_device_us_per_step": {name: mean(xs) for name, xs in dev_us.items()},
+        "loop_per_budget": per_budget,
+        "bulk_pack_rung16": {"us": us_pack16, "GB/s": gbs(2 * dense_bytes, us_pack16)},
+        "bulk_pack_allocated_rungs": {"us": us_pack, "GB/s": gbs(dense_bytes + int(cmix.algorithmic_bytes()), us_pack),
+                                      "bits_per_value": float(cmix.algorithmic_bytes() * 8 / (2 * rows * nb1 * 64 * D))},
+        "bulk_demote_16_to_allocated": {"us": us_demote, "blocks": moved, "GB/s": gbs(moved * 32768 + out_bytes, us_demote)},
     }
-    line = {"metric": "packed_kv_pack_blocks_per_s", "value": blocks / (us_pack / 1e6), "unit": "blocks/s", "n_gpus": 1,
-            "steps": reps, "warmup": 3, "ms_per_step": us_pack / 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16 in, u8 codes + fp16 scales out", "data": "synthetic",
-            "config": {"workload": "cache maintenance: 288 rows x 256 blocks, D=128, g=32, budget 4 bits/value",
-                       "l2": "2.4 GB of dense K/V, larger than L2"},
-            "stages": stages, "gpu_launches": reps,
-            "roofline": {"bound": "hbm", "achieved": stages["pack_allocated_rungs"]["GB/s"], "peak": peak, "unit": "GB/s",
-                         "frac": stages["pack_allocated_rungs"]["GB/s"] / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
-                         "kernel": "pack_blocks (dense bf16 in + packed bytes and scales out)"}}
+    frac_pack = stages["bulk_pack_allocated_rungs"]["GB/s"] / peak
+    line = {"metric": "packed_kv_maintenance_blocks_demoted_per_s", "value": total_demoted / total_wall, "unit": "blocks/s",
+            "n_gpus": 1, "steps": len(budgets) * (nb1 - nb0), "warmup": 3,
+            "ms_per_step": total_wall / (len(budgets) * (nb1 - nb0)) * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 in, u8 codes + fp16 scales out", "data": "synthetic",
+            "config": {"workload": f"cache maintenance: {rows} rows ({B} layers x 8 KV heads) growing 192 -> 256 blocks one block per "
+                                   f"step, budgets {'/'.join(str(b) for b in budgets)} bits/value, D=128, g=32, paged pool",
+                       "l2": "bulk passes stream 2.4 GB of dense K/V, larger than L2; the loop's steps are latency-bound"},
+            "stages": stages, "gpu_launches": len(budgets) * (nb1 - nb0) * 4 + 3 * reps,
+            "roofline": {"bound": "hbm", "achieved": stages["bulk_pack_allocated_rungs"]["GB/s"], "peak": peak, "unit": "GB/s",
+                         "frac": frac_pack, "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "kernel": "pack_rows_fast_kernel (dense bf16 in + packed bytes and scales out)",
+                         "demote_kernel": {"achieved": stages["bulk_demote_16_to_allocated"]["GB/s"],
+                                           "frac": stages["bulk_demote_16_to_allocated"]["GB/s"] / peak,
+                                           "kernel": "paged_demote_kernel (rung-16 bytes in + packed bytes and scales out)"}}}
     print(json.dumps(line), flush=True)
 
 
@@ -552,7 +858,15 @@ def run_reference(args):
     import gkv_oracle
     gkv_oracle.build()
     gkv_oracle.set_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every core
-    w = WORKLOADS[args.workload or "cfg1"]
+    paged = args.workload in PAGED
+    if paged:
+        # the ragged batch is sampled as sequences of the mean length at the rung mix the allocator produced
+        pw = PAGED[args.workload]
+        mean_len = int(lognormal_lengths(pw).mean()) // 64 * 64
+        w = dict(layers=pw["layers"], Hq=pw["Hq"], Hkv=pw["Hkv"], D=pw["D"], B=pw["seqs"], T=mean_len,
+                 probs=PAGED_RUNG_MIX, name=pw["name"])
+    else:
+        w = WORKLOADS[args.workload or "cfg1"]
     nb_full = w["T"] // 64
     # bounded sample: a few sequences (enough cache rows to occupy every host thread), ONE layer, at
     # most 256 blocks per head (the per-sequence block count of the 16k configs); packed on the CPU
@@ -588,16 +902,20 @@ def run_reference(args):
     # layers, i.e. the context-tokens/s a full step would run at if every layer cost what the sample did.
     value = (nseq * nb * 64) / (dt * w["layers"])
     frac = (nseq * nb) / (w["B"] * nb_full * w["layers"])
+    metric, unit = METRIC, UNIT
+    if paged:          # decode tokens/s: one token per sequence and step; a step costs layers x (B / nseq) samples
+        metric, unit = "paged_kv_decode_tokens_per_s", "tokens/s"
+        value = w["B"] / (dt * w["layers"] * (w["B"] / nseq) * (nb_full / nb))
     sample = (f"each timed step is {nseq} sequence(s) x 1 layer x {nb} blocks ({nb * 64} tokens each), all {w['Hkv']} KV heads "
               f"= {frac:.5f} of a full step of the workload; value = sample tokens / time / {w['layers']} layers")
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3, "sample_fraction_of_step": frac,
             "higher_is_better": True, "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "fp64 accumulate (C oracle)",
             "data": "synthetic",
             "config": workload_config(w, args.gpus, split),
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": gkv_oracle.num_threads(), "kind": "port",
+            "cpu_baseline": {"value": value, "unit": unit, "cores": gkv_oracle.num_threads(), "kind": "port",
                              "sample": sample},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference has no CPU kernel for this path and its Python cannot travel; this is the C "
                     "restatement of its algorithm (oracle/gkv_oracle.c) on all host threads"}
     print(json.dumps(line), flush=True)
@@ -608,13 +926,13 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["cfg2"],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(PAGED) + ["cfg2", "cfg2-small"],
                     help="one workload only; default: cfg1 with cfg3 under its own key")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time plain launches instead of a CUDA graph of the step")
     args = ap.parse_args()
-    if args.workload == "cfg2":
+    if args.workload in ("cfg2", "cfg2-small"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the cache-maintenance workload has no reference arm; use the default workload"}))
         elif int(os.environ.get("RANK", "0")) == 0:

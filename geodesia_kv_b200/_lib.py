@@ -42,6 +42,7 @@ SIGNATURES = {
     "gkv_pack_blocks": (_i, [_vp, _vp, _i, _vp, _vp] + [_vp] * 4 + [_vp, _vp] + [_i] * 7 + [_i64, _i, _vp]),
     "gkv_demote_blocks": (_i, [_vp] * 6 + [_vp] * 4 + [_i] * 5 + [_i64, _i64, _i, _vp]),
     "gkv_unpack_blocks": (_i, [_vp] * 7 + [_vp, _vp] + [_i] * 5 + [_i64, _i, _vp]),
+    "gkv_maintenance_status": (_i, [C.POINTER(_i)]),
     "gkv_paged_block_bytes": (_sz, [_i, _i, _i]),
     "gkv_paged_pack_blocks": (_i, [_vp, _vp, _i, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 4 + [_vp]),
     "gkv_paged_demote_blocks": (_i, [_vp] * 8 + [_i] * 4 + [_vp]),

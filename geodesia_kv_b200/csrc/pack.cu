@@ -184,6 +184,7 @@ struct PackParams {
     const int32_t* level; const int32_t* valid;
     int nb, b_lo, D, group, G, gv, per_row_meta;
     int64_t stride_bh;
+    int nbx;                // blocks per row handled by this launch (b_hi - b_lo)
 };
 
 __device__ __forceinline__ float load_src(const void* p, int dtype, size_t i) {
@@ -300,56 +301,11 @@ __global__ void __launch_bounds__(kPackThreads) unpack_blocks_kernel(UnpackParam
 }
 
 
-// ---- register-resident kernels (requantise.cuh) --------------------------------------------------
 // Scale planes of a block of the paged pool: right behind the block's bytes.
 __device__ __forceinline__ void scales_behind(const uint8_t* blk, int lv, int D, int G, int gv, const __half*& klo,
                                               const __half*& kstep, const __half*& vlo, const __half*& vstep) {
     const __half* base = reinterpret_cast<const __half*>(blk + 2 * half_bytes(lv, D));
     klo = base; kstep = klo + G * D; vlo = kstep + G * D; vstep = vlo + kP * gv;
-}
-
-template <int D>
-__global__ void __launch_bounds__(rq::kThreads, 2) pack_rows_fast_kernel(PackParams p) {
-    __shared__ rq::Shared sm;
-    const int blk = p.b_lo + blockIdx.x, row = blockIdx.y;
-    const int mrow = p.per_row_meta ? row : 0;
-    const int lv = p.level[(size_t)mrow * p.nb + blk];
-    if (!level_ok(lv)) return;
-    int nvalid = p.valid ? p.valid[(size_t)mrow * p.nb + blk] : kP;
-    nvalid = max(1, min(nvalid, kP));
-    const size_t src0 = ((size_t)row * p.nb + blk) * kP * D;
-    const size_t esz = p.src_dtype == 0 ? 4 : 2;
-    rq::Job j;
-    j.src_kind = p.src_dtype; j.src_stride = D; j.nvalid = nvalid;
-    j.ksrc = static_cast<const uint8_t*>(p.k) + src0 * esz;
-    j.vsrc = static_cast<const uint8_t*>(p.v) + src0 * esz;
-    j.old_blk = nullptr; j.old_level = 0; j.oklo = j.okstep = j.ovlo = j.ovstep = nullptr;
-    j.dst = p.data + (size_t)row * p.stride_bh + p.offs[(size_t)mrow * p.nb + blk];
-    j.level = lv; j.group = p.group; j.ek = j.ev = nullptr; j.zero_scales = 1;
-    const size_t sb = (size_t)row * p.nb + blk;
-    j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
-    j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
-    rq::requantise<D>(j, sm);
-}
-
-template <int D>
-__global__ void __launch_bounds__(rq::kThreads, 2) demote_rows_fast_kernel(DemoteParams p) {
-    __shared__ rq::Shared sm;
-    const int blk = blockIdx.x, row = blockIdx.y;
-    const int mrow = p.per_row_meta ? row : 0;
-    const size_t mi = (size_t)mrow * p.nb + blk;
-    const int lo = p.level_old[mi], ln = p.level_new[mi];
-    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo) return;   // never promote
-    const size_t sb = (size_t)row * p.nb + blk;
-    rq::Job j;
-    j.src_kind = 3; j.ksrc = j.vsrc = nullptr; j.src_stride = 0; j.nvalid = kP;
-    j.old_blk = p.data_old + (size_t)row * p.stride_old + p.offs_old[mi]; j.old_level = lo;
-    j.klo = p.klo + sb * p.G * D; j.kstep = p.kstep + sb * p.G * D;
-    j.vlo = p.vlo + sb * kP * p.gv; j.vstep = p.vstep + sb * kP * p.gv;
-    j.oklo = j.klo; j.okstep = j.kstep; j.ovlo = j.vlo; j.ovstep = j.vstep;     // rewritten in place
-    j.dst = p.data_new + (size_t)row * p.stride_new + p.offs_new[mi];
-    j.level = ln; j.group = p.group; j.ek = j.ev = nullptr; j.zero_scales = 1;
-    rq::requantise<D>(j, sm);
 }
 
 struct PagedPackParams {
@@ -360,29 +316,6 @@ struct PagedPackParams {
     int group, G, gv;
 };
 
-template <int D>
-__global__ void __launch_bounds__(rq::kThreads, 2) paged_pack_kernel(PagedPackParams p) {
-    __shared__ rq::Shared sm;
-    const int i = blockIdx.x;
-    const int lv = p.level[i];
-    const int64_t off = p.dst_off[i];
-    if (!level_ok(lv) || off < 0) return;
-    const size_t esz = p.src_dtype == 0 ? 4 : 2;
-    rq::Job j;
-    j.src_kind = p.src_dtype; j.src_stride = p.token_stride;
-    j.nvalid = p.nvalid ? max(1, min(p.nvalid[i], kP)) : kP;
-    j.ksrc = static_cast<const uint8_t*>(p.k) + (size_t)p.src_off[i] * esz;
-    j.vsrc = static_cast<const uint8_t*>(p.v) + (size_t)p.src_off[i] * esz;
-    j.old_blk = nullptr; j.old_level = 0; j.oklo = j.okstep = j.ovlo = j.ovstep = nullptr;
-    j.dst = p.pool + off; j.level = lv; j.group = p.group; j.zero_scales = 0;
-    j.ek = p.ek ? p.ek + i : nullptr; j.ev = p.ev ? p.ev + i : nullptr;
-    const __half *a, *b, *c, *d;
-    scales_behind(j.dst, lv, D, p.G, p.gv, a, b, c, d);
-    j.klo = const_cast<__half*>(a); j.kstep = const_cast<__half*>(b);
-    j.vlo = const_cast<__half*>(c); j.vstep = const_cast<__half*>(d);
-    rq::requantise<D>(j, sm);
-}
-
 struct PagedDemoteParams {
     const uint8_t* pool_old; uint8_t* pool_new;
     const int64_t* off_old; const int32_t* level_old;
@@ -390,26 +323,6 @@ struct PagedDemoteParams {
     float* ek; float* ev;
     int group, G, gv;
 };
-
-template <int D>
-__global__ void __launch_bounds__(rq::kThreads, 2) paged_demote_kernel(PagedDemoteParams p) {
-    __shared__ rq::Shared sm;
-    const int i = blockIdx.x;
-    const int lo = p.level_old[i], ln = p.level_new[i];
-    const int64_t oo = p.off_old[i], on = p.off_new[i];
-    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo || oo < 0 || on < 0) return;   // never promote
-    rq::Job j;
-    j.src_kind = 3; j.ksrc = j.vsrc = nullptr; j.src_stride = 0; j.nvalid = kP;
-    j.old_blk = p.pool_old + oo; j.old_level = lo;
-    scales_behind(j.old_blk, lo, D, p.G, p.gv, j.oklo, j.okstep, j.ovlo, j.ovstep);
-    j.dst = p.pool_new + on; j.level = ln; j.group = p.group; j.zero_scales = 0;
-    j.ek = p.ek ? p.ek + i : nullptr; j.ev = p.ev ? p.ev + i : nullptr;
-    const __half *a, *b, *c, *d;
-    scales_behind(j.dst, ln, D, p.G, p.gv, a, b, c, d);
-    j.klo = const_cast<__half*>(a); j.kstep = const_cast<__half*>(b);
-    j.vlo = const_cast<__half*>(c); j.vstep = const_cast<__half*>(d);
-    rq::requantise<D>(j, sm);
-}
 
 struct PagedUnpackParams {
     const uint8_t* pool; const int64_t* offs; const int32_t* level; float* k_out; float* v_out;
@@ -459,6 +372,309 @@ __global__ void paged_append_kernel(AppendParams p) {
     }
 }
 
+
+// ---- persistent, bulk-copy-fed kernels ---------------------------------------------------------------
+// The kernels above start a CTA per block: the CTA reads the block's table entries, then its bytes, then
+// computes, then stores — a chain of dependent memory round trips that two resident CTAs per SM cannot
+// hide.  Here CTAs are persistent (two per SM); thread 0 looks up block i + 2*grid and starts ONE bulk
+// copy per contiguous piece of its source (K rows, V rows; or the packed block and its scale planes)
+// into a two-stage ring in shared memory while all threads work on block i out of the other stage, so
+// every global-memory latency is overlapped with arithmetic.  Sources that a bulk copy cannot take
+// (fp32 rows, a token stride other than D, an address that is not 16-byte aligned) are processed
+// straight from global memory by the same CTA.
+namespace st {
+
+constexpr int kStages = 2;
+constexpr int kTileBytes = 2 * kP * 128 * 2;          // the largest block: rung 16 at D = 128
+constexpr int kScaleBytes = 4 * 4 * 128 * 2;          // four planes of at most (4, 128) fp16
+constexpr int kStageBytes = kTileBytes + kScaleBytes;
+constexpr unsigned long long kWaitNs = 2000000000ull; // a copy that has not landed after 2 s never will
+
+struct Desc {
+    int skip, staged, src_kind, nvalid, old_level, level, zero_scales, pad;
+    const void* ksrc; const void* vsrc; long long src_stride;
+    const uint8_t* old_blk; const __half* oklo; const __half* okstep; const __half* ovlo; const __half* ovstep;
+    uint8_t* dst; __half* klo; __half* kstep; __half* vlo; __half* vstep; float* ek; float* ev;
+};
+
+struct __align__(128) Smem {
+    rq::Shared work;
+    Desc desc[kStages];
+    unsigned long long full[kStages];
+    __align__(128) uint8_t stage[kStages][kStageBytes];
+};
+
+__device__ int g_status;        // set when a wait on a bulk copy ran out
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(unsigned long long* b, int n) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n));
+}
+__device__ __forceinline__ void bar_expect(unsigned long long* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(unsigned long long* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(unsigned long long* b, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(s32(b)), "r"(parity), "r"(2000u) : "memory");
+        if (ok) return true;
+        if ((spin & 63u) == 63u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitNs) return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk(void* dst, const void* src, uint32_t bytes, unsigned long long* b) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---- what block i of each kind of launch is ----------------------------------------------------------
+__device__ __forceinline__ void clear(Desc& d) {
+    d.skip = 0; d.staged = 0; d.src_kind = 0; d.nvalid = kP; d.old_level = 0; d.level = 0; d.zero_scales = 0; d.pad = 0;
+    d.ksrc = d.vsrc = nullptr; d.src_stride = 0; d.old_blk = nullptr; d.oklo = d.okstep = d.ovlo = d.ovstep = nullptr;
+    d.dst = nullptr; d.klo = d.kstep = d.vlo = d.vstep = nullptr; d.ek = d.ev = nullptr;
+}
+
+template <int D>
+__device__ void describe(const PackParams& p, int i, Desc& d) {
+    clear(d);
+    const int row = i / p.nbx, blk = p.b_lo + (i - row * p.nbx);
+    const int mrow = p.per_row_meta ? row : 0;
+    const size_t mi = (size_t)mrow * p.nb + blk;
+    const int lv = p.level[mi];
+    if (!level_ok(lv)) { d.skip = 1; return; }
+    const size_t src0 = ((size_t)row * p.nb + blk) * kP * D, esz = p.src_dtype == 0 ? 4 : 2;
+    d.src_kind = p.src_dtype; d.src_stride = D;
+    d.nvalid = max(1, min(p.valid ? p.valid[mi] : kP, kP));
+    d.ksrc = static_cast<const uint8_t*>(p.k) + src0 * esz;
+    d.vsrc = static_cast<const uint8_t*>(p.v) + src0 * esz;
+    d.dst = p.data + (size_t)row * p.stride_bh + p.offs[mi];
+    d.level = lv; d.zero_scales = 1;
+    const size_t sb = (size_t)row * p.nb + blk;
+    d.klo = p.klo + sb * p.G * D; d.kstep = p.kstep + sb * p.G * D;
+    d.vlo = p.vlo + sb * kP * p.gv; d.vstep = p.vstep + sb * kP * p.gv;
+}
+
+template <int D>
+__device__ void describe(const DemoteParams& p, int i, Desc& d) {
+    clear(d);
+    const int row = i / p.nb, blk = i - row * p.nb;
+    const int mrow = p.per_row_meta ? row : 0;
+    const size_t mi = (size_t)mrow * p.nb + blk;
+    const int lo = p.level_old[mi], ln = p.level_new[mi];
+    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo) { d.skip = 1; return; }   // never promote
+    const size_t sb = (size_t)row * p.nb + blk;
+    d.src_kind = 3; d.old_level = lo;
+    d.old_blk = p.data_old + (size_t)row * p.stride_old + p.offs_old[mi];
+    d.klo = p.klo + sb * p.G * D; d.kstep = p.kstep + sb * p.G * D;
+    d.vlo = p.vlo + sb * kP * p.gv; d.vstep = p.vstep + sb * kP * p.gv;
+    d.oklo = d.klo; d.okstep = d.kstep; d.ovlo = d.vlo; d.ovstep = d.vstep;           // rewritten in place
+    d.dst = p.data_new + (size_t)row * p.stride_new + p.offs_new[mi];
+    d.level = ln; d.zero_scales = 1;
+}
+
+template <int D>
+__device__ void describe(const PagedPackParams& p, int i, Desc& d) {
+    clear(d);
+    const int lv = p.level[i];
+    const int64_t off = p.dst_off[i];
+    if (!level_ok(lv) || off < 0) { d.skip = 1; return; }
+    const size_t esz = p.src_dtype == 0 ? 4 : 2;
+    d.src_kind = p.src_dtype; d.src_stride = p.token_stride;
+    d.nvalid = p.nvalid ? max(1, min(p.nvalid[i], kP)) : kP;
+    d.ksrc = static_cast<const uint8_t*>(p.k) + (size_t)p.src_off[i] * esz;
+    d.vsrc = static_cast<const uint8_t*>(p.v) + (size_t)p.src_off[i] * esz;
+    d.dst = p.pool + off; d.level = lv;
+    d.ek = p.ek ? p.ek + i : nullptr; d.ev = p.ev ? p.ev + i : nullptr;
+    const __half *a, *b, *c, *e;
+    scales_behind(d.dst, lv, D, p.G, p.gv, a, b, c, e);
+    d.klo = const_cast<__half*>(a); d.kstep = const_cast<__half*>(b);
+    d.vlo = const_cast<__half*>(c); d.vstep = const_cast<__half*>(e);
+}
+
+template <int D>
+__device__ void describe(const PagedDemoteParams& p, int i, Desc& d) {
+    clear(d);
+    const int lo = p.level_old[i], ln = p.level_new[i];
+    const int64_t oo = p.off_old[i], on = p.off_new[i];
+    if (lo == ln || !level_ok(lo) || !level_ok(ln) || ln > lo || oo < 0 || on < 0) { d.skip = 1; return; }
+    d.src_kind = 3; d.old_level = lo; d.old_blk = p.pool_old + oo;
+    scales_behind(d.old_blk, lo, D, p.G, p.gv, d.oklo, d.okstep, d.ovlo, d.ovstep);
+    d.dst = p.pool_new + on; d.level = ln;
+    d.ek = p.ek ? p.ek + i : nullptr; d.ev = p.ev ? p.ev + i : nullptr;
+    const __half *a, *b, *c, *e;
+    scales_behind(d.dst, ln, D, p.G, p.gv, a, b, c, e);
+    d.klo = const_cast<__half*>(a); d.kstep = const_cast<__half*>(b);
+    d.vlo = const_cast<__half*>(c); d.vstep = const_cast<__half*>(e);
+}
+
+// Thread 0: look block i up and start its copies into a stage; a source the copy engine cannot take
+// (a token stride other than D, an address that is not 16-byte aligned) is left for all threads to
+// copy by hand when the block's turn comes.
+template <int D, class P>
+__device__ void fetch(const P& p, int i, int n, Smem& sm, int s, int G, int gv) {
+    Desc d;
+    if (i >= n) { clear(d); d.skip = 2; sm.desc[s] = d; bar_arrive(&sm.full[s]); return; }
+    describe<D>(p, i, d);
+    uint8_t* st = sm.stage[s];
+    if (!d.skip) {
+        if (d.src_kind != 3 && d.src_stride == D && al16(d.ksrc) && al16(d.vsrc)) {
+            const uint32_t bytes = (uint32_t)d.nvalid * D * 2;
+            d.staged = 1;
+            sm.desc[s] = d;
+            bar_expect(&sm.full[s], 2 * bytes);
+            bulk(st, d.ksrc, bytes, &sm.full[s]);
+            bulk(st + kP * D * 2, d.vsrc, bytes, &sm.full[s]);
+            return;
+        }
+        if (d.src_kind == 3) {
+            const bool q = d.old_level == 8 || d.old_level == 4 || d.old_level == 2;
+            const uint32_t bytes = 2u * (uint32_t)half_bytes(d.old_level, D), ks = (uint32_t)G * D * 2, vs = (uint32_t)kP * gv * 2;
+            if (al16(d.old_blk) && (!q || (al16(d.oklo) && al16(d.okstep) && al16(d.ovlo) && al16(d.ovstep) && ks % 16 == 0 && vs % 16 == 0))) {
+                d.staged = 1;
+                sm.desc[s] = d;
+                bar_expect(&sm.full[s], bytes + (q ? 2 * ks + 2 * vs : 0u));
+                bulk(st, d.old_blk, bytes, &sm.full[s]);
+                if (q) {
+                    uint8_t* sc = st + kTileBytes;
+                    bulk(sc, d.oklo, ks, &sm.full[s]);
+                    bulk(sc + ks, d.okstep, ks, &sm.full[s]);
+                    bulk(sc + 2 * ks, d.ovlo, vs, &sm.full[s]);
+                    bulk(sc + 2 * ks + vs, d.ovstep, vs, &sm.full[s]);
+                }
+                return;
+            }
+        }
+    }
+    sm.desc[s] = d;
+    bar_arrive(&sm.full[s]);
+}
+
+// All threads: bring a block the copy engine could not take into the stage, in the same layout.
+template <int D>
+__device__ void copy_by_hand(const Desc& d, uint8_t* st, int G, int gv) {
+    const int tid = threadIdx.x;
+    if (d.src_kind != 3) {
+        const uint16_t* ks = static_cast<const uint16_t*>(d.ksrc);
+        const uint16_t* vs = static_cast<const uint16_t*>(d.vsrc);
+        uint16_t* kd = reinterpret_cast<uint16_t*>(st);
+        uint16_t* vd = kd + kP * D;
+        for (int e = tid; e < d.nvalid * D; e += rq::kThreads) {
+            const int t = e / D, c = e - t * D;
+            kd[e] = ks[(size_t)t * d.src_stride + c];
+            vd[e] = vs[(size_t)t * d.src_stride + c];
+        }
+        return;
+    }
+    const int bytes = 2 * half_bytes(d.old_level, D);
+    for (int e = tid; e < bytes; e += rq::kThreads) st[e] = d.old_blk[e];
+    if (d.old_level == 8 || d.old_level == 4 || d.old_level == 2) {
+        __half* sc = reinterpret_cast<__half*>(st + kTileBytes);
+        for (int e = tid; e < G * D; e += rq::kThreads) { sc[e] = d.oklo[e]; sc[G * D + e] = d.okstep[e]; }
+        for (int e = tid; e < kP * gv; e += rq::kThreads) { sc[2 * G * D + e] = d.ovlo[e]; sc[2 * G * D + kP * gv + e] = d.ovstep[e]; }
+    }
+}
+
+template <int D, class P>
+__global__ void __launch_bounds__(rq::kThreads, 2) staged_kernel(P p, int n, int group) {
+    extern __shared__ __align__(128) uint8_t raw[];
+    Smem& sm = *reinterpret_cast<Smem*>(raw);
+    const int tid = threadIdx.x;
+    const int kg = min(group, kP), vg = min(group, D);
+    const int G = kP / kg, gv = D / vg;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) bar_init(&sm.full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0)
+        for (int s = 0; s < kStages; ++s) fetch<D>(p, (int)blockIdx.x + s * (int)gridDim.x, n, sm, s, G, gv);
+    for (int it = 0;; ++it) {
+        const int s = it % kStages;
+        const bool ok = bar_wait(&sm.full[s], (uint32_t)(it / kStages) & 1u);
+        if (!__syncthreads_and(ok)) {                  // a copy never landed: flag it and stop
+            if (tid == 0) atomicExch(&g_status, 1);
+            return;
+        }
+        const Desc& d = sm.desc[s];
+        if (d.skip == 2) return;                       // past the last block
+        if (!d.skip) {
+            uint8_t* st = sm.stage[s];
+            if (!d.staged) {
+                copy_by_hand<D>(d, st, G, gv);
+                __syncthreads();
+            }
+            rq::Job j;
+            j.src_kind = 0; j.ksrc = j.vsrc = nullptr; j.src_stride = 0; j.nvalid = kP; j.old_blk = nullptr; j.old_level = 0;
+            j.oklo = j.okstep = j.ovlo = j.ovstep = nullptr;
+            j.dst = d.dst; j.level = d.level; j.klo = d.klo; j.kstep = d.kstep; j.vlo = d.vlo; j.vstep = d.vstep;
+            j.zero_scales = d.zero_scales; j.ek = d.ek; j.ev = d.ev; j.group = group;
+            rq::StagedSrc src;
+            src.kgs = 31 - __clz(kg); src.vgs = 31 - __clz(vg); src.k = st; src.nvalid = d.nvalid; src.level = d.old_level;
+            if (d.src_kind != 3 || d.old_level == 16) {        // a rung-16 block is two bf16 tiles like dense rows
+                src.kind = d.src_kind == 2 ? 2 : 1;
+                src.v = st + kP * D * 2;
+            } else {
+                src.kind = 3;
+                src.v = st + half_bytes(d.old_level, D);
+            }
+            src.klo = reinterpret_cast<const __half*>(st + kTileBytes); src.kstep = src.klo + G * D;
+            src.vlo = src.kstep + G * D; src.vstep = src.vlo + kP * gv;
+            rq::requantise_staged<D>(src, j, sm.work);
+        }
+        __syncthreads();                               // the stage and the work area are free again
+        if (tid == 0) fetch<D>(p, (int)blockIdx.x + (it + kStages) * (int)gridDim.x, n, sm, s, G, gv);
+    }
+}
+
+// fp32 rows do not fit the stages: one CTA per block, straight from global memory.
+template <int D, class P>
+__global__ void __launch_bounds__(rq::kThreads, 2) direct_kernel(P p, int group) {
+    __shared__ rq::Shared sm;
+    Desc d;
+    describe<D>(p, (int)blockIdx.x, d);
+    if (d.skip) return;
+    rq::Job j;
+    j.src_kind = d.src_kind; j.ksrc = d.ksrc; j.vsrc = d.vsrc; j.src_stride = d.src_stride; j.nvalid = d.nvalid;
+    j.old_blk = d.old_blk; j.old_level = d.old_level; j.oklo = d.oklo; j.okstep = d.okstep; j.ovlo = d.ovlo; j.ovstep = d.ovstep;
+    j.dst = d.dst; j.level = d.level; j.klo = d.klo; j.kstep = d.kstep; j.vlo = d.vlo; j.vstep = d.vstep;
+    j.zero_scales = d.zero_scales; j.ek = d.ek; j.ev = d.ev; j.group = group;
+    rq::requantise<D, false>(j, sm);
+}
+
+template <int D, class P>
+static int launch(const P& p, int n, int group, bool fp32_rows, cudaStream_t stream) {
+    if (fp32_rows) {
+        direct_kernel<D, P><<<n, rq::kThreads, 0, stream>>>(p, group);
+        GKV_LAUNCH_CHECK();
+        return GKV_OK;
+    }
+    int dev = 0, sms = 0;
+    GKV_CUDA_TRY(cudaGetDevice(&dev));
+    GKV_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    GKV_CUDA_TRY(cudaFuncSetAttribute(staged_kernel<D, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+    const int grid = n < 2 * sms ? n : 2 * sms;
+    staged_kernel<D, P><<<grid, rq::kThreads, sizeof(Smem), stream>>>(p, n, group);
+    GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+template <class P>
+static int launch_d(const P& p, int n, int D, int group, bool fp32_rows, cudaStream_t stream) {
+    return D == 128 ? launch<128, P>(p, n, group, fp32_rows, stream) : launch<64, P>(p, n, group, fp32_rows, stream);
+}
+
+}  // namespace st
+
 static size_t tile_smem(int D) { return (size_t)kP * (2 * tile_ld(D) * sizeof(float) + D); }
 
 static int set_smem(const void* fn, size_t bytes) {
@@ -488,12 +704,8 @@ int gkv_pack_blocks(const void* k, const void* v, int src_dtype, uint8_t* data, 
     p.level = level; p.valid = valid; p.nb = nb; p.b_lo = b_lo; p.D = D; p.group = group;
     p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group; p.per_row_meta = meta_rows != 1;
     p.stride_bh = stride_bh;
-    if (rq::shape_ok(D, group)) {
-        if (D == 128) pack_rows_fast_kernel<128><<<dim3(b_hi - b_lo, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-        else pack_rows_fast_kernel<64><<<dim3(b_hi - b_lo, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-        GKV_LAUNCH_CHECK();
-        return GKV_OK;
-    }
+    p.nbx = b_hi - b_lo;
+    if (rq::shape_ok(D, group)) return st::launch_d(p, rows * (b_hi - b_lo), D, group, src_dtype == 0, (cudaStream_t)stream);
     int rc = set_smem((const void*)pack_blocks_kernel, tile_smem(kMaxD));
     if (rc) return rc;
     pack_blocks_kernel<<<dim3(b_hi - b_lo, rows), kPackThreads, tile_smem(D), (cudaStream_t)stream>>>(p);
@@ -519,12 +731,7 @@ int gkv_demote_blocks(const uint8_t* data_old, const int64_t* offs_old, const in
     p.klo = (__half*)klo; p.kstep = (__half*)kstep; p.vlo = (__half*)vlo; p.vstep = (__half*)vstep;
     p.nb = nb; p.D = D; p.group = group; p.G = (kP + group - 1) / group; p.gv = (D + group - 1) / group;
     p.per_row_meta = meta_rows != 1; p.stride_old = stride_old; p.stride_new = stride_new;
-    if (rq::shape_ok(D, group)) {
-        if (D == 128) demote_rows_fast_kernel<128><<<dim3(nb, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-        else demote_rows_fast_kernel<64><<<dim3(nb, rows), rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-        GKV_LAUNCH_CHECK();
-        return GKV_OK;
-    }
+    if (rq::shape_ok(D, group)) return st::launch_d(p, rows * nb, D, group, false, (cudaStream_t)stream);
     int rc = set_smem((const void*)demote_blocks_kernel, tile_smem(kMaxD));
     if (rc) return rc;
     demote_blocks_kernel<<<dim3(nb, rows), kPackThreads, tile_smem(D), (cudaStream_t)stream>>>(p);
@@ -573,10 +780,7 @@ int gkv_paged_pack_blocks(const void* k, const void* v, int src_dtype, const int
     p.k = k; p.v = v; p.src_dtype = src_dtype; p.src_off = src_off; p.token_stride = token_stride; p.nvalid = nvalid;
     p.pool = pool; p.dst_off = dst_off; p.level = level; p.ek = ek; p.ev = ev; p.group = group;
     p.G = kP / min(group, kP); p.gv = D / min(group, D);
-    if (D == 128) paged_pack_kernel<128><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-    else paged_pack_kernel<64><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-    GKV_LAUNCH_CHECK();
-    return GKV_OK;
+    return st::launch_d(p, n, D, group, src_dtype == 0, (cudaStream_t)stream);
 }
 
 int gkv_paged_demote_blocks(const uint8_t* pool_old, const int64_t* off_old, const int32_t* level_old,
@@ -592,10 +796,7 @@ int gkv_paged_demote_blocks(const uint8_t* pool_old, const int64_t* off_old, con
     p.pool_old = pool_old; p.pool_new = pool_new; p.off_old = off_old; p.level_old = level_old;
     p.off_new = off_new; p.level_new = level_new; p.ek = ek; p.ev = ev; p.group = group;
     p.G = kP / min(group, kP); p.gv = D / min(group, D);
-    if (D == 128) paged_demote_kernel<128><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-    else paged_demote_kernel<64><<<n, rq::kThreads, 0, (cudaStream_t)stream>>>(p);
-    GKV_LAUNCH_CHECK();
-    return GKV_OK;
+    return st::launch_d(p, n, D, group, false, (cudaStream_t)stream);
 }
 
 int gkv_paged_unpack_blocks(const uint8_t* pool, const int64_t* offs, const int32_t* level, float* k_out,
@@ -627,6 +828,12 @@ int gkv_paged_append_token(const void* k, const void* v, int src_dtype, uint8_t*
     p.status = status; p.cap = cap; p.D = D;
     paged_append_kernel<<<rows, D <= 64 ? 64 : 128, 0, (cudaStream_t)stream>>>(p);
     GKV_LAUNCH_CHECK();
+    return GKV_OK;
+}
+
+int gkv_maintenance_status(int* status_host) {
+    if (!status_host) return GKV_E_NULL;
+    GKV_CUDA_TRY(cudaMemcpyFromSymbol(status_host, gkv::st::g_status, sizeof(int)));
     return GKV_OK;
 }
 

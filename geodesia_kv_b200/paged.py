@@ -230,6 +230,36 @@ class PagedLayerCache:
         self.lens.copy_(torch.from_numpy(np.repeat(lengths, Hkv).astype(np.int32)), non_blocking=True)
         self.pack_blocks(k, v, src_off, D, nvalid, slots, np.full(total, 16, dtype=np.int32))
 
+    def extend(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Append whole blocks to EVERY sequence: k, v (B, Hkv, n*64, D) dense; all sequences must
+        stand at a block boundary (chunked prefill, or a serving loop that packs a block at a time)."""
+        B, Hkv, T, D = k.shape
+        if (B, Hkv, D) != (self.B, self.Hkv, self.D) or T % BLOCK or np.any(self.len_h % BLOCK):
+            raise ValueError("extend appends whole blocks to sequences that stand at a block boundary")
+        k, v = k.contiguous(), v.contiguous()
+        n = T // BLOCK
+        first = self.len_h // BLOCK
+        if int(first.max()) + n + 1 > self.cap:
+            self._grow(int(first.max()) + n + 1 + 63)
+        row_of = np.repeat(np.arange(self.rows), n)
+        blk_in = np.tile(np.arange(n), self.rows)
+        blk_of = np.repeat(first, Hkv * n) + blk_in
+        slots = self.offs_h[row_of, blk_of].copy()                      # slots reserved earlier are used first
+        fresh = np.nonzero(slots < 0)[0]
+        slots[fresh] = self.pool.alloc(16, fresh.size)
+        self.offs_h[row_of, blk_of] = slots
+        self.level_h[row_of, blk_of] = 16
+        flat = row_of * self.cap + blk_of
+        self._put(self.offs, flat, slots)
+        self._put(self.level, flat, np.full(flat.size, 16, dtype=np.int32))
+        self._put(self.valid, flat, np.full(flat.size, BLOCK, dtype=np.int32))
+        for t in (self.mass, self.ek, self.ev):
+            self._put(t, flat, np.zeros(flat.size, dtype=np.float32))
+        self.len_h += T
+        self.lens += T
+        self.pack_blocks(k, v, (row_of * T + blk_in * BLOCK) * D, D, np.full(flat.size, BLOCK, np.int32), slots,
+                         np.full(flat.size, 16, dtype=np.int32))
+
     def pack_blocks(self, k, v, src_off, token_stride, nvalid, slots, levels, radii: bool = False):
         """Quantise blocks from dense rows into given slots (element offsets into k and v)."""
         dev = self.device
@@ -248,24 +278,39 @@ class PagedLayerCache:
 
     def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
         """One more token for every sequence: k_new, v_new (B, Hkv, 1, D) or (B, Hkv, D)."""
-        starts = np.nonzero(self.len_h % BLOCK == 0)[0]                   # sequences that open a new block
-        if starts.size:
-            blk = self.len_h[starts] // BLOCK
-            if int(blk.max()) + 1 > self.cap:
-                self._grow(int(blk.max()) + 1 + 63)
-            rows = (starts[:, None] * self.Hkv + np.arange(self.Hkv)[None]).reshape(-1)
-            blks = np.repeat(blk, self.Hkv)
-            slots = self.pool.alloc(16, rows.size)
-            self.offs_h[rows, blks] = slots
-            self.level_h[rows, blks] = 16
-            flat = rows * self.cap + blks
-            self._put(self.offs, flat, slots)
-            self._put(self.level, flat, np.full(rows.size, 16, dtype=np.int32))
-            self._put(self.mass, flat, np.zeros(rows.size, dtype=np.float32))
-            self._put(self.ek, flat, np.zeros(rows.size, dtype=np.float32))
-            self._put(self.ev, flat, np.zeros(rows.size, dtype=np.float32))
+        if np.any(self.len_h % BLOCK == 0):                               # some sequence opens a new block
+            self.reserve(1)
         self.append_device(k_new, v_new)
         self.len_h += 1
+
+    def reserve(self, tokens: int) -> None:
+        """Give every row the rung-16 slots its next ``tokens`` appended tokens will need, so that that
+        many :meth:`append_device` calls (e.g. replays of a captured step) need no host work."""
+        first = (self.len_h + BLOCK - 1) // BLOCK                       # first block without a slot yet
+        last = (self.len_h + tokens + BLOCK - 1) // BLOCK               # one past the last block needed
+        cnt = np.maximum(last - first, 0)
+        if int(cnt.sum()) == 0:
+            return
+        if int(last.max()) + 1 > self.cap:
+            self._grow(int(last.max()) + 1 + 63)
+        seq = np.repeat(np.arange(self.B), cnt)
+        blk = np.arange(int(cnt.sum())) - np.repeat(np.cumsum(cnt) - cnt, cnt) + np.repeat(first, cnt)
+        rows = (seq[:, None] * self.Hkv + np.arange(self.Hkv)[None]).reshape(-1)
+        blks = np.repeat(blk, self.Hkv)
+        have = self.offs_h[rows, blks] >= 0
+        rows, blks = rows[~have], blks[~have]
+        slots = self.pool.alloc(16, rows.size)
+        self.offs_h[rows, blks] = slots
+        self.level_h[rows, blks] = 16
+        flat = rows * self.cap + blks
+        self._put(self.offs, flat, slots)
+        self._put(self.level, flat, np.full(rows.size, 16, dtype=np.int32))
+        for t in (self.mass, self.ek, self.ev):
+            self._put(t, flat, np.zeros(rows.size, dtype=np.float32))
+
+    def sync_lengths(self) -> None:
+        """Re-read the row lengths from the device (after append_device calls the host did not count)."""
+        self.len_h[:] = self.lens.cpu().numpy().reshape(self.B, self.Hkv)[:, 0]
 
     def append_device(self, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
         """The device half of :meth:`append` (no host bookkeeping): safe inside a CUDA graph as long

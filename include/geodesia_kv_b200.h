@@ -255,6 +255,11 @@ int gkv_unpack_blocks(const uint8_t *data, const int64_t *offs, const void *klo,
                       float *v_out, int rows, int nb, int D, int block, int group, int64_t stride_bh,
                       int meta_rows, void *stream);
 
+/* The pack and demote kernels wait, bounded (2 s), for their own bulk copies into shared memory; a
+ * wait that runs out makes the kernel set a device-side word and return instead of spinning.  This
+ * reads the word of the current device (0 = never happened); it synchronises.                  */
+int gkv_maintenance_status(int *status_host);
+
 /* ---- paged pool ----------------------------------------------------------------------
  * The reference's serving plugin keeps one cache object per sequence and frees nothing when a
  * block is demoted (vllm_plugin/kv_cache.py:15-104); its capacity claim (README.md:243-248) needs

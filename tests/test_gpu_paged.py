@@ -258,3 +258,63 @@ def test_tokens_appended_on_the_device_are_attended(oracle):
         layer.append_device(new_k[0], new_v[0])
     torch.cuda.synchronize()
     assert int(layer.status.item()) == 1
+
+
+@pytest.mark.parametrize("budget", [2.0, 3.0, 4.0, 5.0])
+def test_one_block_per_step_for_64_steps_against_the_oracle(oracle, budget):
+    """The maintenance scenario end to end on the packed cache: one 64-token block is appended to every
+    row per step for 64 steps, the distortion, allocator and demotion kernels run after each, and every
+    step is compared with the oracle — the rung of every block (bit-exact), the bytes and scale planes
+    of every block demoted in the step (bit-exact), monotone demotion (policies.py:810-908)."""
+    from geodesia_kv_b200 import policies
+    from geodesia_kv_b200.paged import PagedLayerCache, PagedPool
+    D, group, B, Hkv, nb0, steps = 128, 32, 2, 2, 8, 64
+    rows = B * Hkv
+    pool = PagedPool(192 << 20, D, group)
+    layer = PagedLayerCache(pool, B, Hkv)
+    gen = torch.Generator(device="cuda").manual_seed(int(2000 + budget))
+    k = torch.randn(B, Hkv, (nb0 + steps) * P, D, device="cuda", generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, (nb0 + steps) * P, D, device="cuda", generator=gen).to(torch.bfloat16)
+    kf = k.float().cpu().numpy().reshape(rows, nb0 + steps, P, D)
+    vf = v.float().cpu().numpy().reshape(rows, nb0 + steps, P, D)
+    bits = np.asarray(policies.ladder_bits(P, D, group), np.float32)
+    G, gv = P // group, D // group
+    layer.extend(k[:, :, :nb0 * P], v[:, :, :nb0 * P])
+    idx = np.zeros((rows, nb0), np.int32)
+    E_all = np.stack([oracle.distortion(kf[r], vf[r], group, 0.0) for r in range(rows)])
+    demoted_total = 0
+    for step in range(steps + 1):
+        nb = nb0 + step
+        if step:
+            layer.extend(k[:, :, (nb - 1) * P:nb * P], v[:, :, (nb - 1) * P:nb * P])
+            idx = np.concatenate([idx, np.zeros((rows, 1), np.int32)], 1)
+        mass = power_law_mass(layer)
+        tgt = layer.plan_demotion(budget, mass=mass).cpu().numpy()
+        hot = layer.hot_blocks(nb).cpu().numpy()
+        assert np.array_equal(hot[0], policies.hot_mask(nb, nb * P - 1, P, 4, 128).numpy().astype(np.uint8))
+        mh = mass.cpu().numpy()
+        for r in range(rows):
+            E = np.where((idx[r] == 0)[:, None], E_all[r, :nb], 0.0).astype(np.float32)   # demoted blocks carry a zero row
+            want, _ = oracle.allocate(mh[r], E, idx[r], hot[r], bits, budget * 2.0 * nb * P * D)
+            assert np.array_equal(tgt[r], want), (step, r)
+        assert (tgt >= idx).all() and np.array_equal(tgt[idx > 0], idx[idx > 0])
+        moved = np.argwhere(tgt > idx)
+        assert layer.apply_demotion(tgt) == len(moved)
+        demoted_total += len(moved)
+        if len(moved):
+            data = pool.data.cpu().numpy()
+            for r, b in moved:
+                lv = LADDER[tgt[r, b]]
+                want = oracle.pack_row(kf[r, b:b + 1], vf[r, b:b + 1], [lv], group)
+                o, nbytes = int(layer.offs_h[r, b]), oracle.block_bytes(lv, P, D)
+                assert int(layer.level_h[r, b]) == lv
+                assert np.array_equal(data[o:o + nbytes], want["data"]), (step, r, b, lv)
+                if lv in (8, 4, 2):
+                    s = data[o + nbytes:o + nbytes + 4 * (G * D + P * gv)].view(np.uint16)
+                    got = (s[:G * D], s[G * D:2 * G * D], s[2 * G * D:2 * G * D + P * gv], s[2 * G * D + P * gv:])
+                    for a, key in zip(got, ("klo", "kstep", "vlo", "vstep")):
+                        assert np.array_equal(a, want[key].reshape(-1)), (step, r, b, key)
+        idx = tgt
+        assert pool.bytes_in_use == layer.bytes_in_pool()
+    assert demoted_total >= rows * (steps - 4)
+    assert layer.bits_per_value() <= budget + 16.0 * 5 / (nb0 + steps) + 1e-6
