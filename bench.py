@@ -81,7 +81,7 @@ UNIT = "context-tokens/s"
 # its algorithmic bytes, from an ncu capture of the profiling-sized slice of each rung mix; the extra
 # bytes are the per-warp softmax records).  Traffic grows with the number of blocks, so a full-size
 # launch is that ratio times its own algorithmic bytes.
-DRAM_TRAFFIC_RATIO = {"cfg1": 1.067, "cfg1-small": 1.067}
+DRAM_TRAFFIC_RATIO = {"cfg1": 1.051, "cfg1-small": 1.051}
 
 
 def workload_config(w, world, split, cache_gb=None):
@@ -586,6 +586,144 @@ def measure_paged(wname, args, env):
     return line
 
 
+def measure_full_step(args, env):
+    """`--workload cfg1-full`: one FULL decode step of a Qwen3-8B-shaped model with random-init weights
+    (36 layers, hidden 4096, MLP 12288, 32 query / 8 KV heads of 128, vocabulary 151936 — the public
+    Qwen3-8B configuration) over the packed caches of the 16k-token workload, through the transformers
+    model with this library's cache and attention function plugged in.  Every rank holds the weights and
+    its own 32 sequences (no collective)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    from geodesia_kv_b200 import live_cache
+    from geodesia_kv_b200.paged import PagedLayerCache, PagedPool
+    rank, world, device = env["rank"], env["world"], env["device"]
+    w = WORKLOADS["cfg1"]
+    L, B, Hq, Hkv, D, T = w["layers"], w["B"], w["Hq"], w["Hkv"], w["D"], w["T"]
+    nb = T // 64
+    name = live_cache.register()
+    cfg = Qwen3Config(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=L,
+                      num_attention_heads=Hq, num_key_value_heads=Hkv, head_dim=D, max_position_embeddings=40960,
+                      rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    cfg._attn_implementation = name
+    torch.manual_seed(1234 + rank)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(device):
+            model = Qwen3ForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(prev)
+    model.config._attn_implementation = name
+    n_params = sum(p.numel() for p in model.parameters())
+    steps_ahead = 64 * (2 + (4 * (max(args.warmup, 3) + args.steps) + 16) // 64)
+    dense_layer = B * Hkv * T * D * 4
+    pool = PagedPool(int(L * dense_layer * 0.36 + 2 * dense_layer + L * B * Hkv * (steps_ahead // 64 + 1) * 32768 + (1 << 30)),
+                     D, GROUP, device)
+    cache = live_cache.PagedKVCache(num_layers=L, budget_bits=0.0, group=GROUP, pool=pool, maintain_every=0)
+    k = torch.empty(B, Hkv, T, D, device=device, dtype=torch.bfloat16)
+    v = torch.empty_like(k)
+    for layer in range(L):
+        gen = torch.Generator(device=device).manual_seed(1000 + layer + 100003 * rank)
+        k.normal_(generator=gen)
+        v.normal_(generator=gen)
+        pl = PagedLayerCache(pool, B, Hkv, cap_blocks=nb + steps_ahead // 64 + 2)
+        pl.extend(k, v)
+        level = draw_levels(1000 + layer + 100003 * rank, B, Hkv, nb, w["probs"]).view(B * Hkv, nb).numpy()
+        pl.apply_demotion(((level <= 8).astype(np.int32) + (level <= 4) + (level <= 2) + (level <= 1)).astype(np.int32))
+        pl.reserve(steps_ahead)
+        lay = cache.layers[layer]
+        lay.paged, lay.seen, lay.is_initialized, lay.dtype, lay.device = pl, T, True, torch.bfloat16, device
+    del k, v
+    torch.cuda.empty_cache()
+    alg_attn = sum(l.paged.bytes_in_pool() + B * Hkv * nb * 16 for l in cache.layers)
+    ids_host = torch.randint(0, cfg.vocab_size, (B, 1)).pin_memory()
+    ids_dev = torch.empty(B, 1, dtype=torch.long, device=device)
+    next_host = torch.empty(B, dtype=torch.long).pin_memory()
+
+    @torch.no_grad()
+    def step_resident():
+        out = model(input_ids=ids_dev, past_key_values=cache, use_cache=True, logits_to_keep=1)
+        return out.logits[:, -1].argmax(-1)
+
+    @torch.no_grad()
+    def step_e2e():
+        ids_dev.copy_(ids_host, non_blocking=True)
+        nxt = step_resident()
+        next_host.copy_(nxt, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    ids_dev.copy_(ids_host)
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    sampler = ClockSampler(env["local"])
+    if rank == 0:
+        sampler.start()
+    ms_eager = timed(step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_graph, launch_mode = None, "eager (transformers forward, one kernel call of this library per layer)"
+    if not args.eager:
+        try:
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                step_resident()
+            barrier()
+            graph.replay()
+            ms_graph = timed(graph.replay, args.steps)
+            launch_mode = "cuda graph of one model step (positions frozen at capture)"
+        except Exception as e:
+            launch_mode += f"; graph capture failed: {type(e).__name__}"
+            torch.cuda.synchronize()
+    ms_e2e = timed(step_e2e, args.steps)
+    status = max(int(l.paged.status.item()) for l in cache.layers)
+    ms_step = (ms_graph if ms_graph is not None else ms_eager) / args.steps
+    tokens = world * B * T
+    peak, peak_kind = measured_peak_gbs()
+    weight_bytes = n_params * 2
+    achieved = (alg_attn + weight_bytes) / (ms_step / 1e3) / 1e9
+    line = {
+        "metric": METRIC, "value": tokens / (ms_step / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights and activations; attention fp32 accumulate over packed bytes", "data": "synthetic",
+        "config": dict(workload_config(w, world, False, pool.bytes_in_use / 1e9),
+                       workload="FULL decode step, qwen3-8b-shape model with random-init weights over the packed caches of the 16k workload",
+                       model={"hidden_size": 4096, "intermediate_size": 12288, "vocab_size": 151936, "parameters": n_params},
+                       launch=launch_mode),
+        "decode_tokens_per_s": world * B / (ms_step / 1e3),
+        "eager_ms_per_step": ms_eager / args.steps,
+        "e2e": {"value": tokens / (ms_e2e / args.steps / 1e3), "unit": UNIT, "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
+                "ms_per_step": ms_e2e / args.steps, "launch": "eager, token ids up and next-token ids down every step"},
+        "gpu_launches": args.steps * L * (env["ext"].lib.gkv_decode_launch_count(B, Hq, Hkv, D, nb, GROUP, 0) + 2),
+        "append_status": status,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "kernel": "whole step: packed-cache bytes of all layers + every weight once",
+                     "algorithmic_bytes_per_step": alg_attn + weight_bytes, "attention_bytes": alg_attn, "weight_bytes": weight_bytes},
+        "clocks": clocks,
+    }
+    return line
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -605,7 +743,9 @@ def run_gpu(args):
         raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
     env = {"rank": rank, "world": world, "local": local, "device": device, "ext": ext,
            "cpu_baseline": not args.no_cpu_baseline}
-    if args.workload in PAGED:
+    if args.workload == "cfg1-full":
+        line = measure_full_step(args, env)
+    elif args.workload in PAGED:
         line = measure_paged(args.workload, args, env)
     elif args.workload is not None:
         line = measure_decode(args.workload, args, env)
@@ -847,6 +987,65 @@ def run_maintenance(args):
     print(json.dumps(line), flush=True)
 
 
+def run_rung_sweep(args):
+    """`--workload rungs`: the decode call on one layer of the 16k workload's size (32 sequences x 16384
+    tokens, 8 KV heads) packed at ONE rung throughout, and at the two workloads' mixes: microseconds per
+    call and algorithmic GB/s per rung.  Two layers are alternated so that no call finds its blocks in L2."""
+    import torch
+    from geodesia_kv_b200 import cuda_ext
+    from geodesia_kv_b200.pack_layout import pack_cache
+    ext = cuda_ext.get_ext()
+    if ext is None:
+        raise SystemExit("CUDA extension unavailable: refusing to benchmark anything else")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, Hq, Hkv, D, T = 32, 32, 8, 128, 16384
+    nb = T // 64
+    gen = torch.Generator(device=dev).manual_seed(7)
+    k = torch.randn(B, Hkv, T, D, device=dev, dtype=torch.bfloat16, generator=gen)
+    v = torch.randn(B, Hkv, T, D, device=dev, dtype=torch.bfloat16, generator=gen)
+    q = torch.randn(B, Hq, D, device=dev, generator=gen) * D ** -0.5
+    peak, peak_kind = measured_peak_gbs()
+    cases = [("16-bit", (1, 0, 0, 0, 0)), ("8-bit", (0, 1, 0, 0, 0)), ("4-bit", (0, 0, 1, 0, 0)), ("2-bit", (0, 0, 0, 1, 0)),
+             ("centroid", (0, 0, 0, 0, 1)), ("mix 10/20/40/20/10", WORKLOADS["cfg1"]["probs"]),
+             ("mix 2/8/30/40/20", WORKLOADS["cfg3"]["probs"])]
+    table = {}
+    reps = max(args.steps, 10)
+    for name, probs in cases:
+        caches = []
+        for i in range(2):
+            g = torch.Generator().manual_seed(11 + i)
+            pick = torch.multinomial(torch.tensor(probs, dtype=torch.float), B * Hkv * nb, replacement=True, generator=g)
+            level = torch.tensor(LADDER, dtype=torch.int32)[pick].view(B, Hkv, nb).to(dev)
+            caches.append(pack_cache(k, v, level, GROUP))
+        for _ in range(3):
+            for c in caches:
+                ext.mixed_attn_decode(q, *c.kernel_args())
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for c in caches:
+                ext.mixed_attn_decode(q, *c.kernel_args())
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / (2 * reps) * 1e3
+        alg = sum(c.algorithmic_bytes() for c in caches) / 2
+        table[name] = {"us_per_call": us, "algorithmic_MB": alg / 1e6, "GB/s": alg / us / 1e3, "frac_of_peak": alg / us / 1e3 / peak,
+                       "ns_per_block": us * 1e3 / (B * Hkv * nb)}
+        del caches
+    line = {"metric": "packed_kv_decode_gbs_per_rung", "value": table["mix 10/20/40/20/10"]["GB/s"], "unit": "GB/s", "n_gpus": 1,
+            "steps": reps, "warmup": 3, "ms_per_step": table["mix 10/20/40/20/10"]["us_per_call"] / 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
+            "config": {"workload": "one decode call (split kernel + merge, eager launches) over 65536 blocks = 32 seq x 16384 tok x 8 KV heads, per rung",
+                       "l2": "two layers alternate; each is larger than L2 except the centroid one"},
+            "per_rung": table, "gpu_launches": 2 * reps * len(cases) * 2,
+            "roofline": {"bound": "hbm", "achieved": table["mix 10/20/40/20/10"]["GB/s"], "peak": peak, "unit": "GB/s",
+                         "frac": table["mix 10/20/40/20/10"]["frac_of_peak"], "peak_kind": f"of {peak_kind}", "traffic": None}}
+    print(json.dumps(line), flush=True)
+
+
+
 def run_reference(args):
     """Reference arm: the CPU restatement of the reference's path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -858,6 +1057,8 @@ def run_reference(args):
     import gkv_oracle
     gkv_oracle.build()
     gkv_oracle.set_threads(os.cpu_count() or 1)      # torchrun pins OMP_NUM_THREADS=1; this arm may use every core
+    if args.workload == "cfg1-full":
+        args.workload = "cfg1"          # the CPU arm times the attention path of that workload
     paged = args.workload in PAGED
     if paged:
         # the ragged batch is sampled as sequences of the mean length at the rung mix the allocator produced
@@ -926,13 +1127,18 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(PAGED) + ["cfg2", "cfg2-small"],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(PAGED) + ["cfg1-full", "cfg2", "cfg2-small", "rungs"],
                     help="one workload only; default: cfg1 with cfg3 under its own key")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time plain launches instead of a CUDA graph of the step")
     args = ap.parse_args()
-    if args.workload in ("cfg2", "cfg2-small"):
+    if args.workload == "rungs":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the per-rung sweep has no reference arm; use the default workload"}))
+        elif int(os.environ.get("RANK", "0")) == 0:
+            run_rung_sweep(args)
+    elif args.workload in ("cfg2", "cfg2-small"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the cache-maintenance workload has no reference arm; use the default workload"}))
         elif int(os.environ.get("RANK", "0")) == 0:

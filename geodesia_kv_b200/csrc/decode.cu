@@ -25,7 +25,22 @@ struct CombineParams {
     int segs;            // > 1: blockIdx.y merges records [y*per_seg, (y+1)*per_seg) into record y of
     int per_seg;         //      an external-layout (segs, rows, D+2) buffer (normalise must be 0)
     float2* ml_out;      // optional, final level only: (M, L) of every output row (for the per-block softmax mass)
+    // Internal layout written by the tensor-core kernel: a row's used item slots are a prefix of its
+    // slots (the rest hold "empty" records), and how many are used follows from the row's rung-class
+    // counts — so the merge reads only the records that exist.  Null for other producers.
+    const int32_t* plan_tab;
+    int chunk, tab_per_row, warps_per_item;
 };
+
+// Records of output row `orow` that can be non-empty.
+__device__ __forceinline__ int live_parts(const CombineParams& p, int orow) {
+    if (!p.plan_tab || p.rep <= 0) return p.parts;
+    const int32_t* tab = p.plan_tab + (size_t)(p.tab_per_row ? orow / p.rep : 0) * 8;
+    int used = 0;
+#pragma unroll
+    for (int k = 0; k < 5; ++k) used += (tab[k + 1] - tab[k] + p.chunk - 1) / p.chunk;
+    return min(p.parts, used * p.warps_per_item);
+}
 
 constexpr int kCombineThreads = 256;
 
@@ -51,8 +66,9 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     float m = -INFINITY, l = 0.f, o[kPer];
 #pragma unroll
     for (int i = 0; i < kPer; ++i) o[i] = 0.f;
+    const int parts = live_parts(p, orow);
     const int s_lo = p.segs > 1 ? (int)blockIdx.y * p.per_seg : 0;
-    const int s_hi = p.segs > 1 ? min(p.parts, s_lo + p.per_seg) : p.parts;
+    const int s_hi = p.segs > 1 ? min(parts, s_lo + p.per_seg) : parts;
     const size_t out_row = p.segs > 1 ? (size_t)blockIdx.y * gridDim.x + orow : (size_t)orow;
     // kBatch records at a time: all their loads are issued before the first is merged (the merge
     // itself is a serial recurrence, and one load round trip per record made this kernel
@@ -200,12 +216,13 @@ __global__ void __launch_bounds__(kCombineThreads) exchange_combine_kernel(Combi
 #pragma unroll
     for (int i = 0; i < kPer; ++i) o[i] = 0.f;
     constexpr int kBatch = 4;
-    for (int s0 = warp; s0 < p.parts; s0 += 8 * kBatch) {
+    const int parts = live_parts(p, orow);
+    for (int s0 = warp; s0 < parts; s0 += 8 * kBatch) {
         float ms[kBatch], ls[kBatch], v[kBatch][kPer];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
             const int s = s0 + 8 * b;
-            const bool live = s < p.parts;
+            const bool live = s < parts;
             const float* rec = base + (live ? s : s0) * stride;
             ms[b] = live ? rec[0] : -INFINITY;
             ls[b] = rec[1];
@@ -542,6 +559,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     if ((mass_out || paged) && !pl.mma) return GKV_E_SHAPE;  // the by-product and the pool form exist in the tensor-core kernel only
     float2* mass_part = mass_out ? reinterpret_cast<float2*>(static_cast<uint8_t*>(workspace) + need) : nullptr;
     float2* mass_ml = mass_out ? mass_part + (size_t)rows * nb * (kP / group) * rep : nullptr;
+    const int32_t* combine_tab = nullptr;
     if (pl.mma) {
         const uint4* plan = static_cast<const uint4*>(plan_in);
         if (plan) {
@@ -557,6 +575,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         mma::Params mp;
         mp.plan = plan; mp.rows = rows;
         mp.plan_tab = reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(plan) + perm_entries_bytes(meta_rows, nb));
+        combine_tab = mp.plan_tab;
         mp.q = q; mp.data = data; mp.offs = offs;
         mp.klo = static_cast<const __half*>(klo); mp.kstep = static_cast<const __half*>(kstep);
         mp.vlo = static_cast<const __half*>(vlo); mp.vstep = static_cast<const __half*>(vstep);
@@ -601,13 +620,17 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     c.rec = records; c.out = out; c.parts = pl.parts; c.D = D; c.rep = rep; c.nsplit = pl.parts;
     c.stride_s = 0; c.normalise = normalise; c.status = pl.mma ? header + 1 : nullptr;
     c.segs = 1; c.per_seg = 0; c.ml_out = nullptr;
+    c.plan_tab = nullptr; c.chunk = 1; c.tab_per_row = 0; c.warps_per_item = 1;
+    if (pl.mma) {
+        c.plan_tab = combine_tab; c.chunk = pl.bps; c.tab_per_row = meta_rows != 1; c.warps_per_item = mma::kConsumerWarps;
+    }
     if (pl.segs > 1) {
         // level 1: (rows, parts, rep, D+2) -> (segs, B*Hq, D+2) behind the records
         float* mid = records + (size_t)B * Hq * pl.parts * (D + 2);
         c.out = mid; c.normalise = 0; c.segs = pl.segs; c.per_seg = (pl.parts + pl.segs - 1) / pl.segs;
         combine_kernel<<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
         GKV_LAUNCH_CHECK();
-        c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0;
+        c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0; c.plan_tab = nullptr;
         c.stride_s = (int64_t)B * Hq * (D + 2); c.normalise = normalise; c.segs = 1; c.per_seg = 0;
     }
     c.ml_out = mass_ml;
@@ -797,6 +820,7 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     gkv::CombineParams c;
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
     c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr; c.segs = 1; c.per_seg = 0; c.ml_out = nullptr;
+    c.plan_tab = nullptr; c.chunk = 1; c.tab_per_row = 0; c.warps_per_item = 1;
     gkv::combine_kernel<<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;

@@ -90,14 +90,18 @@ class _Extension:
         self._plans.clear()
 
     def _plan(self, offs, level, valid, meta_rows: int, nb: int):
-        if nb == 0 or torch.cuda.is_current_stream_capturing():
-            return None                                                    # built inside the workspace by the call
+        if nb == 0:
+            return None
         key = (offs.data_ptr(), offs._version, level.data_ptr(), level._version, valid.data_ptr(), valid._version,
                meta_rows, nb)
         hit = self._plans.get(key)
         if hit is not None:
+            # also while a CUDA graph is being captured: the graph then replays over the lists made for the
+            # metadata as it stood at capture (whoever edits level/valid/offs in place captures again)
             self._plans.move_to_end(key)
             return hit[0]
+        if torch.cuda.is_current_stream_capturing():
+            return None                                                    # built inside the workspace by the call
         plan = torch.empty(self.lib.gkv_decode_plan_bytes(meta_rows, nb), dtype=torch.uint8, device=level.device)
         rc = self.lib.gkv_decode_build_plan(offs.data_ptr(), level.data_ptr(), valid.data_ptr(), plan.data_ptr(),
                                             meta_rows, nb, _stream(level.device))

@@ -365,7 +365,7 @@ class Policy:
         if allow_demote:
             mass = observed_mass
             if mass is None:
-                mass = _block_mass(q[:, :1].reshape(R, D), k, scaling, q_offset, nb, P)
+                mass = _block_mass(q, st.view(nb), k, scaling, q_offset, nb, P)
             st.mass[:nb] = self.mass_decay * st.mass[:nb] + (1.0 - self.mass_decay) * mass.to(torch.float32)
         budget = self._budget_for(hid)
         cache = st.view(nb)
@@ -403,11 +403,20 @@ def _exact_attention(q, k, v, scaling, q_offset):
     return torch.softmax(s, -1) @ v.float()
 
 
-def _block_mass(q_now, k, scaling, q_offset, nb, P):
-    """Attention mass per block of the current queries (R, D), averaged over them
-    (policies.py:1497-1509 of the reference)."""
+def _block_mass(q, cache, k, scaling, q_offset, nb, P):
+    """Attention mass per block of the first query position, averaged over the R heads of the group
+    (policies.py:1497-1509 of the reference, which takes a dense softmax over all keys).
+
+    A single decode query that sees the whole cache gets it as a by-product of the decode kernel over
+    the packed blocks — one kernel call, no dense scores; any other call (a chunk of queries, a query
+    that sees only part of the keys) is a prefill-style call and falls back to the dense softmax."""
+    R, Q, D = q.shape
     T = k.shape[0]
-    s = (q_now.float() @ k.float().T) * scaling
+    if Q == 1 and q_offset >= T - 1 and D in (64, 128) and cache.group in (16, 32, 64) and R <= 8:
+        from .cuda_ext import get_ext
+        qi = (q[:, 0].float() * scaling).view(1, R, D).contiguous()
+        return get_ext().mixed_attn_decode_with_mass(qi, *cache.kernel_args())[1][0, 0]
+    s = (q[:, 0].float() @ k.float().T) * scaling
     s = s.masked_fill(~(torch.arange(T, device=k.device) <= q_offset)[None], float("-inf"))
     w = torch.softmax(s, -1)
     if nb * P != T:
@@ -492,9 +501,7 @@ def policy_attention(module, query, key, value, attention_mask, scaling, dropout
     for b in range(B):
         for hk in range(Hkv):
             qg = query[b, hk * reps:(hk + 1) * reps].float()
-            mass = None
-            if pol.name == "geodesia":
-                mass = _block_mass(qg[:, 0], key[b, hk], scaling, q_offset, (T + pol.block - 1) // pol.block, pol.block)
+            # the mass the allocator is fed with comes out of the decode kernel (see _block_mass)
             out[b, hk * reps:(hk + 1) * reps] = pol.attend_group(qg, key[b, hk], value[b, hk], scaling, q_offset,
-                                                                (layer, b, hk), True, mass)
+                                                                (layer, b, hk), True, None)
     return out.to(query.dtype).transpose(1, 2).contiguous(), None

@@ -318,3 +318,35 @@ def test_one_block_per_step_for_64_steps_against_the_oracle(oracle, budget):
         assert pool.bytes_in_use == layer.bytes_in_pool()
     assert demoted_total >= rows * (steps - 4)
     assert layer.bits_per_value() <= budget + 16.0 * 5 / (nb0 + steps) + 1e-6
+
+
+def test_serving_manager_stores_sequences_in_one_pool_and_frees_them():
+    """The reference's manager (vllm_plugin/kv_cache.py:85-104) with a pool attached: sequences of
+    different lengths share it, each occupies what its rungs cost, freeing one gives that back."""
+    from geodesia_kv_b200.vllm_plugin import GeodesiaKVCacheManager
+    L, H, Dh = 3, 2, 128
+    mgr = GeodesiaKVCacheManager(block_size=64, target_bpv=4.0, num_layers=L)
+    pool = mgr.attach_pool(256 << 20, Dh, 32)
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    used = {}
+    for seq_id, T in ((7, 64 * 20), (8, 64 * 5 + 9), (9, 64 * 33)):
+        c = mgr.create_sequence_cache(seq_id)
+        k = torch.randn(L, T, H, Dh, device="cuda", generator=gen).to(torch.bfloat16)
+        bpv = c.compress_sequence_kv(k, k * 0.5)
+        assert 4.0 < bpv < 8.0                   # 4-bit blocks with their scales, the last block exact
+        nb = (T + 63) // 64
+        want = L * H * ((nb - 1) * pool.slot[4] + pool.slot[16])          # 4-bit ladder, last block exact
+        assert c.pool_bytes() == want
+        used[seq_id] = want
+        # the pool copy attends like the row-form copy of the same sequence
+        q = (torch.randn(1, 8, Dh, device="cuda", generator=gen) * Dh ** -0.5).contiguous()
+        from geodesia_kv_b200.cuda_ext import get_ext
+        a = c.paged_layers[1].attend(q)
+        b = get_ext().mixed_attn_decode(q, *c.kernel_layers[1].kernel_args())
+        assert (a - b).abs().max().item() < 1e-5
+    assert pool.bytes_in_use == sum(used.values())
+    mgr.free_sequence_cache(8)
+    assert pool.bytes_in_use == used[7] + used[9] and 8 not in mgr.active_caches
+    mgr.free_sequence_cache(7)
+    mgr.free_sequence_cache(9)
+    assert pool.bytes_in_use == 0 and pool.bytes_reserved == 0
