@@ -376,10 +376,11 @@ __global__ void paged_append_kernel(AppendParams p) {
 // ---- persistent, bulk-copy-fed kernels ---------------------------------------------------------------
 // The kernels above start a CTA per block: the CTA reads the block's table entries, then its bytes, then
 // computes, then stores — a chain of dependent memory round trips that two resident CTAs per SM cannot
-// hide.  Here CTAs are persistent (two per SM); thread 0 looks up block i + 2*grid and starts ONE bulk
-// copy per contiguous piece of its source (K rows, V rows; or the packed block and its scale planes)
-// into a two-stage ring in shared memory while all threads work on block i out of the other stage, so
-// every global-memory latency is overlapped with arithmetic.  Sources that a bulk copy cannot take
+// hide.  Here CTAs are persistent (two per SM) and hold a ninth warp, the producer: it looks up block
+// i + grid (table entries: two dependent global loads) and starts ONE bulk copy per contiguous piece of
+// its source (K rows, V rows; or the packed block and its scale planes) into a two-stage ring in shared
+// memory while the 256 working threads are on block i out of the other stage, so every global-memory
+// latency is overlapped with arithmetic.  Sources that a bulk copy cannot take
 // (fp32 rows, a token stride other than D, an address that is not 16-byte aligned) are processed
 // straight from global memory by the same CTA.
 namespace st {
@@ -401,6 +402,7 @@ struct __align__(128) Smem {
     rq::Shared work;
     Desc desc[kStages];
     unsigned long long full[kStages];
+    unsigned long long empty[kStages];
     __align__(128) uint8_t stage[kStages][kStageBytes];
 };
 
@@ -517,8 +519,8 @@ __device__ void describe(const PagedDemoteParams& p, int i, Desc& d) {
     d.vlo = const_cast<__half*>(c); d.vstep = const_cast<__half*>(e);
 }
 
-// Thread 0: look block i up and start its copies into a stage; a source the copy engine cannot take
-// (a token stride other than D, an address that is not 16-byte aligned) is left for all threads to
+// The producer lane: look block i up and start its copies into a stage; a source the copy engine cannot take
+// (a token stride other than D, an address that is not 16-byte aligned) is left for the working threads to
 // copy by hand when the block's turn comes.
 template <int D, class P>
 __device__ void fetch(const P& p, int i, int n, Smem& sm, int s, int G, int gv) {
@@ -584,24 +586,44 @@ __device__ void copy_by_hand(const Desc& d, uint8_t* st, int G, int gv) {
     }
 }
 
+constexpr int kStagedThreads = rq::kThreads + 32;      // 256 working threads + the producer warp
+
 template <int D, class P>
-__global__ void __launch_bounds__(rq::kThreads, 2) staged_kernel(P p, int n, int group) {
+__global__ void __launch_bounds__(kStagedThreads, 2) staged_kernel(P p, int n, int group) {
     extern __shared__ __align__(128) uint8_t raw[];
     Smem& sm = *reinterpret_cast<Smem*>(raw);
     const int tid = threadIdx.x;
     const int kg = min(group, kP), vg = min(group, D);
     const int G = kP / kg, gv = D / vg;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) bar_init(&sm.full[s], 1);
+        for (int s = 0; s < kStages; ++s) { bar_init(&sm.full[s], 1); bar_init(&sm.empty[s], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid == 0)
-        for (int s = 0; s < kStages; ++s) fetch<D>(p, (int)blockIdx.x + s * (int)gridDim.x, n, sm, s, G, gv);
+    if (tid >= rq::kThreads) {
+        // ---- producer warp (one lane): looks blocks up and starts their copies, a stage ahead of the
+        // workers, so that neither the table look-ups nor the copies are ever waited for by them
+        if (tid == rq::kThreads) {
+            for (int it = 0;; ++it) {
+                const int s = it % kStages;
+                if (it >= kStages && !bar_wait(&sm.empty[s], (uint32_t)(it / kStages - 1) & 1u)) {
+                    atomicExch(&g_status, 1);          // the workers never released the stage
+                    return;
+                }
+                const int i = (int)blockIdx.x + it * (int)gridDim.x;
+                fetch<D>(p, i, n, sm, s, G, gv);
+                if (i >= n) return;
+            }
+        }
+        return;
+    }
     for (int it = 0;; ++it) {
         const int s = it % kStages;
         const bool ok = bar_wait(&sm.full[s], (uint32_t)(it / kStages) & 1u);
-        if (!__syncthreads_and(ok)) {                  // a copy never landed: flag it and stop
+        uint32_t all_ok;
+        asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 1, 256, q; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+        if (!all_ok) {                                 // a copy never landed: flag it and stop
             if (tid == 0) atomicExch(&g_status, 1);
             return;
         }
@@ -611,7 +633,7 @@ __global__ void __launch_bounds__(rq::kThreads, 2) staged_kernel(P p, int n, int
             uint8_t* st = sm.stage[s];
             if (!d.staged) {
                 copy_by_hand<D>(d, st, G, gv);
-                __syncthreads();
+                rq::work_sync();
             }
             rq::Job j;
             j.src_kind = 0; j.ksrc = j.vsrc = nullptr; j.src_stride = 0; j.nvalid = kP; j.old_blk = nullptr; j.old_level = 0;
@@ -631,8 +653,8 @@ __global__ void __launch_bounds__(rq::kThreads, 2) staged_kernel(P p, int n, int
             src.vlo = src.kstep + G * D; src.vstep = src.vlo + kP * gv;
             rq::requantise_staged<D>(src, j, sm.work);
         }
-        __syncthreads();                               // the stage and the work area are free again
-        if (tid == 0) fetch<D>(p, (int)blockIdx.x + (it + kStages) * (int)gridDim.x, n, sm, s, G, gv);
+        rq::work_sync();                               // every worker is done with the stage and the work area
+        if (tid == 0) bar_arrive(&sm.empty[s]);
     }
 }
 
@@ -663,7 +685,7 @@ static int launch(const P& p, int n, int group, bool fp32_rows, cudaStream_t str
     GKV_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     GKV_CUDA_TRY(cudaFuncSetAttribute(staged_kernel<D, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
     const int grid = n < 2 * sms ? n : 2 * sms;
-    staged_kernel<D, P><<<grid, rq::kThreads, sizeof(Smem), stream>>>(p, n, group);
+    staged_kernel<D, P><<<grid, kStagedThreads, sizeof(Smem), stream>>>(p, n, group);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }

@@ -458,6 +458,10 @@ __device__ void requantise(const Job& j, Shared& sm) {
 #define GKV_RQ_UNROLL 1
 #endif
 constexpr int kCodeUnroll = GKV_RQ_UNROLL;     // unrolling of the loops over a thread's tokens in the code passes
+// The 256 working threads of a CTA meet at named barrier 1: the CTA may hold more threads (a producer
+// warp that feeds the stages), which must not be part of these barriers.
+__device__ __forceinline__ void work_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
 struct StagedSrc {
     const uint8_t* k; const uint8_t* v;     // dense tiles (kind 1 bf16, 2 fp16), or the halves of the packed block (kind 3)
     int kind, nvalid, level;                // level: rung of a packed source (8, 4 or 2)
@@ -515,22 +519,30 @@ __device__ __forceinline__ float staged1(const StagedSrc& s, int which, int t, i
 // unless the product lands that close to a tie.  `tie` = 0.5 minus several times that bound for the
 // rung's largest quotient; only codes that fail the test (or are not numbers) are redone with the
 // IEEE division, one by one — a warp rarely has any.
+__device__ __forceinline__ float max_nan(float a, float b) {      // maximum that keeps a NaN operand
+    float d;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
 __device__ __forceinline__ void codes8(const float* x, const float* lf, const float* sf, const float* rs, float qmax, int qmaxi,
                                        float tie, uint32_t* code) {
     constexpr float kMagic = 12582912.0f;      // 1.5 * 2^23: adding it rounds to nearest-even into the low mantissa bits
-    uint32_t redo = 0;
+    float worst = 0.f;                         // largest distance of a quotient from the integer it rounded to (NaN sticks)
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         const float q = __fmul_rn(__fsub_rn(x[c], lf[c]), rs[c]);
         const float m = __fadd_rn(q, kMagic);
-        redo |= (fabsf(q - __fsub_rn(m, kMagic)) < tie) ? 0u : (1u << c);         // set for a near-tie and for NaN
+        worst = max_nan(worst, fabsf(q - __fsub_rn(m, kMagic)));
         code[c] = (uint32_t)min(max(__float_as_int(m) - 0x4B400000, 0), qmaxi);   // out-of-range q clamps correctly
     }
-    if (redo) {
+    if (!(worst < tie)) {                      // some quotient is near a tie or not a number: redo those exactly
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            if (redo & (1u << c)) {
-                const float q = __fdiv_rn(__fsub_rn(x[c], lf[c]), sf[c]);
+            const float a = __fsub_rn(x[c], lf[c]);
+            const float q0 = __fmul_rn(a, rs[c]);
+            if (!(fabsf(q0 - rintf(q0)) < tie)) {
+                const float q = __fdiv_rn(a, sf[c]);
                 float r = rintf(q);
                 r = (r != r) ? 0.f : fminf(fmaxf(r, 0.f), qmax);
                 code[c] = (uint32_t)r;
@@ -539,85 +551,19 @@ __device__ __forceinline__ void codes8(const float* x, const float* lf, const fl
     }
 }
 
-template <int D>
-__device__ void requantise_staged(const StagedSrc& src, const Job& j, Shared& sm) {
+template <int D, int LV>
+__device__ __forceinline__ void quantise_staged(const StagedSrc& src, const Job& j, Shared& sm) {
     constexpr int OPR = D / 8, ROWS = kThreads / OPR, NI = kP / ROWS;
+    constexpr int lv = LV;
     const int tid = threadIdx.x, lane = tid & 31;
     const int c8 = tid % OPR, tr = tid / OPR;
-    const int lv = j.level;
     const int kgs = src.kgs, vgs = src.vgs, vg = 1 << vgs;
     const int G = kP >> kgs, gv = D >> vgs;
-    const bool quant = lv == 8 || lv == 4 || lv == 2;
     const bool radii = j.ek != nullptr;
-
-    if (tid < 2) sm.err[tid] = 0u;
-    if (quant) {
-        for (int u = tid; u < G * D; u += kThreads) { sm.kmin[u] = 0xffffffffu; sm.kmax[u] = 0u; }
-    } else if (j.zero_scales) {
-        for (int u = tid; u < G * D; u += kThreads) { j.klo[u] = __ushort_as_half(0); j.kstep[u] = __ushort_as_half(0); }
-        for (int u = tid; u < kP * gv; u += kThreads) { j.vlo[u] = __ushort_as_half(0); j.vstep[u] = __ushort_as_half(0); }
-    }
-
-    if (lv == 1) {
-        // centroid: thread (which, d) adds the 64 tokens of its channel in order
-        const int which = tid / D, d = tid - which * D;
-        float mean = 0.f;
-        if (tid < 2 * D) {
-            float s = 0.f;
-#pragma unroll 8
-            for (int t = 0; t < kP; ++t) s = __fadd_rn(s, staged1<D>(src, which, t, d));
-            mean = __half2float(__float2half_rn(__fdiv_rn(s, (float)kP)));
-            reinterpret_cast<__half*>(j.dst + (which ? half_bytes(1, D) : 0))[d] = __float2half_rn(mean);
-        }
-        if (radii) {
-            for (int u = tid; u < 2 * kP; u += kThreads) sm.csum[u / kP][u % kP] = 0.f;
-            __syncthreads();
-            if (tid < 2 * D) {
-                for (int t = 0; t < kP; ++t) {
-                    const float e = __fsub_rn(staged1<D>(src, which, t, d), mean);
-                    float s2 = e * e;
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-                    if (lane == 0) atomicAdd(&sm.csum[which][t], s2);
-                }
-            }
-            __syncthreads();
-            if (tid < 2) {
-                float m = 0.f;
-                for (int t = 0; t < kP; ++t) m = fmaxf(m, sm.csum[tid][t]);
-                float* acc = tid ? j.ev : j.ek;
-                *acc += sqrtf(m);
-            }
-        }
-        return;
-    }
-
-    if (lv == 16) {
-#pragma unroll
-        for (int w = 0; w < 2; ++w) {
-            uint16_t* half = reinterpret_cast<uint16_t*>(j.dst + (w ? half_bytes(16, D) : 0));
-#pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                float x[8];
-                staged8<D>(src, w, tr + i * ROWS, c8, x);
-                uint32_t o[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const __nv_bfloat162 b = __floats2bfloat162_rn(x[2 * c], x[2 * c + 1]);
-                    o[c] = *reinterpret_cast<const uint32_t*>(&b);
-                }
-                uint16_t* p = half + (size_t)(tr + i * ROWS) * D + 8 * c8;
-                if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) *reinterpret_cast<uint4*>(p) = make_uint4(o[0], o[1], o[2], o[3]);
-                else for (int c = 0; c < 4; ++c) { p[2 * c] = (uint16_t)o[c]; p[2 * c + 1] = (uint16_t)(o[c] >> 16); }
-            }
-        }
-        return;
-    }
-
     const float qmax = (float)((1 << lv) - 1);
     const int qmaxi = (1 << lv) - 1;
     const float tie = 0.5f - (qmax + 1.0f) * 1e-6f;
-    __syncthreads();                           // key tables initialised
+    work_sync();                           // key tables initialised
 
     // ---- K ranges: thread, then the lanes with the same channels, then shared-memory atomics -------
     {
@@ -688,7 +634,7 @@ __device__ void requantise_staged(const StagedSrc& src, const Job& j, Shared& sm
             evmax = fmaxf(evmax, e2);
         }
     }
-    __syncthreads();
+    work_sync();
     for (int u = tid; u < G * D; u += kThreads) {
         const float lo = keyf(sm.kmin[u]), hi = keyf(sm.kmax[u]);
         const float step = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), qmax);
@@ -698,7 +644,7 @@ __device__ void requantise_staged(const StagedSrc& src, const Job& j, Shared& sm
         const int tgu = u / D, du = u - tgu * D;
         sm.ks[(tgu * 8 + (du & 7)) * OPR + (du >> 3)] = make_float4(__half2float(l16), sf, __frcp_rn(sf), 0.f);
     }
-    __syncthreads();
+    work_sync();
 
     // ---- K codes ---------------------------------------------------------------------------
 #pragma unroll kCodeUnroll
@@ -728,13 +674,95 @@ __device__ void requantise_staged(const StagedSrc& src, const Job& j, Shared& sm
             evmax = fmaxf(evmax, __shfl_xor_sync(0xffffffffu, evmax, o));
         }
         if (lane == 0) { atomicMax(&sm.err[0], __float_as_uint(ekmax)); atomicMax(&sm.err[1], __float_as_uint(evmax)); }
-        __syncthreads();
+        work_sync();
         if (tid < 2) {
             float* acc = tid ? j.ev : j.ek;
             *acc += sqrtf(__uint_as_float(sm.err[tid]));
         }
     }
 }
+
+template <int D>
+__device__ void requantise_staged(const StagedSrc& src, const Job& j, Shared& sm) {
+    constexpr int OPR = D / 8, ROWS = kThreads / OPR, NI = kP / ROWS;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int c8 = tid % OPR, tr = tid / OPR;
+    const int lv = j.level;
+    const int kgs = src.kgs, vgs = src.vgs, vg = 1 << vgs;
+    const int G = kP >> kgs, gv = D >> vgs;
+    const bool quant = lv == 8 || lv == 4 || lv == 2;
+    const bool radii = j.ek != nullptr;
+
+    if (tid < 2) sm.err[tid] = 0u;
+    if (quant) {
+        for (int u = tid; u < G * D; u += kThreads) { sm.kmin[u] = 0xffffffffu; sm.kmax[u] = 0u; }
+    } else if (j.zero_scales) {
+        for (int u = tid; u < G * D; u += kThreads) { j.klo[u] = __ushort_as_half(0); j.kstep[u] = __ushort_as_half(0); }
+        for (int u = tid; u < kP * gv; u += kThreads) { j.vlo[u] = __ushort_as_half(0); j.vstep[u] = __ushort_as_half(0); }
+    }
+
+    if (lv == 1) {
+        // centroid: thread (which, d) adds the 64 tokens of its channel in order
+        const int which = tid / D, d = tid - which * D;
+        float mean = 0.f;
+        if (tid < 2 * D) {
+            float s = 0.f;
+#pragma unroll 8
+            for (int t = 0; t < kP; ++t) s = __fadd_rn(s, staged1<D>(src, which, t, d));
+            mean = __half2float(__float2half_rn(__fdiv_rn(s, (float)kP)));
+            reinterpret_cast<__half*>(j.dst + (which ? half_bytes(1, D) : 0))[d] = __float2half_rn(mean);
+        }
+        if (radii) {
+            for (int u = tid; u < 2 * kP; u += kThreads) sm.csum[u / kP][u % kP] = 0.f;
+            work_sync();
+            if (tid < 2 * D) {
+                for (int t = 0; t < kP; ++t) {
+                    const float e = __fsub_rn(staged1<D>(src, which, t, d), mean);
+                    float s2 = e * e;
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+                    if (lane == 0) atomicAdd(&sm.csum[which][t], s2);
+                }
+            }
+            work_sync();
+            if (tid < 2) {
+                float m = 0.f;
+                for (int t = 0; t < kP; ++t) m = fmaxf(m, sm.csum[tid][t]);
+                float* acc = tid ? j.ev : j.ek;
+                *acc += sqrtf(m);
+            }
+        }
+        return;
+    }
+
+    if (lv == 16) {
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+            uint16_t* half = reinterpret_cast<uint16_t*>(j.dst + (w ? half_bytes(16, D) : 0));
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                float x[8];
+                staged8<D>(src, w, tr + i * ROWS, c8, x);
+                uint32_t o[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const __nv_bfloat162 b = __floats2bfloat162_rn(x[2 * c], x[2 * c + 1]);
+                    o[c] = *reinterpret_cast<const uint32_t*>(&b);
+                }
+                uint16_t* p = half + (size_t)(tr + i * ROWS) * D + 8 * c8;
+                if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) *reinterpret_cast<uint4*>(p) = make_uint4(o[0], o[1], o[2], o[3]);
+                else for (int c = 0; c < 4; ++c) { p[2 * c] = (uint16_t)o[c]; p[2 * c + 1] = (uint16_t)(o[c] >> 16); }
+            }
+        }
+        return;
+    }
+
+    // the quantised rungs: one body per rung, so that every shift, mask and byte offset is a constant
+    if (lv == 8) quantise_staged<D, 8>(src, j, sm);
+    else if (lv == 4) quantise_staged<D, 4>(src, j, sm);
+    else quantise_staged<D, 2>(src, j, sm);
+}
+
 
 }  // namespace rq
 }  // namespace gkv
