@@ -44,11 +44,14 @@ __device__ __forceinline__ int live_parts(const CombineParams& p, int orow) {
 
 constexpr int kCombineThreads = 256;
 
-// One CTA per output row.  The records of a row are shared out over the 8 warps (record s goes
-// to warp s mod 8, whose lanes read it coalesced), each warp keeps a running (m, l, o) of its
-// records, and the 8 states are merged through shared memory — the same recurrence at both levels.
-__global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams p) {
-    __shared__ float sm_m[8], sm_l[8], sm_o[8][kMaxD];
+// One CTA per output row.  The records of a row are shared out over the NW warps (record s goes
+// to warp s mod NW, whose lanes read it coalesced), each warp keeps a running (m, l, o) of its
+// records, and the NW states are merged through shared memory — the same recurrence at both levels.
+// NW = 8 normally; 32 for rows with a few hundred records, which one wide CTA merges faster than
+// two launches of narrow ones (the single-sequence case, where the call is launch-bound).
+template <int NW>
+__global__ void __launch_bounds__(NW * 32) combine_kernel(CombineParams p) {
+    __shared__ float sm_m[NW], sm_l[NW], sm_o[NW][kMaxD];
     const int orow = blockIdx.x, D = p.D;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* base;
@@ -74,11 +77,11 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     // itself is a serial recurrence, and one load round trip per record made this kernel
     // latency-bound); the order of the merge is unchanged.
     constexpr int kBatch = 4;
-    for (int s0 = s_lo + warp; s0 < s_hi; s0 += 8 * kBatch) {
+    for (int s0 = s_lo + warp; s0 < s_hi; s0 += NW * kBatch) {
         float ms[kBatch], ls[kBatch], v[kBatch][kPer];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
-            const int s = s0 + 8 * b;
+            const int s = s0 + NW * b;
             const bool live = s < s_hi;
             const float* rec = base + (live ? s : s0) * stride;
             ms[b] = live ? rec[0] : -INFINITY;
@@ -109,17 +112,17 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     __syncthreads();
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) M = fmaxf(M, sm_m[w]);
-    float L = 0.f, wgt[8];
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, sm_m[w]);
+    float L = 0.f, wgt[NW];
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
+    for (int w = 0; w < NW; ++w) {
         wgt[w] = (sm_m[w] > -INFINITY) ? expf(sm_m[w] - M) : 0.f;
         L += sm_l[w] * wgt[w];
     }
-    for (int d = threadIdx.x; d < D; d += kCombineThreads) {
+    for (int d = threadIdx.x; d < D; d += NW * 32) {
         float a = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) a += sm_o[w][d] * wgt[w];
+        for (int w = 0; w < NW; ++w) a += sm_o[w][d] * wgt[w];
         a += poison;
         if (p.normalise) p.out[out_row * D + d] = a / fmaxf(L, 1e-20f);
         else p.out[out_row * (D + 2) + 2 + d] = a;
@@ -327,11 +330,14 @@ struct Plan {
     int parts;            // records per cache row and query head (the tensor-core kernel writes one per consumer warp)
     int segs;             // > 1: the merge runs in two levels, `segs` partial merges per output row first
     bool mma;             // tensor-core kernel (persistent, work items of `bps` blocks)
+    bool wide = false;    // one merge level by a CTA of 32 warps (a few hundred records per row)
     int grid;
 };
 
 constexpr size_t kHeaderBytes = 256;   // work counter + status word in front of the records
 constexpr int kCombineDirect = 256;    // up to this many records per output row one CTA merges them all
+constexpr int kCombineWide = 256;      // up to this many, one CTA of 32 warps would (measured slower than two levels on the
+                                       // single-sequence case, 34.8 against 28.7 us per call: not used, same as kCombineDirect)
 constexpr int kCombineSegs = 32;       // above it: this many CTAs per row merge a slice each, then one merges those
 
 static bool mma_shape_ok(int D, int group, int rep) {
@@ -388,7 +394,8 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
         pl.bps = chunk;
         pl.nsplit = (nb + chunk - 1) / chunk + 4;
         pl.parts = pl.nsplit * mma::kConsumerWarps;
-        pl.segs = pl.parts > kCombineDirect ? (pl.parts / 64 < kCombineSegs ? pl.parts / 64 : kCombineSegs) : 1;
+        pl.wide = pl.parts > kCombineDirect && pl.parts <= kCombineWide;
+        pl.segs = pl.parts > kCombineWide ? (pl.parts / 64 < kCombineSegs ? pl.parts / 64 : kCombineSegs) : 1;
         return pl;
     }
     // generic kernel: enough slices for ~4 CTAs per SM
@@ -628,14 +635,15 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         // level 1: (rows, parts, rep, D+2) -> (segs, B*Hq, D+2) behind the records
         float* mid = records + (size_t)B * Hq * pl.parts * (D + 2);
         c.out = mid; c.normalise = 0; c.segs = pl.segs; c.per_seg = (pl.parts + pl.segs - 1) / pl.segs;
-        combine_kernel<<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
+        combine_kernel<8><<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
         GKV_LAUNCH_CHECK();
         c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0; c.plan_tab = nullptr;
         c.stride_s = (int64_t)B * Hq * (D + 2); c.normalise = normalise; c.segs = 1; c.per_seg = 0;
     }
     c.ml_out = mass_ml;
     if (xch) exchange_combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c, *xch);
-    else combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c);
+    else if (pl.wide && pl.segs <= 1) combine_kernel<32><<<B * Hq, 1024, 0, stream>>>(c);
+    else combine_kernel<8><<<B * Hq, kCombineThreads, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
     if (mass_out) {
         const size_t n = (size_t)rows * nb;
@@ -821,7 +829,7 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
     c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr; c.segs = 1; c.per_seg = 0; c.ml_out = nullptr;
     c.plan_tab = nullptr; c.chunk = 1; c.tab_per_row = 0; c.warps_per_item = 1;
-    gkv::combine_kernel<<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    gkv::combine_kernel<8><<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }

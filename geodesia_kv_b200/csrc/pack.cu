@@ -425,6 +425,7 @@ __device__ __forceinline__ bool bar_wait(unsigned long long* b, uint32_t parity)
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok) : "r"(s32(b)), "r"(parity), "r"(2000u) : "memory");
         if (ok) return true;
+        if (spin > 1) __nanosleep(spin < 16 ? 100 : 400);      // a polling lane must not eat the workers' issue slots
         if ((spin & 63u) == 63u) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));

@@ -83,14 +83,18 @@ __device__ __forceinline__ uint32_t code_of(float x, float lf, float sf, float r
 
 __device__ __forceinline__ void unpack8_16(const uint4 r, bool bf, float* out) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    if (bf) {                                   // one branch for the eight values, not one per pair
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (bf) {
-            out[2 * i] = bf16_bits_to_float(w[i] & 0xffffu);
-            out[2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
-        } else {
-            out[2 * i] = half_bits_to_float((uint16_t)(w[i] & 0xffffu));
-            out[2 * i + 1] = half_bits_to_float((uint16_t)(w[i] >> 16));
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
         }
     }
 }
