@@ -144,6 +144,7 @@ struct Params {
     int items_per_row, items;
     int per_row_meta;
     int rows;
+    int interleave;          // 1: odd rows walk their rungs in another order than even rows (see span_of)
     int paged;               // 1: `data` is a block pool, offs are pool offsets, and the four scale planes of a quantised
                              // block sit right behind its bytes ([klo][kstep][vlo][vstep]); klo..vstep above are unused
     int64_t stride_bh;
@@ -455,10 +456,15 @@ __device__ __forceinline__ Span span_of(const Params& p, int id) {
     int slot = id / p.rows;
     sp.row = id % p.rows;
     const int32_t* tab = p.plan_tab + (size_t)(p.per_row_meta ? sp.row : 0) * kPlanTabInts;
-    int start = tab[0];
+    // Items are handed out slot by slot over all rows, so at any moment the whole grid works on the same
+    // slot index: every row walks its rungs 16, 8, 4, 2, centroid — the costliest items first, the
+    // cheapest in the tail.  With p.interleave odd rows walk 4, 2, 16, 8, centroid instead, so that some
+    // SMs stream wide blocks while others unpack narrow ones; that measured slower and is off by default.
+    const int first = (p.interleave && (sp.row & 1)) ? 2 : 0;
 #pragma unroll 1
-    for (int k = 0; k < 5; ++k) {
-        const int next = tab[k + 1], cnt = next - start;
+    for (int i = 0; i < 5; ++i) {
+        const int k = i < 4 ? ((i + first) & 3) : 4;
+        const int start = tab[k], cnt = tab[k + 1] - start;
         const int n = (cnt + p.chunk - 1) / p.chunk;
         if (slot < n) {
             sp.level = ladder_level(k);
@@ -467,7 +473,6 @@ __device__ __forceinline__ Span span_of(const Params& p, int id) {
             return sp;
         }
         slot -= n;
-        start = next;
     }
     return sp;
 }
