@@ -70,7 +70,7 @@ PAGED = {
 }
 # share of blocks per rung (16, 8, 4, 2, centroid) the allocator leaves at 4 bits/value on the paged workload;
 # the CPU arm, which has no allocator kernel to run, samples its rungs from it
-PAGED_RUNG_MIX = (0.04, 0.02, 0.30, 0.40, 0.24)
+PAGED_RUNG_MIX = (0.03, 0.09, 0.54, 0.0, 0.34)
 GROUP = 32
 LADDER = (16, 8, 4, 2, 1)
 METRIC = "packed_kv_decode_attn_context_tokens_per_s"
