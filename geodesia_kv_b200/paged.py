@@ -17,7 +17,7 @@ GPU at a bit budget (``README.md:243-248``) — needs demotion to hand memory ba
   the per-block softmax mass as a by-product), and maintenance runs the distortion, allocator and
   demotion kernels for all rows at once.
 
-Free lists live on the host (numpy): a maintenance step reads the allocator's verdict back once,
+Free lists live on the host (numpy): a maintenance step reads the allocator's result back once,
 for all rows (and, through :class:`PagedKVCache.maintain`, for all layers), which is the only
 host synchronisation of the serving loop; decode steps in between launch kernels only.
 """
@@ -398,7 +398,7 @@ class PagedLayerCache:
         return tgt
 
     def apply_demotion(self, tgt_idx_host: np.ndarray) -> int:
-        """Demote to the allocator's verdict (host array (rows, nb) of ladder indices): allocate the
+        """Demote to the allocator's result (host array (rows, nb) of ladder indices): allocate the
         smaller slots, re-quantise on the device, free the larger slots.  Returns blocks demoted."""
         nb = tgt_idx_host.shape[1]
         cur = self.level_h[:, :nb]
