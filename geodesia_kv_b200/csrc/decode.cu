@@ -38,7 +38,10 @@ __device__ __forceinline__ int live_parts(const CombineParams& p, int orow) {
     const int32_t* tab = p.plan_tab + (size_t)(p.tab_per_row ? orow / p.rep : 0) * 8;
     int used = 0;
 #pragma unroll
-    for (int k = 0; k < 5; ++k) used += (tab[k + 1] - tab[k] + p.chunk - 1) / p.chunk;
+    for (int k = 0; k < 5; ++k) {
+        const int ck = k == 4 ? min(p.chunk, mma::kMaxCentroidItemBlocks) : p.chunk;     // as the kernel cuts the runs
+        used += (tab[k + 1] - tab[k] + ck - 1) / ck;
+    }
     return min(p.parts, used * p.warps_per_item);
 }
 
@@ -335,6 +338,7 @@ struct Plan {
 };
 
 constexpr size_t kHeaderBytes = 256;   // work counter + status word in front of the records
+constexpr int kAutoItemBlocks = 64;     // largest work item the planner picks by itself
 constexpr int kCombineDirect = 256;    // up to this many records per output row one CTA merges them all
 constexpr int kCombineWide = 256;      // up to this many, one CTA of 32 warps would (measured slower than two levels on the
                                        // single-sequence case, 34.8 against 28.7 us per call: not used, same as kCombineDirect)
@@ -388,13 +392,15 @@ static Plan make_plan(int rows, int nb, int D, int group, int rep, bool allow_mm
         const long total = (long)rows * nb;
         int chunk = (int)(total / ((long)pl.grid * 6));      // ~6 items per CTA; larger items measured faster than finer balance
         if (chunk < mma::kMinItemBlocks) chunk = mma::kMinItemBlocks;
-        if (chunk > mma::kMaxItemBlocks) chunk = mma::kMaxItemBlocks;    // the producers' block tables
+        if (chunk > kAutoItemBlocks) chunk = kAutoItemBlocks;            // larger items (up to mma::kMaxItemBlocks, by
+                                                                         // gkv_set_decode_item_blocks) measured no faster
         if (g_item_blocks > 0) chunk = g_item_blocks;
         // Every rung's run of a row's sorted list is cut into items of `chunk` blocks; whatever the
         // mix of rungs, ceil(nb / chunk) + 4 slots hold them all (five runs, each with one short item
         // at most).  Slots a row does not need stay empty.
         pl.bps = chunk;
-        pl.nsplit = (nb + chunk - 1) / chunk + 4;
+        const int cmin = chunk < mma::kMaxCentroidItemBlocks ? chunk : mma::kMaxCentroidItemBlocks;
+        pl.nsplit = (nb + cmin - 1) / cmin + 4;
         pl.parts = pl.nsplit * mma::kConsumerWarps;
         pl.wide = pl.parts > kCombineDirect && pl.parts <= kCombineWide;
         pl.segs = pl.parts > kCombineWide ? (pl.parts / 64 < kCombineSegs ? pl.parts / 64 : kCombineSegs) : 1;

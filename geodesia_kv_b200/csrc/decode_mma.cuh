@@ -93,7 +93,8 @@ constexpr int kHelperRegs = 56, kConsumerRegs = 152;
 #endif
 constexpr int kNSlot = GKV_NSLOT;        // descriptor slots (blocks in flight) per stream
 constexpr uint32_t kRingBytes = GKV_RING_KB * 1024;
-constexpr int kMaxItemBlocks = 64;       // blocks per work item: 32 per producer (one table entry per lane)
+constexpr int kMaxItemBlocks = 128;      // blocks per work item (the item's block table in shared memory)
+constexpr int kMaxCentroidItemBlocks = 64;   // centroid items are held in registers by the warps that read them: shorter
 constexpr int kMinItemBlocks = kConsumerWarps / 2;   // one block per pair
 constexpr int kItemSlots = 4;            // item descriptors in flight: finishing, current, announced, spare
 #ifndef GKV_WAIT_LIMIT_NS
@@ -465,11 +466,12 @@ __device__ __forceinline__ Span span_of(const Params& p, int id) {
     for (int i = 0; i < 5; ++i) {
         const int k = i < 4 ? ((i + first) & 3) : 4;
         const int start = tab[k], cnt = tab[k + 1] - start;
-        const int n = (cnt + p.chunk - 1) / p.chunk;
+        const int ck = k == 4 ? min(p.chunk, kMaxCentroidItemBlocks) : p.chunk;
+        const int n = (cnt + ck - 1) / ck;
         if (slot < n) {
             sp.level = ladder_level(k);
-            sp.b_lo = start + slot * p.chunk;
-            sp.nblk = min(p.chunk, cnt - slot * p.chunk);
+            sp.b_lo = start + slot * ck;
+            sp.nblk = min(ck, cnt - slot * ck);
             return sp;
         }
         slot -= n;
@@ -674,10 +676,11 @@ __device__ void scheduler_loop(const Params& p, Smem<D, G>& sm, int* abort_flag)
         }
         it.end_seq0 = tot0;
         it.end_seq1 = tot1;
-        // the item's block entries, two per lane, with the row's base offset added
-        uint4 e[2];
+        // the item's block entries, four per lane, with the row's base offset added
+        constexpr int kPerLane = kMaxItemBlocks / 32;
+        uint4 e[kPerLane];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < kPerLane; ++h) {
             e[h] = make_uint4(0, 0, 0, 0);
             const int i = lane + 32 * h;
             if (!it.exit && i < it.nblk) {
@@ -691,8 +694,8 @@ __device__ void scheduler_loop(const Params& p, Smem<D, G>& sm, int* abort_flag)
         const int sl = j % kItemSlots;
         if (j >= kItemSlots) ok = mbar_wait(&sm.item_empty[sl], (uint32_t)(j / kItemSlots - 1) & 1u);
         if (!ok) break;
-        sm.item_tab[sl * kMaxItemBlocks + lane] = e[0];
-        sm.item_tab[sl * kMaxItemBlocks + lane + 32] = e[1];
+#pragma unroll
+        for (int h = 0; h < kPerLane; ++h) sm.item_tab[sl * kMaxItemBlocks + lane + 32 * h] = e[h];
         if (lane == 0) sm.item[sl] = it;
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.item_full[sl]);
@@ -1386,7 +1389,7 @@ __device__ __forceinline__ int ring_item(
 template <int D, int G, bool MASS>
 __device__ __forceinline__ void centroid_item(const Params& p, const Ctx<D, G>& c, const ItemDesc& it, const uint4* tab,
                                               int warp, float* rec0) {
-    constexpr int kMaxMine = (kMaxItemBlocks + kConsumerWarps - 1) / kConsumerWarps;
+    constexpr int kMaxMine = (kMaxCentroidItemBlocks + kConsumerWarps - 1) / kConsumerWarps;
     constexpr int LPV = D / 8;                            // lanes that cover one vector with 16 bytes each
     static_assert(LPV <= 16, "head dim too large for the centroid path");
     const int lane = c.lane, hl = lane & 15, h0 = (lane >> 4) * 4;
