@@ -74,3 +74,18 @@ def test_budgeted_cache_stays_close_and_gives_memory_back():
     assert torch.isfinite(m).all() and float(m.sum()) > 0
     for l in cache.layers:
         assert int(l.paged.status.item()) == 0
+
+
+def test_generate_runs_on_the_packed_cache():
+    """transformers' own generate loop (greedy) with the packed cache passed as past_key_values."""
+    from geodesia_kv_b200.live_cache import PagedKVCache
+    model, name = tiny_qwen3(seed=5)
+    model.config._attn_implementation = name
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    prompt = torch.randint(0, 512, (2, 200), device="cuda", generator=gen)
+    cache = PagedKVCache(num_layers=2, budget_bits=4.0, maintain_every=32)
+    with torch.no_grad():
+        out = model.generate(prompt, past_key_values=cache, max_new_tokens=80, do_sample=False, use_cache=True)
+    assert out.shape == (2, 280) and torch.equal(out[:, :200], prompt)
+    assert cache.get_seq_length() == 279 and cache.blocks_demoted > 0          # the last token is not fed back
+    assert cache.pool.bytes_in_use == cache.bytes_in_use()

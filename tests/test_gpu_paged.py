@@ -350,3 +350,34 @@ def test_serving_manager_stores_sequences_in_one_pool_and_frees_them():
     mgr.free_sequence_cache(7)
     mgr.free_sequence_cache(9)
     assert pool.bytes_in_use == 0 and pool.bytes_reserved == 0
+
+
+@pytest.mark.parametrize("D,group,Hq,Hkv", [(64, 32, 8, 2), (128, 16, 4, 4), (64, 16, 14, 2), (128, 64, 16, 2)])
+def test_other_shapes_through_the_pool(oracle, D, group, Hq, Hkv):
+    """Head dim 64, groups 16 and 64, GQA widths 1, 2, 7, 8: prompts of odd lengths, demotion, tokens appended
+    across block boundaries, then one call over the ragged batch against the oracle."""
+    from geodesia_kv_b200.paged import PagedLayerCache, PagedPool
+    lengths = [64 * 9 + 31, 5, 64 * 14]
+    B = len(lengths)
+    pool = PagedPool(128 << 20, D, group)
+    layer = PagedLayerCache(pool, B, Hkv, cap_blocks=8)
+    k, v = dense_batch(D + group + Hq, B, Hkv, max(lengths), D)
+    layer.prefill(k, v, lengths)
+    layer.maintain(3.5, mass=power_law_mass(layer), window=64)
+    gen = torch.Generator(device="cuda").manual_seed(D)
+    for _ in range(70):
+        layer.append(torch.randn(B, Hkv, 1, D, device="cuda", generator=gen).to(torch.bfloat16),
+                     torch.randn(B, Hkv, 1, D, device="cuda", generator=gen).to(torch.bfloat16))
+    layer.maintain(3.5, mass=power_law_mass(layer), window=64)
+    q = (torch.randn(B, Hq, D, device="cuda", generator=gen) * D ** -0.5).contiguous()
+    out, mass = layer.attend(q, want_mass=True)
+    torch.cuda.synchronize()
+    assert int(layer.status.item()) == 0 and layer.len_h.tolist() == [n + 70 for n in lengths]
+    c = rows_for_oracle(layer)
+    args = (c["data"], c["offs"], c["klo"], c["kstep"], c["vlo"], c["vstep"], c["level"], c["valid"], P, group)
+    want = oracle.mixed_attn_decode(q.cpu().numpy(), *args)
+    assert np.abs(out.cpu().numpy() - want).max() <= 2e-3
+    wm = oracle.block_mass(q.cpu().numpy(), *args).reshape(B * Hkv, -1)
+    assert np.abs(mass.cpu().numpy()[:, :wm.shape[1]] - wm).max() <= 1e-5
+    assert pool.bytes_in_use == layer.bytes_in_pool()
+    assert (layer.level_h[layer.level_h > 0] < 16).any()
