@@ -395,7 +395,7 @@ def measure_paged(wname, args, env):
     lengths_all = lognormal_lengths(w)
     lengths = lengths_all[rank::world]                           # sequences are dealt round-robin to the GPUs
     B = int(lengths.size)
-    steps_ahead = 64 * (2 + (3 * (max(args.warmup, 3) + args.steps) + 8) // 64)
+    steps_ahead = 64 * (2 + (4 * (max(args.warmup, 3) + args.steps) + 24) // 64)
     dense_layer = int(lengths.sum()) * Hkv * D * 2 * 2
     # room for the final caches (about budget/16 of dense plus the exact blocks), one layer's rung-16
     # transient while it is being built, and the blocks the timed steps will open
@@ -537,6 +537,25 @@ def measure_paged(wname, args, env):
             ms_e2e, e2e_mode = timed(run_e2e, args.steps), "cuda graph of one step, copies included"
         except Exception:
             torch.cuda.synchronize()
+    # the same step without the mass by-product and its running mean (a serving loop that refreshes the
+    # masses only every few tokens runs most of its steps like this)
+    def step_plain():
+        for c, q, k1, v1 in zip(layers, qs, kn, vn):
+            c.append_device(k1, v1)
+            c.attend(q)
+    ms_plain = None
+    try:
+        for _ in range(2):
+            step_plain()
+        barrier()
+        graph_plain = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph_plain, capture_error_mode="thread_local"):
+            step_plain()
+        barrier()
+        graph_plain.replay()
+        ms_plain = timed(graph_plain.replay, args.steps) / args.steps
+    except Exception:
+        torch.cuda.synchronize()
     status = max(int(c.status.item()) for c in layers)
     for c in layers:
         c.sync_lengths()
@@ -575,6 +594,9 @@ def measure_paged(wname, args, env):
                 "eager_value": seqs_total / (ms_e2e_eager / args.steps / 1e3), "eager_ms_per_step": ms_e2e_eager / args.steps},
         "gpu_launches": args.steps * L * per_call,
         "append_status": status,
+        "without_mass": (None if ms_plain is None else
+                         {"ms_per_step": ms_plain, "value": seqs_total / (ms_plain / 1e3), "unit": "tokens/s",
+                          "hbm_gbs_per_gpu": alg / (ms_plain / 1e3 / L) / 1e9, "frac": alg / (ms_plain / 1e3 / L) / 1e9 / peak}),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "traffic": None,
                      "kernel": "decode split kernel over the block table (+ append, merge and mass kernels, timed together)",

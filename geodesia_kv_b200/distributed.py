@@ -18,7 +18,7 @@ local memory, then the local merge kernel.
 from __future__ import annotations
 
 import ctypes
-from typing import Callable, Sequence
+from typing import Callable
 
 import torch
 import torch.distributed as dist

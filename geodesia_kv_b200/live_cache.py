@@ -96,7 +96,10 @@ class PagedKVCache(Cache):
     ``budget_bits`` is the resident budget in bits per cached value (0 keeps every block exact);
     ``layer_budget_bits`` overrides it per layer.  ``pool`` shares one pool between caches;
     otherwise ``pool_bytes`` (or a size derived from the first prompt and ``max_new_tokens``) is
-    allocated on first use.  The remaining fields are the reference policy's
+    allocated on first use.  A batch is B sequences of the SAME prompt length (no padding tokens:
+    ragged batches go through :class:`PagedLayerCache` directly, which takes per-sequence lengths);
+    the prompt arrives in one forward pass, then one token per step.  Everything runs on the
+    current stream.  The remaining fields are the reference policy's
     (``policies.py:227-272``): sinks, window, obs, mass_decay, alloc_mass_power, alloc_value_weight.
     """
 
