@@ -196,8 +196,8 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __global__ void __launch_bounds__(kCombineThreads) exchange_combine_kernel(CombineParams p, ExchangeParams x) {
@@ -280,12 +280,12 @@ __global__ void __launch_bounds__(kCombineThreads) exchange_combine_kernel(Combi
         }
         for (int r = 0; r < x.world; ++r) x.inbox[r][slot + d] = a;
     }
-    __threadfence_system();
+    __threadfence_system();                 // every thread's record stores are visible system-wide ...
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int r = 0; r < x.world; ++r) st_release_sys(x.flags[r] + (size_t)x.rank * x.rows + orow, seq);
-        x.seq[orow] = seq;
-    }
+    // ... before the sequence numbers go out: one relaxed store per destination rank, issued by `world`
+    // threads at once (a release store per rank from one thread would serialise a round trip each)
+    if (threadIdx.x < x.world) st_relaxed_sys(x.flags[threadIdx.x] + (size_t)x.rank * x.rows + orow, seq);
+    if (threadIdx.x == 0) x.seq[orow] = seq;
     // one thread per source rank waits for that rank's record of this call
     if (threadIdx.x < x.world) {
         const int* f = x.flags[x.rank] + (size_t)threadIdx.x * x.rows + orow;
