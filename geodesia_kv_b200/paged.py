@@ -209,6 +209,8 @@ class PagedLayerCache:
             raise ValueError("prefill needs an empty cache of matching shape")
         k, v = k.contiguous(), v.contiguous()
         lengths = np.full(B, T, dtype=np.int64) if lengths is None else np.asarray(lengths, dtype=np.int64)
+        if lengths.shape != (B,) or int(lengths.min()) < 1 or int(lengths.max()) > T:
+            raise ValueError("one length per sequence, between 1 and the number of token rows given")
         nblk = (lengths + BLOCK - 1) // BLOCK
         if int(nblk.max()) + 1 > self.cap:
             self._grow(int(nblk.max()) + 1 + 16)
