@@ -25,7 +25,6 @@ SIGNATURES = {
     "gkv_decode_launch_count": (_i, [_i] * 7),
     "gkv_set_decode_kernel": (_i, [_i]),
     "gkv_set_decode_item_blocks": (_i, [_i]),
-    "gkv_set_decode_interleave": (_i, [_i]),
     "gkv_decode_status": (_i, [_vp, C.POINTER(_i), _vp]),
     "gkv_decode_plan_bytes": (_sz, [_i, _i]),
     "gkv_decode_build_plan": (_i, [_vp] * 4 + [_i, _i, _vp]),

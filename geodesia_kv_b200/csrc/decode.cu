@@ -353,8 +353,6 @@ static int g_decode_kernel = 0;
 static bool force_generic() { return g_decode_kernel == 1; }
 // Process-wide override of the tensor-core kernel's work-item size (gkv_set_decode_item_blocks): 0 = by problem size.
 static int g_item_blocks = 0;
-static int g_interleave = 0;     // odd rows walk their rungs in another order than even rows (tensor-core kernel); measured
-                                 // 12 % slower on the 16k workload (the heavy items no longer all come first), so off
 
 // Per-device facts and one-time set-up, keyed by the CUDA device ordinal (a process may drive
 // several GPUs; function attributes and the SM count belong to the device, not the process).
@@ -604,7 +602,6 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         mp.items_per_row = pl.nsplit; mp.items = rows * pl.nsplit; mp.per_row_meta = meta_rows != 1;
         mp.stride_bh = paged ? 0 : stride_bh;
         mp.paged = paged ? 1 : 0;
-        mp.interleave = g_interleave;
         int rc;
         const size_t total = paged ? pool_bytes : (size_t)rows * (size_t)stride_bh;   // bytes the tensor maps span
         if (D == 128 && group == 32) rc = launch_mma<128, 32>(mp, total, pl.grid, stream);
@@ -709,11 +706,6 @@ int gkv_decode_kernel_launches(int B, int Hq, int Hkv, int D, int nb, int group)
 int gkv_set_decode_kernel(int which) {
     if (which != 0 && which != 1) return GKV_E_ARG;
     gkv::g_decode_kernel = which;
-    return GKV_OK;
-}
-
-int gkv_set_decode_interleave(int on) {
-    gkv::g_interleave = on ? 1 : 0;
     return GKV_OK;
 }
 

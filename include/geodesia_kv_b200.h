@@ -91,11 +91,6 @@ int gkv_set_decode_kernel(int which);
  * reference, whose split is fixed by its launcher (geodesia_kv_cuda/mixed_attn.cu:222-224).      */
 int gkv_set_decode_item_blocks(int blocks);
 
-/* Tuning switch (process-wide, default OFF): odd cache rows walk their rungs in the order 4, 2, 16, 8,
- * centroid instead of 16, 8, 4, 2, centroid, so that at any time some SMs stream wide blocks while
- * others unpack narrow ones.  The result does not depend on it; on B200 it measured 12 % slower on
- * the 16k-token workload (240 -> 270 us per layer), which is why it is off.                        */
-int gkv_set_decode_interleave(int on);
 
 /* What happens when a wait inside the tensor-core kernel runs out.  Every wait of that kernel (on
  * a shared-memory barrier that a copy or another warp completes) gives up after about one second
