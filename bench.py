@@ -315,6 +315,8 @@ def measure_decode(wname, args, env):
         sampler.start()
     ms_total = timed(run_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    # the same resident step with plain launches (what a caller without a CUDA graph sees)
+    ms_eager_resident = ms_total if run_step is step_resident else timed(step_resident, args.steps)
     for _ in range(2):
         step_e2e()
     ms_e2e_eager = timed(step_e2e, args.steps)
@@ -353,6 +355,7 @@ def measure_decode(wname, args, env):
         "vs_baseline": None, "dtype": "fp32 accumulate over u8/bf16/fp16 packed bytes", "data": "synthetic",
         "config": dict(workload_config(w, world, split, cache_bytes / 1e9), launch=launch_mode, exchange=exchange),
         "per_gpu": value / world,
+        "eager_ms_per_step": ms_eager_resident / args.steps,
         "hbm_gbs_per_gpu": achieved,
         "e2e": {"value": tokens_per_step / (ms_e2e / args.steps / 1e3), "unit": UNIT,
                 "h2d_bytes_per_step": L * B * Hq * D * 4, "d2h_bytes_per_step": L * B * Hq * D * 4,
@@ -776,7 +779,7 @@ def run_gpu(args):
         line = measure_decode("cfg1", args, env)
         env["cpu_baseline"] = False
         c3 = measure_decode("cfg3", args, env)
-        line["cfg3"] = {k: c3[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "ms_per_step", "scaling", "config",
+        line["cfg3"] = {k: c3[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "ms_per_step", "eager_ms_per_step", "scaling", "config",
                                            "per_gpu", "hbm_gbs_per_gpu", "e2e", "gpu_launches", "roofline")}
     if world > 1:
         dist.destroy_process_group()
