@@ -52,9 +52,12 @@ constexpr int kCombineThreads = 256;
 // records, and the NW states are merged through shared memory — the same recurrence at both levels.
 // NW = 8 normally; 32 for rows with a few hundred records, which one wide CTA merges faster than
 // two launches of narrow ones (the single-sequence case, where the call is launch-bound).
-template <int NW>
+// KPER = channels per lane (D <= 32 * KPER): head dims up to 128 take the instantiation with half the
+// registers, which lets half as many more CTAs sit on an SM (the kernel is bound by the latency of its few
+// loads per warp, i.e. by how many CTAs are resident).
+template <int NW, int KPER = kMaxD / 32>
 __global__ void __launch_bounds__(NW * 32) combine_kernel(CombineParams p) {
-    __shared__ float sm_m[NW], sm_l[NW], sm_o[NW][kMaxD];
+    __shared__ float sm_m[NW], sm_l[NW], sm_o[NW][32 * KPER];
     const int orow = blockIdx.x, D = p.D;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* base;
@@ -68,7 +71,7 @@ __global__ void __launch_bounds__(NW * 32) combine_kernel(CombineParams p) {
         stride = p.stride_s;
     }
     const float poison = (p.status && *p.status) ? __int_as_float(0x7fc00000) : 0.f;
-    constexpr int kPer = kMaxD / 32;                  // channels per lane
+    constexpr int kPer = KPER;                        // channels per lane
     float m = -INFINITY, l = 0.f, o[kPer];
 #pragma unroll
     for (int i = 0; i < kPer; ++i) o[i] = 0.f;
@@ -79,7 +82,7 @@ __global__ void __launch_bounds__(NW * 32) combine_kernel(CombineParams p) {
     // kBatch records at a time: all their loads are issued before the first is merged (the merge
     // itself is a serial recurrence, and one load round trip per record made this kernel
     // latency-bound); the order of the merge is unchanged.
-    constexpr int kBatch = 4;
+    constexpr int kBatch = KPER <= 4 ? 8 : 4;         // as many as fit the registers
     for (int s0 = s_lo + warp; s0 < s_hi; s0 += NW * kBatch) {
         float ms[kBatch], ls[kBatch], v[kBatch][kPer];
 #pragma unroll
@@ -645,7 +648,8 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
         // level 1: (rows, parts, rep, D+2) -> (segs, B*Hq, D+2) behind the records
         float* mid = records + (size_t)B * Hq * pl.parts * (D + 2);
         c.out = mid; c.normalise = 0; c.segs = pl.segs; c.per_seg = (pl.parts + pl.segs - 1) / pl.segs;
-        combine_kernel<8><<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
+        if (D <= 128) combine_kernel<8, 4><<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
+        else combine_kernel<8><<<dim3(B * Hq, pl.segs), kCombineThreads, 0, stream>>>(c);
         GKV_LAUNCH_CHECK();
         c.rec = mid; c.out = out; c.parts = pl.segs; c.rep = 0; c.nsplit = 0; c.plan_tab = nullptr;
         c.stride_s = (int64_t)B * Hq * (D + 2); c.normalise = normalise; c.segs = 1; c.per_seg = 0;
@@ -653,6 +657,7 @@ static int decode_impl(const float* q, const uint8_t* data, const int64_t* offs,
     c.ml_out = mass_ml;
     if (xch) exchange_combine_kernel<<<B * Hq, kCombineThreads, 0, stream>>>(c, *xch);
     else if (pl.wide && pl.segs <= 1) combine_kernel<32><<<B * Hq, 1024, 0, stream>>>(c);
+    else if (D <= 128) combine_kernel<8, 4><<<B * Hq, kCombineThreads, 0, stream>>>(c);
     else combine_kernel<8><<<B * Hq, kCombineThreads, 0, stream>>>(c);
     GKV_LAUNCH_CHECK();
     if (mass_out) {
@@ -839,7 +844,8 @@ int gkv_combine_partials(const float* partials, float* out, int parts, int rows,
     c.rec = partials; c.out = out; c.parts = parts; c.D = D; c.rep = 0; c.nsplit = 0;
     c.stride_s = (int64_t)rows * (D + 2); c.normalise = 1; c.status = nullptr; c.segs = 1; c.per_seg = 0; c.ml_out = nullptr;
     c.plan_tab = nullptr; c.chunk = 1; c.tab_per_row = 0; c.warps_per_item = 1;
-    gkv::combine_kernel<8><<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    if (D <= 128) gkv::combine_kernel<8, 4><<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    else gkv::combine_kernel<8><<<rows, gkv::kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(c);
     GKV_LAUNCH_CHECK();
     return GKV_OK;
 }
