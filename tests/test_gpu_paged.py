@@ -318,6 +318,10 @@ def test_one_block_per_step_for_64_steps_against_the_oracle(oracle, budget):
         assert pool.bytes_in_use == layer.bytes_in_pool()
     assert demoted_total >= rows * (steps - 4)
     assert layer.bits_per_value() <= budget + 16.0 * 5 / (nb0 + steps) + 1e-6
+    # none of the pack/demote kernels' bounded waits ever ran out
+    import ctypes
+    word = ctypes.c_int(-1)
+    assert layer.lib.gkv_maintenance_status(ctypes.byref(word)) == 0 and word.value == 0
 
 
 def test_serving_manager_stores_sequences_in_one_pool_and_frees_them():
